@@ -1,0 +1,45 @@
+// C entry points of libhi_b200_kernels.so. Every function enqueues work on `stream` and
+// returns 0, a cudaError_t, or one of the HB_ERR_* codes of common.cuh; none of them
+// synchronises. dtype codes: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int n, int hidden,
+                    int vocab, cudaStream_t stream);
+int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w, int w_dtype, void* y,
+                   int y_dtype, const int* row_map, int rows, int hidden, float eps, cudaStream_t stream);
+int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream);
+int hb_moe_combine(const float* y, const int* slot_of_entry, const void* shared, int shared_dtype, float* out,
+                   int n, int hidden, int top_k, cudaStream_t stream);
+
+int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, int rot_pairs, int interleaved, int qk_norm,
+                float qk_eps, int temp_on, float floor_scale, float attn_scale, const int* positions,
+                const int* seq_of_token, const int* block_table, int table_stride, void* q_out, void* k_pages,
+                void* v_pages, int page_size, int write_kv, int n_tokens, int nh, int nkv, int hd,
+                cudaStream_t stream);
+
+int hb_paged_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
+                       const int* block_table, int table_stride, const int* seq_of_token, const int* positions,
+                       void* out, int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
+                       float scale, cudaStream_t stream);
+
+int hb_router_topk(const void* x, const void* w, int dtype, int n, int hidden, int experts, int top_k,
+                   float* logits_out, int* ids, float* scores, cudaStream_t stream);
+int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
+                int* slot_of_entry, cudaStream_t stream);
+int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,
+                   const void* w_up, const int* offsets, int experts, const float* scores, void* act,
+                   int n_entries, int inter, int hidden, int few_rows, cudaStream_t stream);
+int hb_moe_down(const void* act, int dtype, const void* w_down, const int* offsets, int experts, float* y,
+                int n_entries, int hidden, int inter, int few_rows, cudaStream_t stream);
+
+int hb_sample_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* uniforms,
+                   int* out, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,133 @@
+// Embedding gather, residual-add + RMSNorm, SwiGLU, expert-output combine.
+// The residual stream is float32 in every mode; statistics and sums are float32.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float load_any(const void* p, int dtype, size_t i) {
+  return dtype == HB_DTYPE_F32 ? reinterpret_cast<const float*>(p)[i]
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void store_any(void* p, int dtype, size_t i, float v) {
+  if (dtype == HB_DTYPE_F32) reinterpret_cast<float*>(p)[i] = v;
+  else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// x[t, :] = table[token[t], :]   (crates/hi-mlx/src/models.rs:6206: no multiplier)
+__global__ void embed_gather_kernel(const void* table, int table_dtype, const int* tokens,
+                                    float* out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  const bool ok = id >= 0 && id < vocab;
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x)
+    out[(size_t)t * hidden + j] = ok ? load_any(table, table_dtype, (size_t)id * hidden + j) : 0.f;
+}
+
+// Row r of the output: src = row_map ? row_map[r] : r.
+//   s = x[src] (+ delta[src]);  if no row_map: x[src] = s  (the residual sum, float32)
+//   y[r] = s * rsqrt(mean(s^2) + eps) * w     (crates/hi-cuda/src/kernels.cu:61-77)
+__global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype, const void* w,
+                                   int w_dtype, void* y, int y_dtype, const int* row_map,
+                                   int hidden, float eps) {
+  __shared__ float scratch[33];
+  extern __shared__ float row[];  // hidden floats
+  const int r = blockIdx.x;
+  const size_t src = row_map ? (size_t)row_map[r] : (size_t)r;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+    float s = x[src * hidden + j];
+    if (delta) s += load_any(delta, delta_dtype, src * hidden + j);
+    row[j] = s;
+    ss += s * s;
+  }
+  const float total = hb::block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+    const float s = row[j];
+    if (!row_map && delta) x[src * hidden + j] = s;
+    const float wv = w ? load_any(w, w_dtype, j) : 1.f;
+    store_any(y, y_dtype, (size_t)r * hidden + j, s * inv * wv);
+  }
+}
+
+// out[t, j] = silu(in[t, j]) * in[t, inter + j]   (crates/hi-mlx/src/models.rs:2307-2312)
+__global__ void swiglu_kernel(const void* in, void* out, int dtype, size_t rows, int inter) {
+  const size_t total = rows * (size_t)inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter;
+    const int j = (int)(i - t * inter);
+    const float g = load_any(in, dtype, t * 2 * inter + j);
+    const float u = load_any(in, dtype, t * 2 * inter + inter + j);
+    store_any(out, dtype, i, g / (1.f + expf(-g)) * u);
+  }
+}
+
+// out[t, :] = shared[t, :] + sum_j y[slot_of_entry[t*k + j], :]   in rank order, no atomics
+// (crates/hi-cuda/src/kernels.cu:10661-10680; models.rs:6099 adds the shared expert).
+__global__ void moe_combine_kernel(const float* y, const int* slot_of_entry, const void* shared,
+                                   int shared_dtype, float* out, int hidden, int top_k) {
+  const int t = blockIdx.x;
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+    float s = shared ? load_any(shared, shared_dtype, (size_t)t * hidden + j) : 0.f;
+    for (int r = 0; r < top_k; ++r)
+      s += y[(size_t)slot_of_entry[t * top_k + r] * hidden + j];
+    out[(size_t)t * hidden + j] = s;
+  }
+}
+
+bool dtype_ok(int d) { return d == HB_DTYPE_F32 || d == HB_DTYPE_BF16; }
+
+}  // namespace
+
+extern "C" int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out,
+                               int n, int hidden, int vocab, cudaStream_t stream) {
+  if (!table || !tokens || !out || n < 0 || hidden <= 0 || vocab <= 0 || !dtype_ok(table_dtype))
+    return HB_ERR_BAD_ARG;
+  if (n == 0) return HB_OK;
+  embed_gather_kernel<<<n, 256, 0, stream>>>(table, table_dtype, tokens, out, hidden, vocab);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w,
+                              int w_dtype, void* y, int y_dtype, const int* row_map, int rows,
+                              int hidden, float eps, cudaStream_t stream) {
+  if (!x || !y || rows < 0 || hidden <= 0 || !dtype_ok(y_dtype) || (delta && !dtype_ok(delta_dtype)) ||
+      (w && !dtype_ok(w_dtype)))
+    return HB_ERR_BAD_ARG;
+  if (rows == 0) return HB_OK;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 200 * 1024) return HB_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int threads = hidden >= 2048 ? 512 : 256;
+  add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, w, w_dtype, y, y_dtype,
+                                                      row_map, hidden, eps);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream) {
+  if (!in || !out || rows < 0 || inter <= 0 || !dtype_ok(dtype)) return HB_ERR_BAD_ARG;
+  if (rows == 0) return HB_OK;
+  const size_t total = (size_t)rows * inter;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  swiglu_kernel<<<blocks, 256, 0, stream>>>(in, out, dtype, (size_t)rows, inter);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_moe_combine(const float* y, const int* slot_of_entry, const void* shared,
+                              int shared_dtype, float* out, int n, int hidden, int top_k,
+                              cudaStream_t stream) {
+  if (!y || !slot_of_entry || !out || n < 0 || hidden <= 0 || top_k <= 0 || (shared && !dtype_ok(shared_dtype)))
+    return HB_ERR_BAD_ARG;
+  if (n == 0) return HB_OK;
+  moe_combine_kernel<<<n, 256, 0, stream>>>(y, slot_of_entry, shared, shared_dtype, out, hidden, top_k);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}

@@ -1,0 +1,358 @@
+// Routed experts: router top-k, the device-side plan (rows grouped by expert), and the
+// general grouped matrix products with the SwiGLU epilogue. No step here returns to the host
+// (the reference syncs per layer to pick the expert: crates/hi-mlx/src/models.rs:6081-6084).
+//
+// Formulas (models.rs:6086-6100): score = sigmoid(selected router logit); the score scales the
+// expert INPUT: act = silu(s * (x Wg^T)) * (s * (x Wu^T)) — by linearity equal to feeding s*x —
+// and y = act Wd^T. Ties between equal logits go to the lower expert id
+// (crates/hi-cuda/src/kernels.cu:578-580). All accumulation, the sigmoid and SwiGLU are float32.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------ router
+// One block per token; warps take experts in turn; lanes stride over the hidden dim.
+template <typename T>
+__global__ void router_topk_kernel(const T* __restrict__ x, const T* __restrict__ w, int hidden, int experts,
+                                   int top_k, float* __restrict__ logits_out, int* __restrict__ ids,
+                                   float* __restrict__ scores) {
+  extern __shared__ float lg[];  // [experts]
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const T* xr = x + (size_t)t * hidden;
+  for (int e = warp; e < experts; e += nwarps) {
+    const T* wr = w + (size_t)e * hidden;
+    float s = 0.f;
+    for (int j = lane; j < hidden; j += 32) s += hb::to_f32(xr[j]) * hb::to_f32(wr[j]);
+    s = hb::warp_sum(s);
+    if (lane == 0) {
+      lg[e] = s;
+      if (logits_out) logits_out[(size_t)t * experts + e] = s;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < top_k; ++r) {
+      int best = -1;
+      float bv = 0.f;
+      for (int e = 0; e < experts; ++e) {
+        bool taken = false;
+        for (int q = 0; q < r; ++q) taken |= (ids[(size_t)t * top_k + q] == e);
+        if (taken) continue;
+        const float v = lg[e];
+        if (best < 0 || v > bv) { best = e; bv = v; }  // strict '>' keeps the lowest id on ties
+      }
+      ids[(size_t)t * top_k + r] = best;
+      scores[(size_t)t * top_k + r] = 1.f / (1.f + expf(-bv));
+    }
+  }
+}
+
+// ------------------------------------------------------------------ plan
+// Stable counting sort of the n = tokens*top_k routing entries by expert, in one block:
+// offsets[e]..offsets[e+1] are the sorted slots of expert e, in entry order.
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int experts, int* __restrict__ offsets,
+                                int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry) {
+  extern __shared__ int sm[];  // cnt[experts], base[experts]
+  int* cnt = sm;
+  int* base = sm + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      offsets[e] = run;
+      base[e] = run;
+      run += cnt[e];
+    }
+    offsets[experts] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    for (int start = 0; start < n; start += 32) {
+      const int i = start + lane;
+      int e = i < n ? ids[i] : -1;
+      if (e >= experts) e = -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      if (e >= 0) {
+        const int slot = base[e] + rank;
+        sorted_entry[slot] = i;
+        slot_of_entry[i] = slot;
+      }
+      __syncwarp();
+      if (e >= 0 && rank == 0) base[e] += __popc(peers);
+      __syncwarp();
+    }
+  }
+}
+
+// ------------------------------------------------------------------ grouped products, general form
+// C[r, n] = sum_k A[row(r), k] * W[e(r), n, k] for the sorted slots r of every expert e.
+// DUAL: two weight stacks (gate, up); out = silu(s*g) * (s*u) in the engine dtype.
+// else: out = float32 product (the down projection).
+// Tiles BM x BN over (expert, rows of that expert) x columns; any K, any number of columns.
+constexpr int BM = 32, BN = 64, BK = 16, GT = 256;
+
+template <typename T, bool DUAL>
+__global__ void grouped_gemm_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry,
+                                    int top_k, const T* __restrict__ W0, const T* __restrict__ W1,
+                                    const int* __restrict__ offsets, int experts,
+                                    const float* __restrict__ scores, void* __restrict__ out, int n_out,
+                                    int K) {
+  __shared__ float As[BK][BM + 1];
+  __shared__ float Bs0[BK][BN + 1];
+  __shared__ float Bs1[DUAL ? BK : 1][BN + 1];
+  __shared__ int tile_expert, tile_row0, tile_rows;
+  if (threadIdx.x == 0) {
+    // blockIdx.y-th row tile in expert order
+    int want = blockIdx.y, e = 0, found = -1, r0 = 0, rows = 0;
+    for (; e < experts; ++e) {
+      const int c = offsets[e + 1] - offsets[e];
+      const int tiles = (c + BM - 1) / BM;
+      if (want < tiles) {
+        found = e;
+        r0 = offsets[e] + want * BM;
+        rows = min(BM, offsets[e + 1] - r0);
+        break;
+      }
+      want -= tiles;
+    }
+    tile_expert = found; tile_row0 = r0; tile_rows = rows;
+  }
+  __syncthreads();
+  const int e = tile_expert;
+  if (e < 0) return;
+  const int row0 = tile_row0, rows = tile_rows;
+  const int col0 = blockIdx.x * BN;
+  const T* w0 = W0 + (size_t)e * n_out * K;
+  const T* w1 = DUAL ? W1 + (size_t)e * n_out * K : nullptr;
+
+  const int tm = threadIdx.x / 16;  // 0..15 -> rows tm*2, tm*2+1
+  const int tn = threadIdx.x % 16;  // 0..15 -> cols tn*4 .. tn*4+3
+  float acc0[2][4] = {}, acc1[2][4] = {};
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    // A tile: BM x BK
+    for (int i = threadIdx.x; i < BM * BK; i += GT) {
+      const int r = i / BK, k = i % BK;
+      float v = 0.f;
+      if (r < rows && k0 + k < K) {
+        const int slot = row0 + r;
+        const size_t arow = sorted_entry ? (size_t)(sorted_entry[slot] / top_k) : (size_t)slot;
+        v = hb::to_f32(A[arow * lda + k0 + k]);
+      }
+      As[k][r] = v;
+    }
+    for (int i = threadIdx.x; i < BN * BK; i += GT) {
+      const int n = i / BK, k = i % BK;
+      const bool ok = col0 + n < n_out && k0 + k < K;
+      Bs0[k][n] = ok ? hb::to_f32(w0[(size_t)(col0 + n) * K + k0 + k]) : 0.f;
+      if (DUAL) Bs1[k][n] = ok ? hb::to_f32(w1[(size_t)(col0 + n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      const float a0 = As[k][tm * 2], a1 = As[k][tm * 2 + 1];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float b = Bs0[k][tn * 4 + c];
+        acc0[0][c] += a0 * b;
+        acc0[1][c] += a1 * b;
+        if (DUAL) {
+          const float b1 = Bs1[k][tn * 4 + c];
+          acc1[0][c] += a0 * b1;
+          acc1[1][c] += a1 * b1;
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int r = tm * 2 + rr;
+    if (r >= rows) continue;
+    const int slot = row0 + r;
+    float s = 1.f;
+    if (DUAL) s = scores[sorted_entry ? sorted_entry[slot] : slot];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int n = col0 + tn * 4 + c;
+      if (n >= n_out) continue;
+      if (DUAL) {
+        const float g = s * acc0[rr][c], u = s * acc1[rr][c];
+        reinterpret_cast<T*>(out)[(size_t)slot * n_out + n] = hb::from_f32<T>(g / (1.f + expf(-g)) * u);
+      } else {
+        reinterpret_cast<float*>(out)[(size_t)slot * n_out + n] = acc0[rr][c];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ grouped products, few rows per expert
+// Decode shape: the weights are streamed once, each warp owns output columns and keeps up to
+// RMAX rows' partial sums; 16-byte loads along K. Needs K % 8 == 0.
+constexpr int RMAX = 4;
+constexpr int GEMV_WARPS = 8;
+constexpr int GEMV_COLS_PER_WARP = 4;
+
+template <typename T, bool DUAL>
+__global__ void grouped_gemv_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry,
+                                    int top_k, const T* __restrict__ W0, const T* __restrict__ W1,
+                                    const int* __restrict__ offsets, const float* __restrict__ scores,
+                                    void* __restrict__ out, int n_out, int K) {
+  const int e = blockIdx.y;
+  const int begin = offsets[e], end = offsets[e + 1];
+  if (begin == end) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int colbase = (blockIdx.x * GEMV_WARPS + warp) * GEMV_COLS_PER_WARP;
+  for (int r0 = begin; r0 < end; r0 += RMAX) {
+    const int nr = min(RMAX, end - r0);
+    const T* arow[RMAX];
+    float sc[RMAX];
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r) {
+      const int slot = r0 + (r < nr ? r : 0);
+      const size_t ar = sorted_entry ? (size_t)(sorted_entry[slot] / top_k) : (size_t)slot;
+      arow[r] = A + ar * lda;
+      sc[r] = DUAL ? scores[sorted_entry ? sorted_entry[slot] : slot] : 1.f;
+    }
+    for (int c = 0; c < GEMV_COLS_PER_WARP; ++c) {
+      const int n = colbase + c;
+      if (n >= n_out) break;
+      const T* w0 = W0 + ((size_t)e * n_out + n) * K;
+      const T* w1 = DUAL ? W1 + ((size_t)e * n_out + n) * K : nullptr;
+      float g[RMAX] = {}, u[RMAX] = {};
+      for (int k = lane * 8; k < K; k += 256) {
+        float wv[8], wu[8];
+        hb::load8(w0 + k, wv);
+        if (DUAL) hb::load8(w1 + k, wu);
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r) {
+          if (r < nr) {
+            float av[8];
+            hb::load8(arow[r] + k, av);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              g[r] += av[i] * wv[i];
+              if (DUAL) u[r] += av[i] * wu[i];
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r) {
+        if (r < nr) {
+          const float gs = hb::warp_sum(g[r]);
+          const float us = DUAL ? hb::warp_sum(u[r]) : 0.f;
+          if (lane == 0) {
+            const size_t o = (size_t)(r0 + r) * n_out + n;
+            if (DUAL) {
+              const float gg = sc[r] * gs, uu = sc[r] * us;
+              reinterpret_cast<T*>(out)[o] = hb::from_f32<T>(gg / (1.f + expf(-gg)) * uu);
+            } else {
+              reinterpret_cast<float*>(out)[o] = gs;
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_grouped(bool dual, const void* A, int lda, const int* sorted_entry, int top_k, const void* W0,
+                   const void* W1, const int* offsets, int experts, const float* scores, void* out, int n_entries,
+                   int n_out, int K, int few_rows, cudaStream_t stream) {
+  if (few_rows && K % 8 == 0 && lda % 8 == 0) {
+    dim3 grid((n_out + GEMV_WARPS * GEMV_COLS_PER_WARP - 1) / (GEMV_WARPS * GEMV_COLS_PER_WARP), experts);
+    if (dual)
+      grouped_gemv_kernel<T, true><<<grid, GEMV_WARPS * 32, 0, stream>>>(
+          (const T*)A, lda, sorted_entry, top_k, (const T*)W0, (const T*)W1, offsets, scores, out, n_out, K);
+    else
+      grouped_gemv_kernel<T, false><<<grid, GEMV_WARPS * 32, 0, stream>>>(
+          (const T*)A, lda, sorted_entry, top_k, (const T*)W0, nullptr, offsets, scores, out, n_out, K);
+  } else {
+    const int max_tiles = (n_entries + BM - 1) / BM + (experts < n_entries ? experts : n_entries);
+    dim3 grid((n_out + BN - 1) / BN, max_tiles);
+    if (grid.y > 65535) return HB_ERR_UNSUPPORTED;
+    if (dual)
+      grouped_gemm_kernel<T, true><<<grid, GT, 0, stream>>>((const T*)A, lda, sorted_entry, top_k, (const T*)W0,
+                                                            (const T*)W1, offsets, experts, scores, out, n_out, K);
+    else
+      grouped_gemm_kernel<T, false><<<grid, GT, 0, stream>>>((const T*)A, lda, sorted_entry, top_k, (const T*)W0,
+                                                             nullptr, offsets, experts, scores, out, n_out, K);
+  }
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+}  // namespace
+
+extern "C" int hb_router_topk(const void* x, const void* w, int dtype, int n, int hidden, int experts, int top_k,
+                              float* logits_out, int* ids, float* scores, cudaStream_t stream) {
+  if (!x || !w || !ids || !scores || n < 0 || hidden <= 0 || experts <= 0 || top_k <= 0 || top_k > experts)
+    return HB_ERR_BAD_ARG;
+  if (experts > 4096) return HB_ERR_UNSUPPORTED;
+  if (n == 0) return HB_OK;
+  const size_t smem = (size_t)experts * sizeof(float);
+  if (dtype == HB_DTYPE_F32)
+    router_topk_kernel<float><<<n, 128, smem, stream>>>((const float*)x, (const float*)w, hidden, experts, top_k,
+                                                        logits_out, ids, scores);
+  else if (dtype == HB_DTYPE_BF16)
+    router_topk_kernel<__nv_bfloat16><<<n, 128, smem, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
+  else
+    return HB_ERR_BAD_ARG;
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
+                           int* slot_of_entry, cudaStream_t stream) {
+  if (!ids || !offsets || !sorted_entry || !slot_of_entry || n_entries < 0 || experts <= 0) return HB_ERR_BAD_ARG;
+  if (experts > 4096) return HB_ERR_UNSUPPORTED;
+  moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, n_entries, experts, offsets,
+                                                                          sorted_entry, slot_of_entry);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+// gate/up with SwiGLU: act[slot, :] (engine dtype, [n_entries, inter]).
+extern "C" int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,
+                              const void* w_up, const int* offsets, int experts, const float* scores, void* act,
+                              int n_entries, int inter, int hidden, int few_rows, cudaStream_t stream) {
+  if (!x || !sorted_entry || !w_gate || !w_up || !offsets || !scores || !act || n_entries < 0 || inter <= 0 ||
+      hidden <= 0 || experts <= 0 || top_k <= 0)
+    return HB_ERR_BAD_ARG;
+  if (n_entries == 0) return HB_OK;
+  if (dtype == HB_DTYPE_F32)
+    return launch_grouped<float>(true, x, hidden, sorted_entry, top_k, w_gate, w_up, offsets, experts, scores, act,
+                                 n_entries, inter, hidden, few_rows, stream);
+  if (dtype == HB_DTYPE_BF16)
+    return launch_grouped<__nv_bfloat16>(true, x, hidden, sorted_entry, top_k, w_gate, w_up, offsets, experts, scores,
+                                         act, n_entries, inter, hidden, few_rows, stream);
+  return HB_ERR_BAD_ARG;
+}
+
+// down projection: y[slot, :] float32 [n_entries, hidden].
+extern "C" int hb_moe_down(const void* act, int dtype, const void* w_down, const int* offsets, int experts, float* y,
+                           int n_entries, int hidden, int inter, int few_rows, cudaStream_t stream) {
+  if (!act || !w_down || !offsets || !y || n_entries < 0 || inter <= 0 || hidden <= 0 || experts <= 0)
+    return HB_ERR_BAD_ARG;
+  if (n_entries == 0) return HB_OK;
+  if (dtype == HB_DTYPE_F32)
+    return launch_grouped<float>(false, act, inter, nullptr, 1, w_down, nullptr, offsets, experts, nullptr, y,
+                                 n_entries, hidden, inter, few_rows, stream);
+  if (dtype == HB_DTYPE_BF16)
+    return launch_grouped<__nv_bfloat16>(false, act, inter, nullptr, 1, w_down, nullptr, offsets, experts, nullptr, y,
+                                         n_entries, hidden, inter, few_rows, stream);
+  return HB_ERR_BAD_ARG;
+}

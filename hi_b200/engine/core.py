@@ -1,0 +1,249 @@
+"""The engine: a model on one GPU, its cache, and the ONE step function.
+
+``Engine.step`` takes a batch of (request, its next tokens): portions of prompts beside
+single decoded tokens, cut anywhere. It runs only those tokens, as one batch, against the
+cache that earlier steps left, and returns float32 logits at the wanted places. The
+scheduler, ``generate`` and the trace replay all drive this same function. (The reference
+has three separate forwards for whole prompts, one span, and decode rows:
+crates/hi-cuda/src/gpu.rs:8842-8929, 10541-10715, 9026-9132.)
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.device import DeviceCache, plan_groups
+from ..cache.pages import CacheManager, OutOfPages
+from ..config.registry import load_architecture, lookup
+from ..parts.context import StepContext
+from ..parts.linear import configure_matmul_precision
+from ..parts.model import Model
+from ..weights.loader import load_from_dir, load_random
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "f32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name in (torch.bfloat16, torch.float32):
+            return name
+    elif str(name).lower() in _DTYPES:
+        return _DTYPES[str(name).lower()]
+    raise ValueError(f"dtype {name!r} is not supported (bfloat16 or float32)")
+
+
+def _require_cuda(device) -> None:
+    if not torch.cuda.is_available() or torch.device(device).type != "cuda":
+        raise RuntimeError("hi_b200 needs a CUDA device; there is no CPU path")
+    configure_matmul_precision()
+
+
+def _pinned_int32(n: int) -> torch.Tensor:
+    return torch.empty(n, dtype=torch.int32, pin_memory=True)
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request in one step; ``want`` indexes into ``tokens``."""
+
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    tokens: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    logit_rows: int = 0
+
+
+class Engine:
+    """One model on one CUDA device.
+
+    ``kv_cache_tokens`` sizes every page pool (tokens, rounded up to pages);
+    ``windowed_cache_tokens`` optionally gives the windowed groups (chunked layers) a smaller
+    pool. ``max_active_requests`` is the number of state slots / block-table rows.
+    """
+
+    def __init__(self, model: Model, *, kv_page_size: int = 64, kv_cache_tokens: int = 8192,
+                 windowed_cache_tokens: Optional[int] = None, max_active_requests: int = 8,
+                 debug_poison: bool = False):
+        _require_cuda(model.device)
+        self.model = model
+        self.device = model.device
+        self.dtype = model.dtype
+        self.page_size = int(kv_page_size)
+        groups, self.group_of = plan_groups(model.cache_specs)
+        pages = []
+        for spec in groups:
+            tokens = kv_cache_tokens if (spec.window is None or windowed_cache_tokens is None) else windowed_cache_tokens
+            pages.append(max(1, -(-int(tokens) // self.page_size)))
+        self.manager = CacheManager(groups, pages, self.page_size, max_active_requests)
+        self.cache = DeviceCache(model.cache_specs, pages, self.page_size, max_active_requests, model.dtype,
+                                 self.device)
+        self.vocab_size = model.spec.vocab_size
+        self.stats = EngineStats()
+        self.debug_poison = debug_poison
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def from_dir(model_dir: str, dtype="bfloat16", device="cuda:0", **options) -> "Engine":
+        """Load a model folder (config.json + safetensors); the model class is chosen by config.json."""
+        arch, cfg, _raw = load_architecture(model_dir)
+        model = Model(arch.build_spec(cfg), parse_dtype(dtype), device)
+        load_from_dir(model, model_dir, arch.normalize_tensor_name)
+        return Engine(model, **options)
+
+    @staticmethod
+    def from_config(config: dict, seed: int = 0, std: float = 0.02, dtype="bfloat16", device="cuda:0",
+                    **options) -> "Engine":
+        """Random weights generated on the device from ``seed`` (no files): for large benchmarks."""
+        arch = lookup(config)
+        model = Model(arch.build_spec(arch.parse_config(config, None)), parse_dtype(dtype), device)
+        load_random(model, seed, std)
+        return Engine(model, **options)
+
+    # ------------------------------------------------------------------ requests
+    def open(self, request_id: Hashable) -> None:
+        slot = self.manager.open(request_id)
+        self.cache.reset_slot(slot)
+
+    def finish(self, request_id: Hashable) -> None:
+        """The request is over: its pages and its slot go back."""
+        if self.manager.is_open(request_id):
+            self.manager.close(request_id)
+
+    def length(self, request_id: Hashable) -> int:
+        return self.manager.length(request_id) if self.manager.is_open(request_id) else 0
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch. Returns float32 logits [wanted, vocab] on the device, in the order
+        of the entries and of each entry's ``want`` (None if nothing is wanted)."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries:
+            return None
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+            if bad:
+                raise ValueError(f"request {e.request_id!r}: token ids {bad[:4]} outside 0..{self.vocab_size - 1}")
+            if any(not 0 <= int(w) < len(e.tokens) for w in e.want):
+                raise ValueError(f"request {e.request_id!r}: 'want' {list(e.want)} outside its {len(e.tokens)} tokens")
+        # pages for every entry, or for none
+        opened, reserved = [], []
+        try:
+            for e in entries:
+                if not self.manager.is_open(e.request_id):
+                    self.open(e.request_id)
+                    opened.append(e.request_id)
+                before = [list(t) for t in self.manager.requests[e.request_id].tables]
+                reserved.append((e.request_id, before))
+                self.manager.reserve(e.request_id, len(e.tokens))
+        except Exception:
+            for rid, before in reserved:
+                if rid in opened:
+                    continue
+                rc = self.manager.requests[rid]
+                for g, table in enumerate(rc.tables):
+                    for b in range(len(before[g]), len(table)):
+                        if table[b] >= 0:
+                            self.manager.pools[g].give(table[b], rid)
+                    del table[len(before[g]):]
+            for rid in opened:
+                self.manager.close(rid)
+            raise
+
+        ctx, logit_rows = self._build_context(entries)
+        logits = self.model.forward(ctx, self.cache.views, logit_rows)
+        for e in entries:
+            returned = self.manager.commit(e.request_id, len(e.tokens))
+            if self.debug_poison and returned:
+                self.cache.poison_pages(returned)
+        st = self.stats
+        st.steps += 1
+        st.tokens += ctx.n_tokens
+        for e in entries:
+            if len(e.tokens) == 1:
+                st.decode_tokens += 1
+            else:
+                st.prefill_tokens += len(e.tokens)
+        st.logit_rows += 0 if logit_rows is None else int(logit_rows.numel())
+        return logits
+
+    def _build_context(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, Optional[torch.Tensor]]:
+        """All of a step's integer inputs in one pinned buffer, one host-to-device copy."""
+        mgr = self.manager
+        n_seqs = len(entries)
+        n_tokens = sum(len(e.tokens) for e in entries)
+        starts = [mgr.length(e.request_id) for e in entries]
+        n_new = [len(e.tokens) for e in entries]
+        slots = [mgr.slot(e.request_id) for e in entries]
+        tables = [[mgr.table(g, e.request_id) for e in entries] for g in range(len(mgr.groups))]
+        widths = [max(len(t) for t in tg) for tg in tables]
+        n_want = sum(len(e.want) for e in entries)
+
+        def pad4(n):
+            return (n + 3) // 4 * 4
+
+        sizes = [n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_want] + [n_seqs * w for w in widths]
+        offsets, total = [], 0
+        for s in sizes:
+            offsets.append(total)
+            total += pad4(s)
+        host = _pinned_int32(max(total, 4))
+        buf = host.numpy()
+        o_tok, o_pos, o_seq, o_cu, o_slot, o_want = offsets[:6]
+        cursor, want_cursor = 0, 0
+        buf[o_cu] = 0
+        for s, e in enumerate(entries):
+            n = n_new[s]
+            buf[o_tok + cursor: o_tok + cursor + n] = list(e.tokens)
+            buf[o_pos + cursor: o_pos + cursor + n] = range(starts[s], starts[s] + n)
+            buf[o_seq + cursor: o_seq + cursor + n] = s
+            for w in e.want:
+                buf[o_want + want_cursor] = cursor + int(w)
+                want_cursor += 1
+            cursor += n
+            buf[o_cu + s + 1] = cursor
+            buf[o_slot + s] = slots[s]
+        for g, tg in enumerate(tables):
+            o, w = offsets[6 + g], widths[g]
+            view = buf[o: o + n_seqs * w].reshape(n_seqs, w)
+            view[:] = -1
+            for s, t in enumerate(tg):
+                view[s, : len(t)] = t
+        dev = host.to(self.device, non_blocking=True)
+
+        def seg(off, n):
+            return dev[off: off + n]
+
+        block_tables = {g: seg(offsets[6 + g], n_seqs * widths[g]).view(n_seqs, widths[g])
+                        for g in range(len(tables))}
+        ctx = StepContext(
+            n_tokens=n_tokens, n_seqs=n_seqs, tokens=seg(o_tok, n_tokens), positions=seg(o_pos, n_tokens),
+            seq_of_token=seg(o_seq, n_tokens), cu_seqlens=seg(o_cu, n_seqs + 1), slots=seg(o_slot, n_seqs),
+            start_pos=starts, n_new=n_new, slot_ids=slots, block_tables=block_tables, page_size=self.page_size,
+            max_context=max(s + n for s, n in zip(starts, n_new)))
+        ctx._host_buffer = host       # keep the pinned buffer alive until the copy has run
+        logit_rows = seg(o_want, n_want) if n_want else None
+        return ctx, logit_rows
+
+    # ------------------------------------------------------------------ bookkeeping
+    def snapshot(self) -> dict:
+        s = self.manager.snapshot()
+        s.update(steps=self.stats.steps, tokens=self.stats.tokens, prefill_tokens=self.stats.prefill_tokens,
+                 decode_tokens=self.stats.decode_tokens, cache_bytes=self.cache.bytes)
+        return s

@@ -1,0 +1,285 @@
+"""Python faces of the CUDA kernels in ``hi_b200/csrc``.
+
+Every function takes CUDA tensors, checks shapes and dtypes, and enqueues the kernel on
+torch's current stream. There is no CPU path and no torch fallback: a tensor that is not
+on a CUDA device, or a library that cannot be built, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional, Tuple
+
+import torch
+
+from . import build as _build
+
+P, I, F = c_void_p, c_int, c_float
+
+_SIGNATURES = {
+    "hb_embed_gather": [P, I, P, P, I, I, I, P],
+    "hb_add_rmsnorm": [P, P, I, P, I, P, I, P, I, I, F, P],
+    "hb_swiglu": [P, P, I, I, I, P],
+    "hb_moe_combine": [P, P, P, I, P, I, I, I, P],
+    "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
+    "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
+    "hb_router_topk": [P, P, I, I, I, I, I, P, P, P, P],
+    "hb_moe_plan": [P, I, I, P, P, P, P],
+    "hb_moe_gate_up": [P, I, P, I, P, P, P, I, P, P, I, I, I, I, P],
+    "hb_moe_down": [P, I, P, P, I, P, I, I, I, I, P],
+    "hb_sample_rows": [P, I, I, P, P, P, P],
+}
+
+_ERRORS = {1001: "bad argument (size, pointer or dtype)", 1002: "shape not supported by this kernel"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        handle = _build.library()
+        for name, sig in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = sig
+            fn.restype = c_int
+        _lib = handle
+    return _lib
+
+
+def _check(code: int, name: str) -> None:
+    if code != 0:
+        what = _ERRORS.get(code, f"CUDA error {code}")
+        raise KernelError(f"{name}: {what}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"dtype {t.dtype} is not supported (float32 or bfloat16)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor; this engine has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+# --------------------------------------------------------------------------- elementwise
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """Rows of ``table`` [V, H] for int32 ``tokens`` [N] -> float32 residual stream [N, H]."""
+    _need(table, "table"); _need(tokens, "tokens", torch.int32)
+    n, (vocab, hidden) = tokens.numel(), table.shape
+    out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _check(lib().hb_embed_gather(_ptr(table), _dt(table), _ptr(tokens), _ptr(out), n, hidden, vocab, _stream()),
+           "embed_gather")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                out_dtype: torch.dtype, row_map: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x += delta`` (float32, in place) then ``rmsnorm(x) * weight`` in ``out_dtype``.
+
+    With ``row_map`` (int32 [R]) only those rows are normalised (output [R, H]) and ``x`` is
+    left untouched: the rows whose logits are wanted.
+    """
+    _need(x, "x", torch.float32)
+    rows_total, hidden = x.shape
+    if delta is not None:
+        _need(delta, "delta")
+        if delta.shape != x.shape:
+            raise KernelError(f"delta shape {tuple(delta.shape)} != residual shape {tuple(x.shape)}")
+    if weight is not None:
+        _need(weight, "weight")
+        if weight.numel() != hidden:
+            raise KernelError(f"norm weight has {weight.numel()} elements for hidden size {hidden}")
+    rows = rows_total
+    if row_map is not None:
+        _need(row_map, "row_map", torch.int32)
+        rows = row_map.numel()
+    y = torch.empty((rows, hidden), dtype=out_dtype, device=x.device)
+    _check(lib().hb_add_rmsnorm(_ptr(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(weight),
+                                _dt(weight) if weight is not None else 0, _ptr(y), _dt(y), _ptr(row_map),
+                                rows, hidden, float(eps), _stream()), "add_rmsnorm")
+    return y
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """[N, 2I] (gate columns first) -> silu(gate) * up, [N, I], same dtype, float32 math."""
+    _need(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("swiglu input needs an even number of columns")
+    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().hb_swiglu(_ptr(gate_up), _ptr(out), _dt(gate_up), n, two_i // 2, _stream()), "swiglu")
+    return out
+
+
+def moe_combine(y: torch.Tensor, slot_of_entry: torch.Tensor, shared: Optional[torch.Tensor], n: int,
+                top_k: int) -> torch.Tensor:
+    """out[t] = shared[t] + sum_j y[slot_of_entry[t*k + j]]  -> float32 [n, H]."""
+    _need(y, "y", torch.float32); _need(slot_of_entry, "slot_of_entry", torch.int32)
+    hidden = y.shape[1]
+    if shared is not None:
+        _need(shared, "shared")
+        if tuple(shared.shape) != (n, hidden):
+            raise KernelError("shared expert output has the wrong shape")
+    out = torch.empty((n, hidden), dtype=torch.float32, device=y.device)
+    _check(lib().hb_moe_combine(_ptr(y), _ptr(slot_of_entry), _ptr(shared), _dt(shared) if shared is not None else 0,
+                                _ptr(out), n, hidden, top_k, _stream()), "moe_combine")
+    return out
+
+
+# --------------------------------------------------------------------------- attention
+def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Tensor,
+             inv_freq: Optional[torch.Tensor], interleaved: bool, qk_norm: bool, qk_eps: float,
+             temperature: Optional[Tuple[float, float]], seq_of_token: Optional[torch.Tensor],
+             block_table: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
+             v_pages: Optional[torch.Tensor], page_size: int, write_kv: bool) -> torch.Tensor:
+    """Rotary or temperature, optional L2 norm, and the cache append; returns q [N, nh, hd].
+
+    ``qkv`` is [N, (nh + 2*nkv) * hd]; ``k_pages``/``v_pages`` are [pages, nkv, page_size, hd];
+    ``block_table`` [S, width] int32 maps (sequence row, position // page_size) to a page.
+    """
+    _need(qkv, "qkv"); _need(positions, "positions", torch.int32)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * hd:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(nh + 2 * nkv) * hd}")
+    if hd % 16 != 0 or hd > 256:
+        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256)")
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != hd // 2:
+            raise KernelError("inv_freq must have head_dim/2 entries (all of head_dim rotates)")
+    stride = 0
+    if write_kv:
+        for t, nm in ((seq_of_token, "seq_of_token"), (block_table, "block_table")):
+            _need(t, nm, torch.int32)
+        _need(k_pages, "k_pages", qkv.dtype); _need(v_pages, "v_pages", qkv.dtype)
+        if tuple(k_pages.shape[1:]) != (nkv, page_size, hd) or k_pages.shape != v_pages.shape:
+            raise KernelError(f"cache pages have shape {tuple(k_pages.shape)}, expected [*, {nkv}, {page_size}, {hd}]")
+        stride = block_table.shape[1]
+    q = torch.empty((n, nh, hd), dtype=qkv.dtype, device=qkv.device)
+    fs, asc = temperature if temperature is not None else (1.0, 0.0)
+    _check(lib().hb_qkv_post(_ptr(qkv), _dt(qkv), _ptr(inv_freq), hd // 2, int(interleaved), int(qk_norm),
+                             float(qk_eps), int(temperature is not None), float(fs), float(asc), _ptr(positions),
+                             _ptr(seq_of_token), _ptr(block_table), stride, _ptr(q), _ptr(k_pages), _ptr(v_pages),
+                             page_size, int(write_kv), n, nh, nkv, hd, _stream()), "qkv_post")
+    return q
+
+
+def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                    seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int,
+                    scale: float) -> torch.Tensor:
+    """softmax(q k^T * scale) v over the keys each token may read; q [N, nh, hd] -> [N, nh, hd]."""
+    _need(q, "q"); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
+    for t, nm in ((block_table, "block_table"), (seq_of_token, "seq_of_token"), (positions, "positions")):
+        _need(t, nm, torch.int32)
+    n, nh, hd = q.shape
+    _, nkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd or k_pages.shape != v_pages.shape:
+        raise KernelError("cache pages do not match the query's head_dim")
+    if nh % nkv:
+        raise KernelError(f"{nh} query heads are not a multiple of {nkv} kv heads")
+    if hd % 16 != 0 or hd > 256:
+        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256)")
+    out = torch.empty_like(q)
+    _check(lib().hb_paged_attention(_ptr(q), _dt(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                    block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv,
+                                    hd, page_size, int(chunk), int(window), float(scale), _stream()),
+           "paged_attention")
+    return out
+
+
+# --------------------------------------------------------------------------- experts
+def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool = False):
+    """Router logits (float32), the top-k expert ids (ties to the lower id) and sigmoid scores."""
+    _need(x, "x"); _need(w, "router weight", x.dtype)
+    n, hidden = x.shape
+    experts = w.shape[0]
+    if w.shape[1] != hidden:
+        raise KernelError("router weight does not match the hidden size")
+    ids = torch.empty((n, top_k), dtype=torch.int32, device=x.device)
+    scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
+    logits = torch.empty((n, experts), dtype=torch.float32, device=x.device) if want_logits else None
+    _check(lib().hb_router_topk(_ptr(x), _ptr(w), _dt(x), n, hidden, experts, top_k, _ptr(logits), _ptr(ids),
+                                _ptr(scores), _stream()), "router_topk")
+    return ids, scores, logits
+
+
+def moe_plan(ids: torch.Tensor, experts: int):
+    """Group the routing entries by expert: (offsets [E+1], sorted_entry [n], slot_of_entry [n])."""
+    _need(ids, "ids", torch.int32)
+    n = ids.numel()
+    dev = ids.device
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+    sorted_entry = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    slot_of_entry = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    _check(lib().hb_moe_plan(_ptr(ids), n, experts, _ptr(offsets), _ptr(sorted_entry), _ptr(slot_of_entry),
+                             _stream()), "moe_plan")
+    return offsets, sorted_entry, slot_of_entry
+
+
+def moe_gate_up(x: torch.Tensor, sorted_entry: torch.Tensor, top_k: int, w_gate: torch.Tensor,
+                w_up: torch.Tensor, offsets: torch.Tensor, scores: torch.Tensor, few_rows: bool) -> torch.Tensor:
+    """act[slot] = silu(s * x Wg[e]^T) * (s * x Wu[e]^T), [N*k, I] in the engine dtype."""
+    _need(x, "x"); _need(w_gate, "w_gate", x.dtype); _need(w_up, "w_up", x.dtype)
+    _need(scores, "scores", torch.float32)
+    n, hidden = x.shape
+    experts, inter, h2 = w_gate.shape
+    if h2 != hidden or w_up.shape != w_gate.shape:
+        raise KernelError("expert gate/up weights do not match the hidden size")
+    n_entries = n * top_k
+    act = torch.empty((n_entries, inter), dtype=x.dtype, device=x.device)
+    _check(lib().hb_moe_gate_up(_ptr(x), _dt(x), _ptr(sorted_entry), top_k, _ptr(w_gate), _ptr(w_up), _ptr(offsets),
+                                experts, _ptr(scores), _ptr(act), n_entries, inter, hidden, int(few_rows), _stream()),
+           "moe_gate_up")
+    return act
+
+
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, few_rows: bool) -> torch.Tensor:
+    """y[slot] = act[slot] Wd[e]^T, float32 [N*k, H]."""
+    _need(act, "act"); _need(w_down, "w_down", act.dtype)
+    n_entries, inter = act.shape
+    experts, hidden, i2 = w_down.shape
+    if i2 != inter:
+        raise KernelError("expert down weights do not match the intermediate size")
+    y = torch.empty((n_entries, hidden), dtype=torch.float32, device=act.device)
+    _check(lib().hb_moe_down(_ptr(act), _dt(act), _ptr(w_down), _ptr(offsets), experts, _ptr(y), n_entries, hidden,
+                             inter, int(few_rows), _stream()), "moe_down")
+    return y
+
+
+# --------------------------------------------------------------------------- sampling
+def sample_rows(logits: torch.Tensor, temperatures: Optional[torch.Tensor],
+                uniforms: Optional[torch.Tensor]) -> torch.Tensor:
+    """One token per row of float32 logits: argmax where temperature <= 0, else inverse CDF."""
+    _need(logits, "logits", torch.float32)
+    rows, vocab = logits.shape
+    for t, nm in ((temperatures, "temperatures"), (uniforms, "uniforms")):
+        if t is not None:
+            _need(t, nm, torch.float32)
+            if t.numel() != rows:
+                raise KernelError(f"{nm} needs one entry per row")
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(lib().hb_sample_rows(_ptr(logits), rows, vocab, _ptr(temperatures), _ptr(uniforms), _ptr(out), _stream()),
+           "sample_rows")
+    return out

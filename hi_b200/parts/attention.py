@@ -1,0 +1,85 @@
+"""The attention mixer: grouped-query attention over a paged cache, global or windowed."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from .basic import Part
+from .linear import linear
+from .registry import build, register
+from .spec import CacheSpec, PartSpec, TensorSpec
+
+
+@register("mixer", "attention")
+class AttentionMixer(Part):
+    """q/k/v projections, position encoding or temperature, optional weightless q/k norm, cache
+    append, softmax(q k^T scale + mask) v, output projection
+    (Llama4Attention::forward, crates/hi-mlx/src/models.rs:5978-6052).
+
+    params:
+      ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``
+      ``window``       None (every earlier key) | ("chunk", C) | ("sliding", W)
+      ``position``     PartSpec of the position family
+      ``qk_norm``, ``qk_norm_eps``   weightless L2 norm of q and k after the rotation
+      ``temperature``  None | (floor_scale, attn_scale): q *= 1 + attn_scale*ln(1 + floor((pos+1)/floor_scale))
+      ``scale``        softmax scale; default head_dim ** -0.5 (models.rs:5963)
+    tensors: ``<prefix>.{q,k,v,o}_proj.weight``.
+    """
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.hd = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        if self.nh % self.nkv:
+            raise ValueError(f"{prefix}: {self.nh} heads are not a multiple of {self.nkv} kv heads")
+        if self.hd % 16 or self.hd > 256:
+            raise ValueError(f"{prefix}: head_dim {self.hd} is not supported (multiples of 16 up to 256)")
+        self.window = tuple(p["window"]) if p.get("window") else None
+        self.position = build("position", p.get("position") or PartSpec("none"), env, prefix)
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
+        self.temperature = tuple(p["temperature"]) if p.get("temperature") else None
+        self.scale = float(p.get("scale") or self.hd ** -0.5)
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    def cache_spec(self):
+        return CacheSpec(kv_heads=self.nkv, head_dim=self.hd, window=self.window)
+
+    def tensor_specs(self):
+        h, nh, nkv, hd = self.hidden, self.nh, self.nkv, self.hd
+        return [TensorSpec(f"{self.prefix}.q_proj.weight", (nh * hd, h)),
+                TensorSpec(f"{self.prefix}.k_proj.weight", (nkv * hd, h)),
+                TensorSpec(f"{self.prefix}.v_proj.weight", (nkv * hd, h)),
+                TensorSpec(f"{self.prefix}.o_proj.weight", (h, nh * hd))]
+
+    def load(self, fetch):
+        q, k, v = (fetch(f"{self.prefix}.{n}_proj.weight") for n in "qkv")
+        if not (q.dtype == k.dtype == v.dtype):
+            q, k, v = q.float(), k.float(), v.float()
+        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()     # one product for q, k and v
+        self.w_o = fetch(f"{self.prefix}.o_proj.weight").contiguous()
+
+    def forward(self, normed, ctx, cache):
+        qkv = linear(normed, self.w_qkv)
+        positions = ctx.positions
+        table = self.position.rotary_table()
+        if table is None and hasattr(self.position, "apply"):
+            # a position part without a rotary table encodes q and k itself
+            n = qkv.shape[0]
+            q, k, v = qkv.split([self.nh * self.hd, self.nkv * self.hd, self.nkv * self.hd], dim=1)
+            q, k = self.position.apply(q.reshape(n, self.nh, self.hd), k.reshape(n, self.nkv, self.hd), positions)
+            qkv = torch.cat([q.reshape(n, -1), k.reshape(n, -1), v], dim=1).to(normed.dtype).contiguous()
+        inv_freq, interleaved = table if table is not None else (None, False)
+        block_table = ctx.block_tables[cache.group]
+        q = ops.qkv_post(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
+                         self.qk_norm_eps, self.temperature, ctx.seq_of_token, block_table, cache.k_pages,
+                         cache.v_pages, ctx.page_size, cache.writes)
+        chunk = self.window[1] if self.window and self.window[0] == "chunk" else 0
+        sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
+        o = ops.paged_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
+                                chunk, sliding, self.scale)
+        return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o)

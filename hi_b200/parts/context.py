@@ -1,0 +1,46 @@
+"""What the step function hands to the parts: the batch of one step, and a mixer's cache."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+
+@dataclass
+class StepContext:
+    """One step: N new tokens of S requests, flat. All tensors live on the device.
+
+    Request ``s`` contributes ``n_new[s]`` consecutive tokens at positions
+    ``start_pos[s] ..``; rows ``cu_seqlens[s] .. cu_seqlens[s+1]`` of every [N, ...] tensor
+    are its tokens. ``slots[s]`` is the request's fixed-size state slot.
+    """
+
+    n_tokens: int
+    n_seqs: int
+    tokens: torch.Tensor          # int32 [N]
+    positions: torch.Tensor       # int32 [N]  absolute position of each token
+    seq_of_token: torch.Tensor    # int32 [N]  row of the block tables / index into slots
+    cu_seqlens: torch.Tensor      # int32 [S+1]
+    slots: torch.Tensor           # int32 [S]
+    start_pos: List[int]          # host copies
+    n_new: List[int]
+    slot_ids: List[int]
+    block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)   # group -> int32 [S, width]
+    page_size: int = 0
+    max_context: int = 0          # longest start_pos + n_new in the step
+
+    @property
+    def max_new(self) -> int:
+        return max(self.n_new) if self.n_new else 0
+
+
+@dataclass
+class CacheView:
+    """The cache slot of one schedule entry, as its mixer sees it."""
+
+    group: Optional[int] = None                  # page group (None: no paged cache)
+    k_pages: Optional[torch.Tensor] = None       # [pages, kv_heads, page_size, head_dim]
+    v_pages: Optional[torch.Tensor] = None
+    state: Optional[torch.Tensor] = None         # [max_slots, *state_shape]
+    writes: bool = True                          # False: read another entry's cache, do not append

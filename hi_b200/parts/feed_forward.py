@@ -1,0 +1,116 @@
+"""Feed-forward parts: dense SwiGLU, and sigmoid-routed top-k experts with a shared expert."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from .basic import Part
+from .linear import linear
+from .registry import register
+from .spec import TensorSpec
+
+
+class _SwiGLU:
+    """(silu(x Wg^T) * x Wu^T) Wd^T with gate and up fused into one product
+    (Mlp::forward, crates/hi-mlx/src/models.rs:2307-2312)."""
+
+    def __init__(self, prefix: str, hidden: int, inter: int):
+        self.prefix, self.hidden, self.inter = prefix, hidden, inter
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}.gate_proj.weight", (self.inter, self.hidden)),
+                TensorSpec(f"{self.prefix}.up_proj.weight", (self.inter, self.hidden)),
+                TensorSpec(f"{self.prefix}.down_proj.weight", (self.hidden, self.inter))]
+
+    def load(self, fetch):
+        g, u = fetch(f"{self.prefix}.gate_proj.weight"), fetch(f"{self.prefix}.up_proj.weight")
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        self.w_down = fetch(f"{self.prefix}.down_proj.weight").contiguous()
+
+    def forward(self, x):
+        return linear(ops.swiglu(linear(x, self.w_gate_up)), self.w_down)
+
+
+@register("feed_forward", "dense_swiglu")
+class DenseSwiGLU(Part):
+    """params: ``hidden_size``, ``intermediate_size``; tensors ``<prefix>.{gate,up,down}_proj.weight``."""
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.mlp = _SwiGLU(prefix, int(params["hidden_size"]), int(params["intermediate_size"]))
+
+    def tensor_specs(self):
+        return self.mlp.tensor_specs()
+
+    def load(self, fetch):
+        self.mlp.load(fetch)
+
+    def forward(self, normed, ctx):
+        return self.mlp.forward(normed)
+
+
+@register("feed_forward", "moe_sigmoid")
+class SigmoidRoutedExperts(Part):
+    """Router logits in float32, the k largest (ties to the lower id), score = sigmoid(logit)
+    without renormalisation; the score scales the expert input; an always-on shared expert
+    sees the unscaled input; outputs are summed (Llama4Moe::forward,
+    crates/hi-mlx/src/models.rs:6055-6103; the reference is top-1 only).
+
+    params: ``hidden_size``, ``num_experts``, ``top_k``, ``intermediate_size``, ``shared_expert``.
+    tensors: ``<prefix>.router.weight`` [E, H]; ``<prefix>.experts.{gate,up}_proj.weight`` [E, I, H];
+    ``<prefix>.experts.down_proj.weight`` [E, H, I]; ``<prefix>.shared_expert.{gate,up,down}_proj.weight``.
+    """
+
+    FEW_ROWS = 128   # up to this many routed rows the weight-streaming kernel is used
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.hidden, self.experts = int(params["hidden_size"]), int(params["num_experts"])
+        self.top_k, self.inter = int(params["top_k"]), int(params["intermediate_size"])
+        if not 1 <= self.top_k <= self.experts:
+            raise ValueError(f"{prefix}: top_k {self.top_k} outside 1..{self.experts}")
+        self.shared = _SwiGLU(f"{prefix}.shared_expert", self.hidden, self.inter) \
+            if params.get("shared_expert", True) else None
+        self.w_router = self.w_gate = self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        e, i, h, p = self.experts, self.inter, self.hidden, self.prefix
+        specs = [TensorSpec(f"{p}.router.weight", (e, h)),
+                 TensorSpec(f"{p}.experts.gate_proj.weight", (e, i, h)),
+                 TensorSpec(f"{p}.experts.up_proj.weight", (e, i, h)),
+                 TensorSpec(f"{p}.experts.down_proj.weight", (e, h, i))]
+        return specs + (self.shared.tensor_specs() if self.shared else [])
+
+    def load(self, fetch):
+        p = self.prefix
+
+        def expert_tensor(name):
+            t = fetch(name)
+            if t.dtype != self.env.dtype:
+                raise ValueError(
+                    f"tensor '{name}' is stored in {t.dtype} and stays so; the expert kernels of the "
+                    f"{self.env.dtype} path cannot take it (run with --dtype float32)")
+            return t.contiguous()
+
+        self.w_router = expert_tensor(f"{p}.router.weight")
+        self.w_gate = expert_tensor(f"{p}.experts.gate_proj.weight")
+        self.w_up = expert_tensor(f"{p}.experts.up_proj.weight")
+        self.w_down = expert_tensor(f"{p}.experts.down_proj.weight")
+        if self.shared:
+            self.shared.load(fetch)
+
+    def forward(self, normed, ctx):
+        n = normed.shape[0]
+        ids, scores, _ = ops.router_topk(normed, self.w_router, self.top_k)
+        offsets, sorted_entry, slot_of_entry = ops.moe_plan(ids, self.experts)
+        few = n * self.top_k <= self.FEW_ROWS
+        act = ops.moe_gate_up(normed, sorted_entry, self.top_k, self.w_gate, self.w_up, offsets, scores, few)
+        y = ops.moe_down(act, self.w_down, offsets, few)
+        shared = self.shared.forward(normed) if self.shared else None
+        return ops.moe_combine(y, slot_of_entry, shared, n, self.top_k)
