@@ -1,0 +1,152 @@
+"""Command line, in the manner of the reference's ``hi-local`` (crates/hi-local/src/main.rs:20-84):
+
+    python -m hi_b200 inspect MODEL_PATH
+    python -m hi_b200 run MODEL_PATH --tokens "1,2,3" [--max-tokens N] [--top-k 5] [--temperature T]
+                          [--top-p P] [--seed S] [--include-logits] [--dtype bfloat16|float32]
+                          [--max-batch-size 8] [--max-batched-tokens 8192] [--kv-page-size 64]
+    python -m hi_b200 random-weights CONFIG_JSON OUT_DIR [--seed S] [--std 0.02]
+
+``run`` is the counterpart of ``hi-local qwen-cpu``: token ids in, pretty JSON out with the same
+fields (crates/hi-cuda/src/qwen_cpu.rs:62-81); ``--top-k`` is the number of top logits shown,
+as there. There is no ``serve``: servers are outside this engine.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from typing import List
+
+
+def parse_token_ids(value: str) -> List[int]:
+    """Comma- or whitespace-separated ids (crates/hi-local/src/main.rs:466-475)."""
+    out = []
+    for part in value.replace(",", " ").split():
+        if not part.isdigit():
+            raise ValueError(f"invalid token id {part!r}")
+        out.append(int(part))
+    return out
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="hi_b200", description="Llama 4 text-decoder inference on one B200")
+    sub = p.add_subparsers(dest="command", required=True)
+    i = sub.add_parser("inspect", help="inspect a model folder")
+    i.add_argument("model_path")
+    r = sub.add_parser("run", help="run token ids through the model and generate")
+    r.add_argument("model_path")
+    r.add_argument("--tokens")
+    r.add_argument("--tokens-file")
+    r.add_argument("--max-tokens", type=int, default=0)
+    r.add_argument("--top-k", type=int, default=5)
+    r.add_argument("--temperature", type=float, default=0.0)
+    r.add_argument("--top-p", type=float, default=1.0)
+    r.add_argument("--seed", type=int, default=None)
+    r.add_argument("--include-logits", action="store_true")
+    r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.add_argument("--max-batch-size", type=int, default=8)
+    r.add_argument("--max-active-requests", type=int, default=None)
+    r.add_argument("--max-batched-tokens", type=int, default=8192)
+    r.add_argument("--kv-page-size", type=int, default=64)
+    w = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
+    w.add_argument("config_json")
+    w.add_argument("out_dir")
+    w.add_argument("--seed", type=int, default=0)
+    w.add_argument("--std", type=float, default=0.02)
+    return p
+
+
+def cmd_inspect(args) -> int:
+    import torch
+
+    from .config.registry import load_architecture
+    from .parts.model import Model
+    from .weights.loader import WeightError, check_names
+    from .weights.safetensors_io import Checkpoint
+
+    arch, cfg, raw = load_architecture(args.model_path)
+    spec = arch.build_spec(cfg)
+    model = Model(spec, torch.bfloat16, "cpu")
+    specs = model.tensor_specs()
+    params = sum(int(torch.Size(s.shape).numel()) for s in specs if s.init != "absent")
+    report = {
+        "architecture": arch.name, "architectures": list(getattr(cfg, "architectures", ())),
+        "layers": [{"layer": i, "mixer": l.mixer.kind, "window": l.mixer.params.get("window"),
+                    "position": (l.mixer.params.get("position") or {}).kind if l.mixer.params.get("position") else None,
+                    "feed_forward": l.feed_forward.kind} for i, l in enumerate(spec.layers)],
+        "schedule": [e.layer for e in spec.schedule],
+        "parameters": params, "weight_bytes_bf16": 2 * params,
+        "kv_bytes_per_token_bf16": sum(2 * 2 * cs.kv_heads * cs.head_dim for cs in model.cache_specs.values() if cs),
+        "config": {k: v for k, v in vars(cfg).items() if k != "raw"},
+    }
+    try:
+        ckpt = Checkpoint(args.model_path)
+        names = {}
+        for n in ckpt.names():
+            m = arch.normalize_tensor_name(n)
+            if m is not None:
+                names[m] = ckpt.describe(n)[1]
+        check_names(specs, names, args.model_path)
+        report["tensors"] = {"count": len(names), "status": "ok"}
+    except (WeightError, ValueError) as e:
+        report["tensors"] = {"status": "error", "message": str(e)}
+    print(json.dumps(report, indent=2, default=str))
+    return 0 if report["tensors"]["status"] == "ok" else 1
+
+
+def cmd_run(args) -> int:
+    if bool(args.tokens) == bool(args.tokens_file):
+        raise SystemExit("provide either --tokens or --tokens-file")
+    text = args.tokens if args.tokens else open(args.tokens_file).read()
+    tokens = parse_token_ids(text)
+    if not tokens:
+        raise SystemExit("--tokens must include at least one token id")
+    import torch
+
+    from .engine.core import StepEntry
+    from .engine.generate import LLM
+    from .sampling.sampler import SamplingParams
+
+    llm = LLM(args.model_path, dtype=args.dtype, max_batch_size=args.max_batch_size,
+              max_active_requests=args.max_active_requests, max_batched_tokens=args.max_batched_tokens,
+              kv_page_size=args.kv_page_size,
+              kv_cache_tokens=max(args.max_batched_tokens, len(tokens) + args.max_tokens + args.kv_page_size))
+    logits = llm.engine.step([StepEntry("inspect", tokens, [len(tokens) - 1])])[0]
+    llm.engine.finish("inspect")
+    top = torch.topk(logits, min(args.top_k, logits.numel())) if args.top_k > 0 else None
+    host = logits.cpu()
+    order = sorted(range(host.numel()), key=lambda i: (-float(host[i]), i))[:max(args.top_k, 0)]
+    generated: List[int] = []
+    if args.max_tokens > 0:
+        out = llm.generate([tokens], SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature,
+                                                    top_p=args.top_p, seed=args.seed))[0]
+        generated = out.token_ids
+    result = {
+        "backend": f"hi_b200-cuda-{args.dtype}", "input_tokens": tokens, "next_token": order[0] if order else int(host.argmax()),
+        "next_text": "", "generated_tokens": generated, "generated_text": "",
+        "top_logits": [{"token_id": i, "token": None, "logit": float(host[i])} for i in order],
+        "logit_count": host.numel(),
+    }
+    if args.include_logits:
+        result["logits"] = [float(v) for v in host]
+    print(json.dumps(result, indent=2))
+    return 0
+
+
+def cmd_random_weights(args) -> int:
+    from .weights.loader import write_random_model
+
+    with open(args.config_json) as f:
+        config = json.load(f)
+    write_random_model(config, args.out_dir, args.seed, args.std)
+    print(json.dumps({"model_path": args.out_dir, "seed": args.seed, "std": args.std}))
+    return 0
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    return {"inspect": cmd_inspect, "run": cmd_run, "random-weights": cmd_random_weights}[args.command](args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

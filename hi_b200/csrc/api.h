@@ -11,7 +11,8 @@ extern "C" {
 int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int n, int hidden,
                     int vocab, cudaStream_t stream);
 int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w, int w_dtype, void* y,
-                   int y_dtype, const int* row_map, int rows, int hidden, float eps, cudaStream_t stream);
+                   int y_dtype, float* y_f32, const int* row_map, int rows, int hidden, float eps,
+                   cudaStream_t stream);
 int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream);
 int hb_moe_combine(const float* y, const int* slot_of_entry, const void* shared, int shared_dtype, float* out,
                    int n, int hidden, int top_k, cudaStream_t stream);
@@ -27,8 +28,8 @@ int hb_paged_attention(const void* q, int dtype, const void* k_pages, const void
                        void* out, int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
                        float scale, cudaStream_t stream);
 
-int hb_router_topk(const void* x, const void* w, int dtype, int n, int hidden, int experts, int top_k,
-                   float* logits_out, int* ids, float* scores, cudaStream_t stream);
+int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
+                   int top_k, float* logits_out, int* ids, float* scores, cudaStream_t stream);
 int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
                 int* slot_of_entry, cudaStream_t stream);
 int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,

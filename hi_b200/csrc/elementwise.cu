@@ -28,7 +28,7 @@ __global__ void embed_gather_kernel(const void* table, int table_dtype, const in
 //   s = x[src] (+ delta[src]);  if no row_map: x[src] = s  (the residual sum, float32)
 //   y[r] = s * rsqrt(mean(s^2) + eps) * w     (crates/hi-cuda/src/kernels.cu:61-77)
 __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype, const void* w,
-                                   int w_dtype, void* y, int y_dtype, const int* row_map,
+                                   int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
                                    int hidden, float eps) {
   __shared__ float scratch[33];
   extern __shared__ float row[];  // hidden floats
@@ -48,6 +48,7 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
     if (!row_map && delta) x[src * hidden + j] = s;
     const float wv = w ? load_any(w, w_dtype, j) : 1.f;
     store_any(y, y_dtype, (size_t)r * hidden + j, s * inv * wv);
+    if (y_f32) y_f32[(size_t)r * hidden + j] = s * inv * wv;
   }
 }
 
@@ -92,7 +93,7 @@ extern "C" int hb_embed_gather(const void* table, int table_dtype, const int* to
 }
 
 extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w,
-                              int w_dtype, void* y, int y_dtype, const int* row_map, int rows,
+                              int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map, int rows,
                               int hidden, float eps, cudaStream_t stream) {
   if (!x || !y || rows < 0 || hidden <= 0 || !dtype_ok(y_dtype) || (delta && !dtype_ok(delta_dtype)) ||
       (w && !dtype_ok(w_dtype)))
@@ -106,7 +107,7 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
   }
   const int threads = hidden >= 2048 ? 512 : 256;
   add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, w, w_dtype, y, y_dtype,
-                                                      row_map, hidden, eps);
+                                                      y_f32, row_map, hidden, eps);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

@@ -13,16 +13,18 @@ namespace {
 
 // ------------------------------------------------------------------ router
 // One block per token; warps take experts in turn; lanes stride over the hidden dim.
-template <typename T>
-__global__ void router_topk_kernel(const T* __restrict__ x, const T* __restrict__ w, int hidden, int experts,
+// x may be float32 while the weights are bfloat16: the router reads the float32 output of the
+// norm, so its logits carry no activation rounding of their own.
+template <typename TX, typename TW>
+__global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int hidden, int experts,
                                    int top_k, float* __restrict__ logits_out, int* __restrict__ ids,
                                    float* __restrict__ scores) {
   extern __shared__ float lg[];  // [experts]
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const T* xr = x + (size_t)t * hidden;
+  const TX* xr = x + (size_t)t * hidden;
   for (int e = warp; e < experts; e += nwarps) {
-    const T* wr = w + (size_t)e * hidden;
+    const TW* wr = w + (size_t)e * hidden;
     float s = 0.f;
     for (int j = lane; j < hidden; j += 32) s += hb::to_f32(xr[j]) * hb::to_f32(wr[j]);
     s = hb::warp_sum(s);
@@ -296,18 +298,22 @@ int launch_grouped(bool dual, const void* A, int lda, const int* sorted_entry, i
 
 }  // namespace
 
-extern "C" int hb_router_topk(const void* x, const void* w, int dtype, int n, int hidden, int experts, int top_k,
-                              float* logits_out, int* ids, float* scores, cudaStream_t stream) {
+extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden,
+                              int experts, int top_k, float* logits_out, int* ids, float* scores,
+                              cudaStream_t stream) {
   if (!x || !w || !ids || !scores || n < 0 || hidden <= 0 || experts <= 0 || top_k <= 0 || top_k > experts)
     return HB_ERR_BAD_ARG;
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
   if (n == 0) return HB_OK;
   const size_t smem = (size_t)experts * sizeof(float);
-  if (dtype == HB_DTYPE_F32)
-    router_topk_kernel<float><<<n, 128, smem, stream>>>((const float*)x, (const float*)w, hidden, experts, top_k,
-                                                        logits_out, ids, scores);
-  else if (dtype == HB_DTYPE_BF16)
-    router_topk_kernel<__nv_bfloat16><<<n, 128, smem, stream>>>(
+  if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_F32)
+    router_topk_kernel<float, float><<<n, 128, smem, stream>>>((const float*)x, (const float*)w, hidden, experts,
+                                                               top_k, logits_out, ids, scores);
+  else if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_BF16)
+    router_topk_kernel<float, __nv_bfloat16><<<n, 128, smem, stream>>>(
+        (const float*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
+  else if (x_dtype == HB_DTYPE_BF16 && w_dtype == HB_DTYPE_BF16)
+    router_topk_kernel<__nv_bfloat16, __nv_bfloat16><<<n, 128, smem, stream>>>(
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
   else
     return HB_ERR_BAD_ARG;

@@ -124,9 +124,11 @@ class Engine:
         return self.manager.length(request_id) if self.manager.is_open(request_id) else 0
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], tap=None) -> Optional[torch.Tensor]:
         """Run one batch. Returns float32 logits [wanted, vocab] on the device, in the order
-        of the entries and of each entry's ``want`` (None if nothing is wanted)."""
+        of the entries and of each entry's ``want`` (None if nothing is wanted). ``tap(name,
+        tensor)``, if given, is called by parts that report intermediate tensors (router ids),
+        in the step's flat token order (crates/hi-cuda/src/lib.rs:87-201 has such a dump hook)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             return None
@@ -167,6 +169,7 @@ class Engine:
             raise
 
         ctx, logit_rows = self._build_context(entries)
+        ctx.tap = tap
         logits = self.model.forward(ctx, self.cache.views, logit_rows)
         for e in entries:
             returned = self.manager.commit(e.request_id, len(e.tokens))

@@ -1,0 +1,82 @@
+"""Trace replay: feed given token ids through the model step by step and write logits.
+
+It samples nothing and has no forward pass, cache or loader of its own: it builds the same
+:class:`~hi_b200.engine.core.Engine` that generation uses and calls its ``step``. (The
+reference's closest tools: ``hi-local qwen-cpu --tokens … --include-logits``,
+crates/hi-local/src/main.rs:60-83, and the captured-batch replay of
+crates/hi-mlx/src/models.rs:11709-11831.)
+
+    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+
+Standard input: one JSON object per line,
+    {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
+For a step that wants logits, ``OUT/<step>.f32`` holds them as little-endian float32
+[wanted, vocab] in the order of the entries and of ``want``. After every step a line
+``done <step>`` is printed and flushed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+PAGE_SIZE = 64
+MAX_LIVE_REQUESTS = 8
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="trace_run", description="Replay a token trace and write logits.")
+    p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    p.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    p.add_argument("--out", required=True, help="folder for <step>.f32 files")
+    p.add_argument("--max-tokens", type=int, required=True,
+                   help="most tokens live requests hold at any time (each rounded up to the page size)")
+    p.add_argument("--device", default="cuda:0")
+    p.add_argument("--dump-taps", action="store_true",
+                   help="debug: also write <step>.taps.json with the integer tensors parts report "
+                        "(the router's expert choices, in the step's flat token order)")
+    return p
+
+
+def run(args, stdin=None, stdout=None) -> int:
+    stdin = stdin or sys.stdin
+    stdout = stdout or sys.stdout
+    import numpy as np
+
+    from .core import Engine, StepEntry
+
+    os.makedirs(args.out, exist_ok=True)
+    capacity = max(PAGE_SIZE, -(-args.max_tokens // PAGE_SIZE) * PAGE_SIZE)
+    engine = Engine.from_dir(args.model, dtype=args.dtype, device=args.device, kv_page_size=PAGE_SIZE,
+                             kv_cache_tokens=capacity, max_active_requests=MAX_LIVE_REQUESTS)
+    for line in stdin:
+        line = line.strip()
+        if not line:
+            continue
+        obj = json.loads(line)
+        step = obj["step"]
+        entries = [StepEntry(e["id"], e["tokens"], e.get("want", [])) for e in obj.get("entries", [])]
+        taps = {}
+        tap = (lambda name, t: taps.__setitem__(name, t.detach().to("cpu").tolist())) if args.dump_taps else None
+        logits = engine.step(entries, tap=tap) if entries else None
+        if args.dump_taps:
+            with open(os.path.join(args.out, f"{step}.taps.json"), "w") as f:
+                json.dump(taps, f)
+        if logits is not None:
+            arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+            tmp = os.path.join(args.out, f"{step}.f32.tmp")
+            arr.tofile(tmp)
+            os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
+        for rid in obj.get("end", []):
+            engine.finish(rid)
+        print(f"done {step}", file=stdout, flush=True)
+    return 0
+
+
+def main(argv=None) -> int:
+    return run(build_parser().parse_args(argv))
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -18,12 +18,12 @@ P, I, F = c_void_p, c_int, c_float
 
 _SIGNATURES = {
     "hb_embed_gather": [P, I, P, P, I, I, I, P],
-    "hb_add_rmsnorm": [P, P, I, P, I, P, I, P, I, I, F, P],
+    "hb_add_rmsnorm": [P, P, I, P, I, P, I, P, P, I, I, F, P],
     "hb_swiglu": [P, P, I, I, I, P],
     "hb_moe_combine": [P, P, P, I, P, I, I, I, P],
     "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
     "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
-    "hb_router_topk": [P, P, I, I, I, I, I, P, P, P, P],
+    "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P],
     "hb_moe_gate_up": [P, I, P, I, P, P, P, I, P, P, I, I, I, I, P],
     "hb_moe_down": [P, I, P, P, I, P, I, I, I, I, P],
@@ -95,8 +95,11 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
-                out_dtype: torch.dtype, row_map: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out_dtype: torch.dtype, row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
     """``x += delta`` (float32, in place) then ``rmsnorm(x) * weight`` in ``out_dtype``.
+
+    ``also_f32`` returns ``(y, y_float32)``: the same normalised rows unrounded, for a consumer
+    that computes in 32-bit (the router).
 
     With ``row_map`` (int32 [R]) only those rows are normalised (output [R, H]) and ``x`` is
     left untouched: the rows whose logits are wanted.
@@ -116,9 +119,14 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional
         _need(row_map, "row_map", torch.int32)
         rows = row_map.numel()
     y = torch.empty((rows, hidden), dtype=out_dtype, device=x.device)
+    y32 = None
+    if also_f32 and out_dtype != torch.float32:
+        y32 = torch.empty((rows, hidden), dtype=torch.float32, device=x.device)
     _check(lib().hb_add_rmsnorm(_ptr(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(weight),
-                                _dt(weight) if weight is not None else 0, _ptr(y), _dt(y), _ptr(row_map),
+                                _dt(weight) if weight is not None else 0, _ptr(y), _dt(y), _ptr(y32), _ptr(row_map),
                                 rows, hidden, float(eps), _stream()), "add_rmsnorm")
+    if also_f32:
+        return y, (y if y32 is None else y32)
     return y
 
 
@@ -212,7 +220,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
 # --------------------------------------------------------------------------- experts
 def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool = False):
     """Router logits (float32), the top-k expert ids (ties to the lower id) and sigmoid scores."""
-    _need(x, "x"); _need(w, "router weight", x.dtype)
+    _need(x, "x"); _need(w, "router weight")
     n, hidden = x.shape
     experts = w.shape[0]
     if w.shape[1] != hidden:
@@ -220,8 +228,8 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool 
     ids = torch.empty((n, top_k), dtype=torch.int32, device=x.device)
     scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
     logits = torch.empty((n, experts), dtype=torch.float32, device=x.device) if want_logits else None
-    _check(lib().hb_router_topk(_ptr(x), _ptr(w), _dt(x), n, hidden, experts, top_k, _ptr(logits), _ptr(ids),
-                                _ptr(scores), _stream()), "router_topk")
+    _check(lib().hb_router_topk(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, _ptr(logits),
+                                _ptr(ids), _ptr(scores), _stream()), "router_topk")
     return ids, scores, logits
 
 

@@ -48,8 +48,8 @@ class RMSNorm(Part):
         self.weight = fetch(f"{self.prefix}.weight").contiguous()
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
-                row_map: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.env.dtype, row_map)
+                row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
+        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.env.dtype, row_map, also_f32)
 
 
 # --------------------------------------------------------------------------- positions
@@ -163,6 +163,10 @@ class PreNormBlock(Part):
     def forward(self, layer, residual, pending, ctx, cache_view):
         h = layer.norm_mixer.forward(residual, pending)
         pending = layer.mixer.forward(h, ctx, cache_view)
-        h = layer.norm_feed_forward.forward(residual, pending)
-        pending = layer.feed_forward.forward(h, ctx)
+        if getattr(layer.feed_forward, "wants_f32_input", False):
+            h, h32 = layer.norm_feed_forward.forward(residual, pending, also_f32=True)
+            pending = layer.feed_forward.forward(h, ctx, normed_f32=h32)
+        else:
+            h = layer.norm_feed_forward.forward(residual, pending)
+            pending = layer.feed_forward.forward(h, ctx)
         return residual, pending

@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Callable, Dict, List, Optional
 
 import torch
 
@@ -29,6 +29,7 @@ class StepContext:
     block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)   # group -> int32 [S, width]
     page_size: int = 0
     max_context: int = 0          # longest start_pos + n_new in the step
+    tap: Optional[Callable[[str, torch.Tensor], None]] = None   # debug: parts report named tensors
 
     @property
     def max_new(self) -> int:

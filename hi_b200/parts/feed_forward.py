@@ -68,6 +68,7 @@ class SigmoidRoutedExperts(Part):
     """
 
     FEW_ROWS = 128   # up to this many routed rows the weight-streaming kernel is used
+    wants_f32_input = True   # the router reads the norm's float32 output
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -105,9 +106,11 @@ class SigmoidRoutedExperts(Part):
         if self.shared:
             self.shared.load(fetch)
 
-    def forward(self, normed, ctx):
+    def forward(self, normed, ctx, normed_f32=None):
         n = normed.shape[0]
-        ids, scores, _ = ops.router_topk(normed, self.w_router, self.top_k)
+        ids, scores, _ = ops.router_topk(normed if normed_f32 is None else normed_f32, self.w_router, self.top_k)
+        if ctx.tap is not None:
+            ctx.tap(f"{self.prefix}.router_ids", ids)
         offsets, sorted_entry, slot_of_entry = ops.moe_plan(ids, self.experts)
         few = n * self.top_k <= self.FEW_ROWS
         act = ops.moe_gate_up(normed, sorted_entry, self.top_k, self.w_gate, self.w_up, offsets, scores, few)

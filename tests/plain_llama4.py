@@ -193,13 +193,25 @@ def router_top_k(logits: torch.Tensor, k: int):
     return ids, 1.0 / (1.0 + torch.exp(-chosen))
 
 
-def moe_feed_forward(cfg: dict, w, prefix: str, x: torch.Tensor) -> torch.Tensor:
+def moe_feed_forward(cfg: dict, w, prefix: str, x: torch.Tensor, forced_ids=None, record=None) -> torch.Tensor:
     """Llama4Moe::forward (models.rs:6055-6103): the score scales the expert INPUT; the
-    shared expert sees the unscaled input; outputs are summed."""
+    shared expert sees the unscaled input; outputs are summed.
+
+    ``forced_ids`` [T, k] replaces the top-k choice (scores still come from this function's own
+    logits): a reduced-precision engine may pick another expert where two logits are nearly
+    equal, and its logits are then compared given ITS choice. ``record(prefix, ids, margin)``
+    receives this function's own choice and the gap between the k-th and (k+1)-th logit."""
     T, H = x.shape
     k = cfg.get("num_experts_per_tok", 1)
     logits = x @ w[f"{prefix}.router.weight"].to(F32).T
     ids, scores = router_top_k(logits, k)
+    if record is not None:
+        srt = torch.sort(logits, dim=-1, descending=True).values
+        margin = srt[:, k - 1] - srt[:, k] if logits.shape[1] > k else torch.full((T,), float("inf"))
+        record(prefix, ids.clone(), margin)
+    if forced_ids is not None:
+        ids = forced_ids.to(torch.long)
+        scores = 1.0 / (1.0 + torch.exp(-torch.gather(logits, 1, ids)))
     wg, wu, wd = (w[f"{prefix}.experts.{n}_proj.weight"] for n in ("gate", "up", "down"))
     out = torch.zeros(T, H, dtype=F32)
     for t in range(T):
@@ -216,29 +228,32 @@ def dense_feed_forward(w, prefix: str, x: torch.Tensor) -> torch.Tensor:
     return swiglu(x, *(w[f"{prefix}.{n}_proj.weight"] for n in ("gate", "up", "down")))
 
 
-def block(cfg: dict, w, i: int, x: torch.Tensor, inv_freq) -> torch.Tensor:
+def block(cfg: dict, w, i: int, x: torch.Tensor, inv_freq, forced_routing=None, record=None) -> torch.Tensor:
     """h = x + attn(norm(x)); y = h + ffn(norm(h))  (Llama4Block::forward, models.rs:6143-6149)."""
     p = f"model.layers.{i}"
     eps = cfg.get("rms_norm_eps", 1e-6)
     h = x + attention(cfg, w, f"{p}.self_attn", i, rms_norm(x, w[f"{p}.input_layernorm.weight"], eps), inv_freq)
     n = rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps)
     if layer_is_moe(cfg, i):
-        return h + moe_feed_forward(cfg, w, f"{p}.feed_forward", n)
+        forced = forced_routing.get(f"{p}.feed_forward") if forced_routing else None
+        return h + moe_feed_forward(cfg, w, f"{p}.feed_forward", n, forced, record)
     return h + dense_feed_forward(w, f"{p}.feed_forward", n)
 
 
 def forward(raw_cfg: dict, weights: Dict[str, torch.Tensor], token_ids: List[int],
-            schedule: Optional[List[int]] = None) -> torch.Tensor:
+            schedule: Optional[List[int]] = None, forced_routing=None, record=None) -> torch.Tensor:
     """Logits [T, V] at every position of one sequence (Llama4Like::forward,
     models.rs:6204-6217; head by tensor presence, models.rs:6186-6193).
-    ``schedule`` lists the layers in the order they run (default 0..L-1)."""
+    ``schedule`` lists the layers in the order they run (default 0..L-1).
+    ``forced_routing`` {"model.layers.i.feed_forward": ids [T, k]} and ``record``: see
+    :func:`moe_feed_forward`."""
     cfg = text_config(raw_cfg)
     w = weights
     hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
     inv_freq = rope_inverse_frequencies(hd, float(cfg.get("rope_theta", 1e6)), cfg.get("rope_scaling"))
     x = w["model.embed_tokens.weight"].to(F32)[torch.tensor(token_ids, dtype=torch.long)]
     for i in (schedule if schedule is not None else range(cfg["num_hidden_layers"])):
-        x = block(cfg, w, i, x, inv_freq)
+        x = block(cfg, w, i, x, inv_freq, forced_routing, record)
     x = rms_norm(x, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-6))
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return x @ head.to(F32).T

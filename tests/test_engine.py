@@ -1,0 +1,232 @@
+"""The engine in process, with small pages so that every edge is crossed often: the four ways
+of cutting, long decoding, the first tokens, crafted weights that make one far key or one page
+matter, a schedule that runs a layer twice, generation through the entry point, and a toy mixer
+with state of its own registered from here."""
+import numpy as np
+import pytest
+import torch
+
+import harness as h
+import plain_llama4 as plain
+from tiny_configs import TINY_A, TINY_B, TINY_C
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [("float32", h.TOL_F32), ("bfloat16", h.TOL_BF16)]
+
+
+def engine_for(mdir, dtype, page, tokens=256, slots=4, **kw):
+    from hi_b200.engine.core import Engine
+
+    return Engine.from_dir(mdir, dtype=dtype, kv_page_size=page, kv_cache_tokens=tokens, max_active_requests=slots, **kw)
+
+
+def check(cfg, mdir, dtype, tol, steps, reqs, page, tokens, what, **kw):
+    eng = engine_for(mdir, dtype, page, tokens, **kw)
+    got, forced = h.replay_in_process(eng, steps, record_routing=True)
+    h.compare_with_plain(cfg, h.read_weights(mdir), reqs, got, tol, forced=forced if dtype == "bfloat16" else None,
+                         what=what, margin=0.1)
+    assert not eng.manager.requests, "requests left open"
+    for pool in eng.manager.pools:
+        assert pool.free == pool.total, "pages were lost"
+    return eng
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 16), ("C", 8)])
+def test_four_ways_of_cutting(name, page, dtype, tol, model_dirs):
+    cfg, mdir = model_dirs[name]
+    reqs = {f"r{i}": h.random_tokens(cfg, n, seed=7 + i) for i, n in enumerate([23, 35, 49, 64, 97, 70])}
+    for regime, steps, cap in (("whole", h.trace_whole(reqs), 128), ("tail", h.trace_tail_decode(reqs), 128),
+                               ("portions", h.trace_portions(reqs), 128),
+                               ("mixed", h.trace_mixed(reqs, max_tokens=288, page=page, seed=5), 288)):
+        eng = check(cfg, mdir, dtype, tol, steps, reqs, page, cap, f"{name} {dtype} page {page} {regime}",
+                    debug_poison=True)
+        if regime == "mixed":
+            snap = eng.manager.snapshot()
+            assert all(g["allocations"] > g["total"] for g in snap["groups"]), "pages were not used again"
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_long_decoding_and_first_tokens(dtype, tol, model_dirs):
+    """A 5-token prompt fed one token at a time from position 0, then 300 decoded tokens one by one:
+    many chunk edges, many pages freed and used again by the same request."""
+    cfg, mdir = model_dirs["A"]
+    toks = h.random_tokens(cfg, 305, seed=21)
+    steps = [([("x", [t], [0])], []) for t in toks]
+    steps[-1] = (steps[-1][0], ["x"])
+    eng = check(cfg, mdir, dtype, tol, steps, {"x": toks}, 8, 352, f"long decode {dtype}", debug_poison=True)
+    chunked = [g for g in eng.manager.snapshot()["groups"] if g["window"]]
+    assert chunked and chunked[0]["peak"] <= 32 // 8 + 1, "the chunked group kept pages of dead chunks"
+
+
+def peaky_overrides(cfg, mdir, scale=6.0):
+    """q and k projections scaled up: softmax is then far from uniform, so a key that is missing,
+    stale or at the wrong place changes the logits far beyond the tolerance."""
+    w = h.read_weights(mdir)
+    return {n: (t.float() * scale) for n, t in w.items() if n.endswith(("q_proj.weight", "k_proj.weight"))}
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_peaked_attention_under_cutting(name, dtype, tol, model_dirs, tmp_path):
+    cfg, mdir = model_dirs[name]
+    sharp = h.make_model(str(tmp_path / "sharp"), cfg, seed=11, std=0.08, overrides=peaky_overrides(cfg, mdir))
+    reqs = {f"r{i}": h.random_tokens(cfg, n, seed=40 + i) for i, n in enumerate([130, 75, 48])}
+    # the softmax must really be peaked somewhere, else this test shows nothing
+    w = h.read_weights(sharp)
+    for steps, regime in ((h.trace_portions(reqs), "portions"), (h.trace_mixed(reqs, 272, 16, seed=9), "mixed")):
+        check(cfg, sharp, dtype, tol, steps, reqs, 16, 272, f"peaked {name} {dtype} {regime}", debug_poison=True)
+
+
+def test_schedule_runs_a_layer_twice(model_dirs):
+    """The order of layers is data: layer 0 runs twice (two cache slots), then layer 1."""
+    from hi_b200.config.registry import load_architecture
+    from hi_b200.engine.core import Engine, parse_dtype
+    from hi_b200.parts.model import Model
+    from hi_b200.parts.spec import ModelSpec, ScheduleEntry
+    from hi_b200.weights.loader import load_from_dir
+    import dataclasses
+
+    dtype, tol = "float32", h.TOL_F32
+    cfg, mdir = model_dirs["A"]
+    arch, typed, _ = load_architecture(mdir)
+    spec = arch.build_spec(typed)
+    order = [0, 1, 0, 1, 1]
+    spec = dataclasses.replace(spec, schedule=tuple(ScheduleEntry(layer=l, cache=i) for i, l in enumerate(order)))
+    model = Model(spec, parse_dtype(dtype), "cuda:0")
+    load_from_dir(model, mdir, arch.normalize_tensor_name)
+    eng = Engine(model, kv_page_size=8, kv_cache_tokens=128, max_active_requests=2)
+    toks = h.random_tokens(cfg, 90, seed=3)
+    steps = h.trace_portions({"a": toks})
+    got, _ = h.replay_in_process(eng, steps, record_routing=False)
+    ref = plain.forward(cfg, h.read_weights(mdir), toks, schedule=order)
+    out = torch.tensor(np.stack([got["a"][p] for p in range(len(toks))]))
+    err = h.rel_err(out, ref)
+    assert err <= tol, f"repeated layers: rel err {err}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(dtype, model_dirs):
+    """hi_b200.generate: greedy tokens of four prompts, batched by the scheduler, against the plain
+    model fed the same tokens: every generated token must be (within rounding) the plain argmax."""
+    import hi_b200
+
+    cfg, mdir = model_dirs["A"]
+    w = h.read_weights(mdir)
+    prompts = [h.random_tokens(cfg, n, seed=60 + n) for n in (7, 19, 33, 48)]
+    outs = hi_b200.generate(mdir, prompts, hi_b200.SamplingParams(max_tokens=16, ignore_eos=True), dtype=dtype,
+                            kv_page_size=16, max_batched_tokens=40, max_batch_size=4, kv_cache_tokens=512)
+    slack = 1e-4 if dtype == "float32" else 0.08
+    for prompt, out in zip(prompts, outs):
+        assert out.completion_tokens == 16 and out.finish_reason == "length"
+        ref = plain.forward(cfg, w, prompt + out.token_ids)
+        for i, tok in enumerate(out.token_ids):
+            row = ref[len(prompt) - 1 + i]
+            assert float(row.max() - row[tok]) <= slack * float(row.abs().max()), (
+                f"{dtype}: generated token {i} = {tok} is not the plain argmax {int(row.argmax())}")
+        if dtype == "float32":
+            assert out.token_ids == [int(ref[len(prompt) - 1 + i].argmax()) for i in range(16)]
+
+
+def test_seeded_sampling_does_not_depend_on_batching(model_dirs):
+    import hi_b200
+
+    cfg, mdir = model_dirs["B"]
+    prompts = [h.random_tokens(cfg, n, seed=80 + n) for n in (5, 40, 70)]
+    sp = [hi_b200.SamplingParams(max_tokens=12, temperature=0.9, seed=5 + i, ignore_eos=True) for i in range(3)]
+    llm = hi_b200.LLM(mdir, dtype="float32", kv_page_size=16, max_batch_size=4, kv_cache_tokens=512)
+    together = [o.token_ids for o in llm.generate(prompts, sp)]
+    alone = [llm.generate([p], [s])[0].token_ids for p, s in zip(prompts, sp)]
+    assert together == alone
+
+
+# --------------------------------------------------------------------------- a toy mixer with state
+def test_toy_mixer_with_state_registers_builds_and_steps(model_dirs):
+    """A mixer defined here, with per-request state of fixed size (a running mean of a projection),
+    is registered, built into a model and stepped, without touching the framework's files."""
+    from hi_b200.engine.core import Engine, StepEntry
+    from hi_b200.parts import registry
+    from hi_b200.parts.basic import Part
+    from hi_b200.parts.model import Model
+    from hi_b200.parts.spec import CacheSpec, LayerSpec, ModelSpec, PartSpec, TensorSpec
+    from hi_b200.weights.loader import load_random
+
+    @registry.register("mixer", "toy_running_mean")
+    class ToyRunningMean(Part):
+        def __init__(self, params, prefix, env):
+            super().__init__(params, prefix, env)
+            self.h, self.d = int(params["hidden_size"]), int(params["state_size"])
+
+        def cache_spec(self):
+            return CacheSpec(state_shape=(self.d + 1,))          # running sum and count
+
+        def tensor_specs(self):
+            return [TensorSpec(f"{self.prefix}.in.weight", (self.d, self.h)),
+                    TensorSpec(f"{self.prefix}.out.weight", (self.h, self.d))]
+
+        def load(self, fetch):
+            self.w_in, self.w_out = fetch(f"{self.prefix}.in.weight"), fetch(f"{self.prefix}.out.weight")
+
+        def forward(self, normed, ctx, cache):
+            u = normed.float() @ self.w_in.float().T
+            out = torch.empty_like(u)
+            cu = [0]
+            for n in ctx.n_new:
+                cu.append(cu[-1] + n)
+            for s, slot in enumerate(ctx.slot_ids):
+                st = cache.state[slot]
+                seg = u[cu[s]:cu[s + 1]]
+                sums = st[: self.d] + torch.cumsum(seg, 0)
+                counts = st[self.d] + torch.arange(1, seg.shape[0] + 1, device=u.device)
+                out[cu[s]:cu[s + 1]] = sums / counts[:, None]
+                st[: self.d], st[self.d] = sums[-1], counts[-1]
+            return (out @ self.w_out.float().T).to(normed.dtype)
+
+    try:
+        H, V = 64, 97
+        norm = lambda n: PartSpec("rmsnorm", {"name": n, "size": H, "eps": 1e-5})
+        layers = []
+        for i in range(3):
+            mixer = PartSpec("toy_running_mean", {"name": "mix", "hidden_size": H, "state_size": 24}) if i != 1 else \
+                PartSpec("attention", {"name": "attn", "hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                                       "window": ("sliding", 9)})
+            layers.append(LayerSpec(prefix=f"toy.layers.{i}", mixer=mixer, norm_mixer=norm("n1"), norm_feed_forward=norm("n2"),
+                                    feed_forward=PartSpec("dense_swiglu", {"name": "ff", "hidden_size": H, "intermediate_size": 80})))
+        spec = ModelSpec(hidden_size=H, vocab_size=V, layers=tuple(layers), schedule=ModelSpec.sequential(3),
+                         embedding=PartSpec("token_embedding", {"name": "toy.embed", "vocab_size": V, "hidden_size": H}),
+                         final_norm=norm("toy.norm"), head=PartSpec("linear_head", {"name": "toy.head", "vocab_size": V,
+                                                                                    "hidden_size": H}))
+        model = Model(spec, torch.float32, "cuda:0")
+        load_random(model, seed=4, std=0.2)
+        eng = Engine(model, kv_page_size=4, kv_cache_tokens=64, max_active_requests=3)
+        assert [g.window for g in eng.manager.groups] == [("sliding", 9)]
+        toks = {r: [(7 * i + 3 * k) % V for i in range(n)] for k, (r, n) in enumerate((("a", 40), ("b", 23)))}
+        whole = {r: eng.step([StepEntry(r, t, list(range(len(t))))]) for r, t in toks.items()}
+        for r in toks:
+            eng.finish(r)
+        # the same requests in portions, interleaved: state and window must carry over
+        outs = {r: [] for r in toks}
+        pos = {r: 0 for r in toks}
+        sizes = [5, 1, 2, 7, 1, 3]
+        i = 0
+        while any(pos[r] < len(toks[r]) for r in toks):
+            entries = []
+            for r in toks:
+                if pos[r] < len(toks[r]):
+                    n = min(sizes[i % len(sizes)], len(toks[r]) - pos[r]); i += 1
+                    entries.append(StepEntry(r, toks[r][pos[r]:pos[r] + n], list(range(n))))
+                    pos[r] += n
+            lg = eng.step(entries)
+            row = 0
+            for e in entries:
+                outs[e.request_id].append(lg[row:row + len(e.tokens)]); row += len(e.tokens)
+            eng.manager.check_invariants()
+        for r in toks:
+            got = torch.cat(outs[r])
+            assert h.rel_err(got, whole[r].cpu()) <= 1e-4, f"toy mixer: request {r} differs between cuttings"
+            eng.finish(r)
+        sliding = eng.manager.snapshot()["groups"][0]
+        assert sliding["peak"] <= 2 * (9 // 4 + 3), "the sliding window kept pages it had passed"
+    finally:
+        registry.unregister("mixer", "toy_running_mean")

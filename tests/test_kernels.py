@@ -1,0 +1,280 @@
+"""Each CUDA kernel alone against a plain float32 reference, at sizes other than the models'."""
+import math
+
+import pytest
+import torch
+
+import plain_llama4 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)]
+
+
+def ops():
+    from hi_b200.kernels import ops as o
+    from hi_b200.parts.linear import configure_matmul_precision
+
+    configure_matmul_precision()
+    return o
+
+
+def close(got, want, tol, what=""):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = float((got - want).abs().max() / (want.abs().max() + 1e-12))
+    assert math.isfinite(err) and err <= tol, f"{what}: rel err {err:.3e} > {tol}"
+
+
+@pytest.mark.parametrize("dt,tol", DT)
+def test_embed_and_norm(dt, tol):
+    o = ops()
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(331, 120, generator=g).to(dt)
+    toks = torch.randint(0, 331, (29,), generator=g, dtype=torch.int32)
+    close(o.embed_gather(table.to(DEV), toks.to(DEV)), table.float()[toks.long()], 1e-7, "embed")
+    for hidden in (48, 120, 1000, 5120, 7168):
+        x = torch.randn(11, hidden, generator=g) * 3
+        d = torch.randn(11, hidden, generator=g).to(dt)
+        w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dt)
+        xg = x.clone().to(DEV)
+        y, y32 = o.add_rmsnorm(xg, d.to(DEV), w.to(DEV), 1e-5, dt, None, True)
+        want = plain.rms_norm(x + d.float(), w, 1e-5)
+        close(y, want, tol, f"rmsnorm hidden {hidden}")
+        close(y32, want, 2e-6, "rmsnorm float32 output")
+        close(xg, x + d.float(), 1e-7, "residual sum")
+        rows = torch.tensor([10, 0, 4], dtype=torch.int32)
+        before = xg.clone()
+        y2 = o.add_rmsnorm(xg, d.to(DEV), w.to(DEV), 1e-5, dt, rows.to(DEV))
+        close(y2, plain.rms_norm(before.cpu()[rows.long()] + d.float()[rows.long()], w, 1e-5), tol, "row map")
+        assert torch.equal(xg, before), "row-mapped norm must not touch the residual"
+
+
+@pytest.mark.parametrize("dt,tol", DT)
+def test_swiglu(dt, tol):
+    o = ops()
+    gu = (torch.randn(13, 2 * 72) * 2).to(dt)
+    g, u = gu[:, :72].float(), gu[:, 72:].float()
+    close(o.swiglu(gu.to(DEV)), g * torch.sigmoid(g) * u, tol, "swiglu")
+
+
+def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, interleaved, qk_norm, temp, seed):
+    """Two phases: fill `starts` tokens of every sequence, then run `lens` new tokens; returns the
+    kernel's q and attention output for the second phase and the plain reference's."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(lens)
+    total = [s + l for s, l in zip(starts, lens)]
+    n_pages = sum(-(-t // page) for t in total) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-t // page) for t in total)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    c = 0
+    for s in range(S):
+        for b in range(-(-total[s] // page)):
+            bt[s, b] = perm[c]; c += 1
+    kp = torch.full((n_pages, nkv, page, hd), float("nan")).to(dt).to(DEV)     # unwritten slots poison
+    vp = kp.clone()
+    qkv_all = [(torch.randn(t, (nh + 2 * nkv) * hd, generator=g) * 1.5).to(dt) for t in total]
+    got = None
+    for phase, (lo, hi) in enumerate((([0] * S, starts), (starts, total))):
+        spans = [(lo[s], hi[s]) for s in range(S)]
+        if sum(b - a for a, b in spans) == 0:
+            continue
+        qkv = torch.cat([qkv_all[s][a:b] for s, (a, b) in enumerate(spans)])
+        pos = torch.cat([torch.arange(a, b) for a, b in spans]).to(torch.int32)
+        sot = torch.cat([torch.full((b - a,), s) for s, (a, b) in enumerate(spans)]).to(torch.int32)
+        q = o.qkv_post(qkv.to(DEV), nh, nkv, hd, pos.to(DEV), None if inv_freq is None else inv_freq.to(DEV),
+                       interleaved, qk_norm, 1e-6, temp, sot.to(DEV), bt.to(DEV), kp, vp, page, True)
+        out = o.paged_attention(q, kp, vp, bt.to(DEV), sot.to(DEV), pos.to(DEV), chunk, window, hd ** -0.5)
+        got = (q, out)
+    # plain: whole sequences
+    want_q, want_o = [], []
+    for s in range(S):
+        x = qkv_all[s].float().view(total[s], nh + 2 * nkv, hd)
+        q, k, v = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
+        pos = torch.arange(total[s])
+        if inv_freq is not None:
+            q, k = plain.apply_rope(q, pos, inv_freq, interleaved), plain.apply_rope(k, pos, inv_freq, interleaved)
+        if qk_norm:
+            q, k = plain.rms_norm(q, None, 1e-6), plain.rms_norm(k, None, 1e-6)
+        if temp:
+            q = plain.attention_temperature(q, pos, *temp)
+        # the cache holds k, v in the engine dtype
+        k, v, qr = k.to(dt).float(), v.to(dt).float(), q.to(dt).float()
+        vis = plain.visibility(total[s], chunk or None)
+        if window:
+            idx = torch.arange(total[s])
+            vis = vis & (idx[None, :] > idx[:, None] - window)
+        o_ref = torch.empty(total[s], nh, hd)
+        for hh in range(nh):
+            sc = (qr[:, hh] @ k[:, hh // (nh // nkv)].T) * hd ** -0.5
+            o_ref[:, hh] = torch.softmax(sc.masked_fill(~vis, float("-inf")), -1) @ v[:, hh // (nh // nkv)]
+        want_q.append(q[starts[s]:]); want_o.append(o_ref[starts[s]:])
+    return got, (torch.cat(want_q), torch.cat(want_o))
+
+
+CASES = [  # nh, nkv, hd, page, chunk, window, interleaved, qk_norm, temp
+    (4, 2, 16, 4, 32, 0, False, True, None),
+    (10, 2, 48, 8, 0, 0, True, False, (8.0, 0.25)),
+    (6, 3, 32, 16, 16, 0, False, False, None),
+    (40, 8, 128, 64, 0, 0, False, True, None),
+    (5, 1, 256, 16, 0, 20, True, True, None),
+    (8, 8, 64, 32, 24, 0, False, False, None),
+    (7, 7, 80, 2, 10, 7, False, True, None),
+    (12, 4, 112, 64, 100, 0, False, False, None),
+]
+
+
+@pytest.mark.parametrize("dt,tol", DT)
+@pytest.mark.parametrize("case", CASES)
+def test_qkv_post_and_paged_attention(case, dt, tol):
+    o = ops()
+    nh, nkv, hd, page, chunk, window, inter, qkn, temp = case
+    inv = None if temp else plain.rope_inverse_frequencies(hd, 10000.0, None)
+    got, want = paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens=[37, 1, 70, 1], starts=[0, 130, 23, 63],
+                           inv_freq=inv, interleaved=inter, qk_norm=qkn, temp=temp, seed=nh * hd)
+    close(got[0], want[0].reshape(got[0].shape), tol, f"q {case}")
+    close(got[1], want[1].reshape(got[1].shape), tol, f"attention {case}")
+
+
+@pytest.mark.parametrize("dt,tol", DT)
+def test_one_far_key_among_hundreds(dt, tol):
+    """One old key, in the first page, matches the decoded token's query exactly and strongly:
+    the output must be that key's value row. Any key dropped at a page's edge shows at once."""
+    o = ops()
+    nh, nkv, hd, page = 4, 2, 64, 16
+    for far in (0, 15, 16, 17, 255, 256, 600):
+        n = 601
+        g = torch.Generator().manual_seed(far)
+        k = torch.randn(n, nkv, hd, generator=g) * 0.05
+        v = torch.randn(n, nkv, hd, generator=g)
+        q = torch.randn(1, nh, hd, generator=g) * 0.05
+        direction = torch.nn.functional.normalize(torch.randn(hd, generator=g), dim=0)
+        k[far] = direction * 30.0
+        q[0] = direction * 30.0
+        blocks = -(-n // page)
+        bt = torch.arange(blocks, dtype=torch.int32).flip(0).reshape(1, blocks).contiguous()
+        kp = torch.zeros(blocks, nkv, page, hd); vp = torch.zeros_like(kp)
+        for p in range(n):
+            kp[bt[0, p // page], :, p % page] = k[p]; vp[bt[0, p // page], :, p % page] = v[p]
+        out = o.paged_attention(q.to(dt).to(DEV), kp.to(dt).to(DEV), vp.to(dt).to(DEV), bt.to(DEV),
+                                torch.zeros(1, dtype=torch.int32, device=DEV),
+                                torch.tensor([n - 1], dtype=torch.int32, device=DEV), 0, 0, hd ** -0.5)
+        want = v[far].to(dt).float().repeat_interleave(nh // nkv, 0)
+        close(out[0], want, tol, f"far key at {far}")
+
+
+@pytest.mark.parametrize("dt,tol", DT)
+def test_window_edges(dt, tol):
+    """The strong key sits just inside or just outside the chunk or the sliding window."""
+    o = ops()
+    nh, nkv, hd, page = 2, 1, 32, 8
+    n = 100
+    g = torch.Generator().manual_seed(1)
+    direction = torch.nn.functional.normalize(torch.randn(hd, generator=g), dim=0)
+    for chunk, window, key, visible in ((32, 0, 96, True), (32, 0, 95, False), (0, 10, 90, True), (0, 10, 89, False),
+                                        (40, 0, 80, True), (40, 0, 79, False)):
+        k = torch.randn(n, nkv, hd, generator=g) * 0.05
+        v = torch.randn(n, nkv, hd, generator=g)
+        k[key] = direction * 30.0
+        q = (direction * 30.0).repeat(1, nh, 1)
+        blocks = -(-n // page)
+        bt = torch.arange(blocks, dtype=torch.int32).reshape(1, blocks)
+        kp = k.reshape(blocks, page, nkv, hd).permute(0, 2, 1, 3).contiguous() if n % page == 0 else None
+        if kp is None:
+            pad = blocks * page - n
+            kp = torch.cat([k, torch.zeros(pad, nkv, hd)]).reshape(blocks, page, nkv, hd).permute(0, 2, 1, 3).contiguous()
+            vp = torch.cat([v, torch.zeros(pad, nkv, hd)]).reshape(blocks, page, nkv, hd).permute(0, 2, 1, 3).contiguous()
+        else:
+            vp = v.reshape(blocks, page, nkv, hd).permute(0, 2, 1, 3).contiguous()
+        out = o.paged_attention(q.to(dt).to(DEV), kp.to(dt).to(DEV), vp.to(dt).to(DEV), bt.to(DEV),
+                                torch.zeros(1, dtype=torch.int32, device=DEV),
+                                torch.tensor([n - 1], dtype=torch.int32, device=DEV), chunk, window, hd ** -0.5)
+        hit = float((out[0, 0].float().cpu() - v[key, 0].to(dt).float()).abs().max()) < 0.05
+        assert hit == visible, f"chunk {chunk} window {window}: key {key} should be {'seen' if visible else 'masked'}"
+
+
+@pytest.mark.parametrize("dt,tol", DT)
+@pytest.mark.parametrize("shape", [(64, 4, 1, 128, 50), (192, 8, 2, 96, 33), (120, 5, 3, 72, 300), (120, 5, 5, 72, 1),
+                                   (256, 16, 1, 512, 8), (200, 128, 1, 64, 64), (104, 3, 2, 40, 700), (100, 4, 2, 36, 20)])
+def test_router_plan_and_experts(shape, dt, tol):
+    o = ops()
+    H, E, k, I, n = shape
+    g = torch.Generator().manual_seed(H + n)
+    x32 = torch.randn(n, H, generator=g)
+    x = x32.to(dt)
+    wr = torch.randn(E, H, generator=g).to(dt)
+    wg, wu = ((torch.randn(E, I, H, generator=g) * 0.1).to(dt) for _ in range(2))
+    wd = (torch.randn(E, H, I, generator=g) * 0.1).to(dt)
+    ids, scores, logits = o.router_topk(x32.to(DEV), wr.to(DEV), k, True)
+    ref_logits = x32 @ wr.float().T
+    close(logits, ref_logits, 1e-5, "router logits")
+    # the reference choice computed from the kernel's own logits: ties and order must agree exactly
+    ref_ids, ref_scores = plain.router_top_k(logits.cpu(), k)
+    assert torch.equal(ids.cpu().long(), ref_ids), "top-k choice or its order differs"
+    close(scores, ref_scores, 1e-6, "sigmoid scores")
+    offsets, sorted_entry, slot_of_entry = o.moe_plan(ids, E)
+    flat = ids.cpu().view(-1).long()
+    order = torch.sort(flat, stable=True).indices
+    counts = torch.bincount(flat, minlength=E)
+    assert offsets.cpu().tolist() == [0] + torch.cumsum(counts, 0).tolist()
+    assert torch.equal(sorted_entry.cpu()[: n * k].long(), order), "plan is not the stable sort by expert"
+    assert torch.equal(slot_of_entry.cpu()[: n * k].long()[order], torch.arange(n * k))
+    # experts: per sorted slot
+    expert_of_slot = flat[order]
+    token_of_slot = order // k
+    s = scores.cpu().view(-1)[order]
+    gate = torch.einsum("rh,rih->ri", x.float()[token_of_slot], wg.float()[expert_of_slot]) * s[:, None]
+    up = torch.einsum("rh,rih->ri", x.float()[token_of_slot], wu.float()[expert_of_slot]) * s[:, None]
+    act_ref = gate * torch.sigmoid(gate) * up
+    for few in (True, False):
+        act = o.moe_gate_up(x.to(DEV), sorted_entry, k, wg.to(DEV), wu.to(DEV), offsets, scores, few)
+        close(act, act_ref, tol, f"gate/up few={few}")
+        a = act_ref.to(dt)
+        y = o.moe_down(a.to(DEV), wd.to(DEV), offsets, few)
+        y_ref = torch.einsum("ri,rhi->rh", a.float(), wd.float()[expert_of_slot])
+        close(y, y_ref, 1e-5 if dt == torch.float32 else 1e-5, f"down few={few}")
+    shared = torch.randn(n, H, generator=g).to(dt)
+    out = o.moe_combine(y, slot_of_entry, shared.to(DEV), n, k)
+    want = shared.float() + y_ref[slot_of_entry.cpu()[: n * k].long()].view(n, k, H).sum(1)
+    close(out, want, 1e-5, "combine")
+
+
+def test_router_ties_go_to_the_lower_id():
+    o = ops()
+    x = torch.zeros(3, 16); x[:, 0] = 1.0
+    w = torch.zeros(6, 16)
+    w[:, 0] = torch.tensor([0.5, 2.0, 2.0, -1.0, 2.0, 0.5])
+    ids, scores, _ = o.router_topk(x.to(DEV), w.to(DEV), 4)
+    assert ids.cpu().tolist() == [[1, 2, 4, 0]] * 3
+    close(scores[0], torch.sigmoid(torch.tensor([2.0, 2.0, 2.0, 0.5])), 1e-6)
+
+
+def test_sampling_kernel_matches_the_plain_sampler():
+    o = ops()
+    g = torch.Generator().manual_seed(5)
+    for vocab in (17, 515, 1024, 50000):
+        logits = torch.randn(8, vocab, generator=g) * 3
+        logits[2, vocab // 2] = logits[2, 3] = 40.0            # a tie: the lower id wins
+        got = o.sample_rows(logits.to(DEV), None, None).cpu().tolist()
+        assert got == [int(torch.argmax(r)) for r in logits] and got[2] == 3
+        temps = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.5, 2.0, 0.9, 1.0])
+        us = torch.tensor([0.1, 0.5, 0.9, 0.3, 0.999, 0.0, 0.25, 0.75])
+        got = o.sample_rows(logits.to(DEV), temps.to(DEV), us.to(DEV)).cpu().tolist()
+        want = [plain.sample(logits[i], float(temps[i]), 1.0, 0, float(us[i])) for i in range(8)]
+        assert got == want, f"vocab {vocab}: {got} != {want}"
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    o = ops()
+    from hi_b200.kernels.ops import KernelError
+
+    with pytest.raises(KernelError):
+        o.embed_gather(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32))        # not on the GPU
+    q = torch.zeros(1, 2, 24, device=DEV)
+    pages = torch.zeros(1, 2, 4, 24, device=DEV)
+    bt = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError):
+        o.paged_attention(q, pages, pages, bt, z, z, 0, 0, 1.0)                     # head_dim 24
+    with pytest.raises(KernelError):
+        o.router_topk(torch.zeros(2, 8, device=DEV), torch.zeros(3, 8, device=DEV), 4)   # k > experts

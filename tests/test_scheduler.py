@@ -1,0 +1,154 @@
+"""The scheduler's decisions, on the host: admission, token budget and portions, decoding,
+finishing and freeing, and what happens when pages run out."""
+import random
+
+import pytest
+
+from hi_b200.cache import CacheManager
+from hi_b200.engine.scheduler import FINISHED, Request, Scheduler, SchedulerConfig
+from hi_b200.parts.spec import CacheSpec
+from hi_b200.sampling import SamplingParams
+
+GLOBAL = CacheSpec(kv_heads=1, head_dim=16, window=None)
+CHUNK = CacheSpec(kv_heads=1, head_dim=16, window=("chunk", 16))
+
+
+def make(pages=(64, 64), page=4, slots=8, eos=(), max_len=None, **cfg):
+    mgr = CacheManager([GLOBAL, CHUNK], list(pages), page_size=page, max_requests=slots)
+    return mgr, Scheduler(mgr, SchedulerConfig(**cfg), eos_token_ids=eos, max_model_len=max_len)
+
+
+def run_step(mgr, sched, next_token=lambda r: 1):
+    """What the engine does with a plan: reserve and commit pages, 'sample', commit the plan."""
+    plan = sched.plan()
+    for e in plan.entries:
+        rid = e.request.request_id
+        if not mgr.is_open(rid):
+            mgr.open(rid)
+        mgr.reserve(rid, len(e.tokens))
+    for e in plan.entries:
+        mgr.commit(e.request.request_id, len(e.tokens))
+    sampled = {e.request.request_id: next_token(e.request) for e in plan.entries if e.samples}
+    done = sched.commit(plan, sampled)
+    mgr.check_invariants()
+    return plan, done
+
+
+def req(rid, n, max_tokens=4, **kw):
+    return Request(rid, list(range(1, n + 1)), SamplingParams(max_tokens=max_tokens, **kw))
+
+
+def test_budget_cuts_prompts_into_portions_and_decodes_go_first():
+    mgr, s = make(max_batched_tokens=10, max_batch_size=4)
+    s.add(req("a", 23)); s.add(req("b", 5))
+    p1, _ = run_step(mgr, s)
+    assert [(e.request.request_id, len(e.tokens), e.samples) for e in p1.entries] == [("a", 10, False)]
+    p2, _ = run_step(mgr, s)
+    assert [(e.request.request_id, len(e.tokens)) for e in p2.entries] == [("a", 10)]
+    p3, _ = run_step(mgr, s)       # a's last 3 tokens (sampled), b admitted into the rest of the budget
+    assert [(e.request.request_id, len(e.tokens), e.samples) for e in p3.entries] == [("a", 3, True), ("b", 5, True)]
+    p4, _ = run_step(mgr, s)       # both decode: one token each, in one batch
+    assert [(e.request.request_id, e.tokens, e.samples) for e in p4.entries] == [("a", [1], True), ("b", [1], True)]
+    assert p4.entries[0].request.computed == 24
+
+
+def test_portions_respect_max_prefill_portion_and_batch_size():
+    mgr, s = make(max_batched_tokens=100, max_batch_size=2, max_prefill_portion=7)
+    for i in range(3):
+        s.add(req(i, 20))
+    p, _ = run_step(mgr, s)
+    assert [(e.request.request_id, len(e.tokens)) for e in p.entries] == [(0, 7), (1, 7)]
+    assert len(s.running) == 2 and len(s.waiting) == 1
+
+
+def test_finish_on_length_and_on_eos_frees_everything():
+    mgr, s = make(eos=(9,))
+    s.add(req("a", 6, max_tokens=3)); s.add(req("b", 6, max_tokens=50)); s.add(req("c", 6, max_tokens=50, ignore_eos=True))
+    toks = {"a": iter([5, 5, 5]), "b": iter([5, 9]), "c": iter([9, 9] + [5] * 60)}
+    done = []
+    while s.has_work():
+        _, d = run_step(mgr, s, lambda r: next(toks[r.request_id]))
+        done += d
+    by = {r.request_id: r for r in done}
+    assert by["a"].output == [5, 5, 5] and by["a"].finish_reason == "length"
+    assert by["b"].output == [5] and by["b"].finish_reason == "stop"          # EOS is not emitted
+    assert by["c"].output[:2] == [9, 9] and len(by["c"].output) == 50
+    assert all(p.free == p.total for p in mgr.pools) and mgr.free_slots == 8 and not mgr.requests
+
+
+def test_requests_are_validated_when_added():
+    mgr, s = make(pages=(4, 4), page=4, max_len=64)
+    with pytest.raises(ValueError, match="prompt is empty"):
+        s.add(Request("e", [], SamplingParams()))
+    with pytest.raises(ValueError, match="max_tokens"):
+        s.add(req("m", 3, max_tokens=0))
+    with pytest.raises(ValueError, match="temperature"):
+        s.add(req("t", 3, temperature=-1.0))
+    with pytest.raises(ValueError, match="top_p"):
+        s.add(req("p", 3, top_p=1.5))
+    with pytest.raises(ValueError, match="top_k"):
+        s.add(req("k", 3, top_k=0))
+    with pytest.raises(ValueError, match="context_length_exceeded"):
+        s.add(req("l", 60, max_tokens=5))
+    with pytest.raises(ValueError, match="insufficient_gpu_memory"):
+        s.add(req("g", 14, max_tokens=4))          # 18 tokens need 5 pages of the global group; it has 4
+    s.add(req("ok", 12, max_tokens=4))
+
+
+def test_when_pages_run_out_prompts_shrink_and_wait_and_nothing_new_is_admitted():
+    mgr, s = make(pages=(6, 6), page=4, max_batched_tokens=64, max_batch_size=4)
+    s.add(req("a", 16, max_tokens=2)); s.add(req("b", 14, max_tokens=2))
+    p1, _ = run_step(mgr, s)        # a takes 4 pages; b gets the 2 that are left: 8 of its 14 tokens
+    assert [(e.request.request_id, len(e.tokens)) for e in p1.entries] == [("a", 16), ("b", 8)]
+    assert s.counters["shrunk_portions"] == 1
+    s.add(req("c", 4, max_tokens=2))
+    p2, _ = run_step(mgr, s)        # a decodes (its 5th page would be needed: none free -> see below)
+    ids = [e.request.request_id for e in p2.entries]
+    assert "c" not in ids, "a new request was admitted while running ones lack pages"
+
+
+def test_a_decode_that_cannot_get_a_page_preempts_the_youngest_request():
+    mgr, s = make(pages=(6, 6), page=4, max_batched_tokens=64, max_batch_size=4)
+    s.add(req("old", 11, max_tokens=8)); s.add(req("young", 11, max_tokens=8))
+    run_step(mgr, s)                               # both prefilled: 3 + 3 pages, pool full
+    plan, _ = run_step(mgr, s)                     # position 11 fits the third page of each
+    assert len(plan.entries) == 2 and not plan.preempted
+    plan, _ = run_step(mgr, s)                     # position 12 needs a 4th page: none -> young is preempted
+    assert [r.request_id for r in plan.preempted] == ["young"]
+    assert [e.request.request_id for e in plan.entries] == ["old"]
+    young = plan.preempted[0]
+    assert young.status == "waiting" and young.computed == 0 and young.preemptions == 1 and len(young.output) == 2
+    assert s.waiting[0] is young and not mgr.is_open("young")
+    # it comes back with prompt + generated tokens as its prompt once pages are free, and finishes
+    while s.has_work():
+        run_step(mgr, s)
+    assert young.status == FINISHED and len(young.output) == 8 and young.finish_reason == "length"
+    assert all(p.free == p.total for p in mgr.pools)
+
+
+def test_seeded_generators_survive_preemption():
+    r = req("x", 3, temperature=1.0, seed=42)
+    first = [r.rng.next_f32() for _ in range(3)]
+    r2 = req("y", 3, temperature=1.0, seed=42)
+    assert [r2.rng.next_f32() for _ in range(3)] == first and all(0.0 <= u < 1.0 for u in first)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_workloads_finish_and_leak_nothing(seed):
+    rng = random.Random(seed)
+    mgr, s = make(pages=(rng.randint(12, 24),) * 2, page=4, slots=4, max_batched_tokens=rng.choice([8, 16, 40]),
+                  max_batch_size=3, max_active_requests=4, max_prefill_portion=rng.choice([None, 5]))
+    reqs = [req(i, rng.randint(1, 30), max_tokens=rng.randint(1, 12)) for i in range(12)]
+    pending = list(reqs)
+    steps = 0
+    while pending or s.has_work():
+        if pending and rng.random() < 0.5:
+            s.add(pending.pop(0))
+        if s.has_work():
+            plan, _ = run_step(mgr, s, lambda r: rng.randrange(3, 50))
+            assert plan.n_tokens <= s.config.max_batched_tokens and len(plan.entries) <= 3
+            assert plan.entries or plan.preempted
+        steps += 1
+        assert steps < 5000, "the scheduler does not make progress"
+    assert all(r.status == FINISHED and len(r.output) == r.params.max_tokens for r in reqs)
+    assert all(p.free == p.total for p in mgr.pools) and mgr.free_slots == 4
