@@ -123,6 +123,14 @@ class Engine:
     def length(self, request_id: Hashable) -> int:
         return self.manager.length(request_id) if self.manager.is_open(request_id) else 0
 
+    def assume_cached(self, request_id: Hashable, length: int) -> None:
+        """Benchmarks only: treat ``length`` tokens of a new request as already in the cache
+        (pages are taken; their contents are whatever the pools hold). Lets a decode step at a
+        long context be timed without running the prefill that would produce it."""
+        self.open(request_id)
+        self.manager.reserve(request_id, length)
+        self.manager.commit(request_id, length)
+
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], tap=None) -> Optional[torch.Tensor]:
         """Run one batch. Returns float32 logits [wanted, vocab] on the device, in the order

@@ -52,7 +52,11 @@ def lib():
     return _lib
 
 
+LAUNCHES = [0]     # kernels of this library enqueued so far (benchmarks report the difference)
+
+
 def _check(code: int, name: str) -> None:
+    LAUNCHES[0] += 1
     if code != 0:
         what = _ERRORS.get(code, f"CUDA error {code}")
         raise KernelError(f"{name}: {what}")

@@ -24,6 +24,22 @@ import torch
 F32 = torch.float32
 
 
+class precision:
+    """``with precision(torch.float64):`` runs the functions below in another float type; tests
+    use it to measure how much of a difference is the oracle's own rounding."""
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        global F32
+        self.saved, F32 = F32, self.dtype
+
+    def __exit__(self, *exc):
+        global F32
+        F32 = self.saved
+
+
 # --------------------------------------------------------------------------- config
 def layer_uses_rope(cfg: dict, i: int) -> bool:
     """models.rs:5953-5954 fixes NoPE to every 4th layer; the interval is a config key here.

@@ -67,14 +67,26 @@ def peaky_overrides(cfg, mdir, scale=6.0):
     return {n: (t.float() * scale) for n, t in w.items() if n.endswith(("q_proj.weight", "k_proj.weight"))}
 
 
+# how far q and k can be scaled up before the oracle's own float32 rounding (measured against
+# float64 in the test) or bfloat16's three digits drown the comparison. A and C norm q and k on
+# their rotary layers, so the sharpening lands on the global layers (every earlier key, with
+# temperature); B has no such norm, its scores grow with the square of the scale and its float32
+# oracle loses five digits at scale 2, so it is left out here.
+SHARPEN = {("A", "float32"): 5.0, ("A", "bfloat16"): 2.5, ("C", "float32"): 3.0, ("C", "bfloat16"): 2.0}
+
+
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "C"])
 def test_peaked_attention_under_cutting(name, dtype, tol, model_dirs, tmp_path):
     cfg, mdir = model_dirs[name]
-    sharp = h.make_model(str(tmp_path / "sharp"), cfg, seed=11, std=0.08, overrides=peaky_overrides(cfg, mdir))
+    sharp = h.make_model(str(tmp_path / "sharp"), cfg, seed=11, std=0.08,
+                         overrides=peaky_overrides(cfg, mdir, SHARPEN[name, dtype]))
     reqs = {f"r{i}": h.random_tokens(cfg, n, seed=40 + i) for i, n in enumerate([130, 75, 48])}
-    # the softmax must really be peaked somewhere, else this test shows nothing
     w = h.read_weights(sharp)
+    ref32 = plain.forward(cfg, w, reqs["r0"])
+    with plain.precision(torch.float64):
+        ref64 = plain.forward(cfg, {k: v.double() for k, v in w.items()}, reqs["r0"])
+    assert h.rel_err(ref32, ref64.float()) < h.TOL_F32 / 4, "the sharpened model is too ill-conditioned to be an oracle"
     for steps, regime in ((h.trace_portions(reqs), "portions"), (h.trace_mixed(reqs, 272, 16, seed=9), "mixed")):
         check(cfg, sharp, dtype, tol, steps, reqs, 16, 272, f"peaked {name} {dtype} {regime}", debug_poison=True)
 
