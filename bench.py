@@ -167,22 +167,24 @@ def main(argv=None) -> int:
 
     def timed_decode(batch):
         """W + K single-token steps of `batch` requests whose contexts end at ctx_len."""
-        total = args.warmup + args.steps
+        total = args.warmup + args.steps + 1
         ids = [f"d{batch}-{i}" for i in range(batch)]
         for rid in ids:
             engine.assume_cached(rid, ctx_len - total)
         toks = torch.randint(0, vocab, (total, batch), generator=cpu_gen).tolist()
-        distinct = []
+        # one step with a tap to count the distinct experts a step touches, then the warm-up
+        # steps (the first is eager, the second captures the CUDA graph of this shape)
+        taps = {}
+        engine.step([StepEntry(r, [toks[total - 1][i]], [0]) for i, r in enumerate(ids)],
+                    tap=lambda n, t: taps.__setitem__(n, t))
+        distinct = [len(set(t.flatten().tolist())) for n, t in taps.items() if n.endswith("router_ids")]
         for s in range(args.warmup):
-            taps = {}
-            engine.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)],
-                        tap=lambda n, t: taps.__setitem__(n, t))
-            distinct = [len(set(t.flatten().tolist())) for n, t in taps.items() if n.endswith("router_ids")]
+            engine.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
         torch.cuda.synchronize()
         launches0 = ops.LAUNCHES[0]
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        for s in range(args.warmup, total):
+        for s in range(args.warmup, total - 1):
             logits = engine.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
         end.record()
         torch.cuda.synchronize()

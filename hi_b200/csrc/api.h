@@ -26,7 +26,15 @@ int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, int rot_pairs
 int hb_paged_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                        const int* block_table, int table_stride, const int* seq_of_token, const int* positions,
                        void* out, int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
-                       float scale, cudaStream_t stream);
+                       float scale, int split_size, int max_splits, float* part_acc, float* part_ml,
+                       cudaStream_t stream);
+
+int hb_attention_merge(const float* part_acc, const float* part_ml, void* out, int dtype, int n_rows, int hd,
+                       int max_splits, cudaStream_t stream);
+int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                        int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
+                        int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int split_size,
+                        int max_splits, float* part_acc, float* part_ml, cudaStream_t stream);
 
 int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
                    int top_k, float* logits_out, int* ids, float* scores, cudaStream_t stream);

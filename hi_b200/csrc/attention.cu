@@ -21,19 +21,35 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
                                        int table_stride, const int* __restrict__ seq_of_token,
                                        const int* __restrict__ positions, T* __restrict__ out, int n_tokens,
                                        int nh, int nkv, int hd, int page_size, int chunk, int window,
-                                       float scale) {
+                                       float scale, int split_size, int max_splits,
+                                       float* __restrict__ part_acc, float* __restrict__ part_ml) {
   extern __shared__ float q_smem[];  // [warps][hd]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-  if (wid >= (long long)n_tokens * nh) return;
-  const int t = (int)(wid / nh);
-  const int h = (int)(wid - (long long)t * nh);
+  if (wid >= (long long)n_tokens * nh * max_splits) return;
+  const int split = (int)(wid % max_splits);
+  const long long th = wid / max_splits;
+  const int t = (int)(th / nh);
+  const int h = (int)(th - (long long)t * nh);
   const int kvh = h / (nh / nkv);
   const int pos = positions[t];
   const int* table = block_table + (size_t)seq_of_token[t] * table_stride;
   int lo = 0;
   if (chunk > 0) lo = (pos / chunk) * chunk;
   if (window > 0 && pos - window + 1 > lo) lo = pos - window + 1;
+  // split s of a token covers keys [lo + s*split_size, lo + (s+1)*split_size): a function of the
+  // token's own visible range only, never of the batch
+  int hi = pos;
+  if (max_splits > 1) {
+    float* ml = part_ml + ((size_t)th * max_splits + split) * 2;
+    const int first = lo + split * split_size;
+    if (first > pos) {
+      if (lane == 0) { ml[0] = -INFINITY; ml[1] = 0.f; }
+      return;
+    }
+    lo = first;
+    hi = min(pos, first + split_size - 1);
+  }
 
   float* qs = q_smem + warp * hd;
   const T* qrow = q + ((size_t)t * nh + h) * hd;
@@ -45,9 +61,9 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
 #pragma unroll
   for (int i = 0; i < kMaxDimsPerLane; ++i) acc[i] = 0.f;
 
-  for (int base = lo; base <= pos; base += 32) {
+  for (int base = lo; base <= hi; base += 32) {
     const int key = base + lane;
-    const bool valid = key <= pos;
+    const bool valid = key <= hi;
     float s = -INFINITY;
     int page = -1;
     if (valid) {
@@ -71,7 +87,7 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
     l = l * corr + hb::warp_sum(p);
 #pragma unroll
     for (int i = 0; i < kMaxDimsPerLane; ++i) acc[i] *= corr;
-    const int count = min(32, pos - base + 1);
+    const int count = min(32, hi - base + 1);
     for (int j = 0; j < count; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const int pg = __shfl_sync(0xffffffffu, page, j);
@@ -85,6 +101,19 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
     }
     m = m_new;
   }
+  if (max_splits > 1) {
+    float* pa = part_acc + ((size_t)th * max_splits + split) * hd;
+#pragma unroll
+    for (int i = 0; i < kMaxDimsPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) pa[d] = acc[i];
+    }
+    if (lane == 0) {
+      float* ml = part_ml + ((size_t)th * max_splits + split) * 2;
+      ml[0] = m; ml[1] = l;
+    }
+    return;
+  }
   const float inv = l > 0.f ? 1.f / l : 0.f;
   T* orow = out + ((size_t)t * nh + h) * hd;
 #pragma unroll
@@ -94,32 +123,79 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
   }
 }
 
+// Combine the splits of each (token, head): o = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m},
+// in split order.
+template <typename T>
+__global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                       T* __restrict__ out, int hd, int max_splits) {
+  const size_t th = blockIdx.x;
+  const float* ml = part_ml + th * max_splits * 2;
+  float m = -INFINITY;
+  for (int s = 0; s < max_splits; ++s) m = fmaxf(m, ml[2 * s]);
+  float l = 0.f;
+  for (int s = 0; s < max_splits; ++s) l += ml[2 * s] == -INFINITY ? 0.f : ml[2 * s + 1] * expf(ml[2 * s] - m);
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < max_splits; ++s)
+      if (ml[2 * s] != -INFINITY) o += part_acc[(th * max_splits + s) * hd + d] * expf(ml[2 * s] - m);
+    out[th * hd + d] = hb::from_f32<T>(o * inv);
+  }
+}
+
 }  // namespace
 
 extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                                   const int* block_table, int table_stride, const int* seq_of_token,
                                   const int* positions, void* out, int n_tokens, int nh, int nkv, int hd,
-                                  int page_size, int chunk, int window, float scale, cudaStream_t stream) {
+                                  int page_size, int chunk, int window, float scale, int split_size,
+                                  int max_splits, float* part_acc, float* part_ml, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !seq_of_token || !positions || !out) return HB_ERR_BAD_ARG;
+  if (max_splits < 1 || (max_splits > 1 && (split_size <= 0 || !part_acc || !part_ml))) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 ||
       chunk < 0 || window < 0)
     return HB_ERR_BAD_ARG;
   if (hd <= 0 || hd % 8 != 0 || hd > 32 * kMaxDimsPerLane) return HB_ERR_UNSUPPORTED;
   if (n_tokens == 0) return HB_OK;
   const int warps_per_block = 4;
-  const long long warps = (long long)n_tokens * nh;
+  const long long warps = (long long)n_tokens * nh * max_splits;
   const long long blocks = (warps + warps_per_block - 1) / warps_per_block;
   if (blocks > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
   const size_t smem = (size_t)warps_per_block * hd * sizeof(float);
   if (dtype == HB_DTYPE_F32)
     paged_attention_kernel<float><<<(int)blocks, warps_per_block * 32, smem, stream>>>(
         (const float*)q, (const float*)k_pages, (const float*)v_pages, block_table, table_stride, seq_of_token,
-        positions, (float*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale);
+        positions, (float*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale, split_size, max_splits,
+        part_acc, part_ml);
   else if (dtype == HB_DTYPE_BF16)
     paged_attention_kernel<__nv_bfloat16><<<(int)blocks, warps_per_block * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
         table_stride, seq_of_token, positions, (__nv_bfloat16*)out, n_tokens, nh, nkv, hd, page_size, chunk,
-        window, scale);
+        window, scale, split_size, max_splits, part_acc, part_ml);
+  else
+    return HB_ERR_BAD_ARG;
+  HB_LAUNCH_CHECK();
+  if (max_splits > 1) {
+    if (dtype == HB_DTYPE_F32)
+      attention_merge_kernel<float><<<n_tokens * nh, 64, 0, stream>>>(part_acc, part_ml, (float*)out, hd, max_splits);
+    else
+      attention_merge_kernel<__nv_bfloat16><<<n_tokens * nh, 64, 0, stream>>>(part_acc, part_ml,
+                                                                              (__nv_bfloat16*)out, hd, max_splits);
+    HB_LAUNCH_CHECK();
+  }
+  return HB_OK;
+}
+
+// Merge of split partials alone (the decode kernel writes the same partial layout).
+extern "C" int hb_attention_merge(const float* part_acc, const float* part_ml, void* out, int dtype, int n_rows,
+                                  int hd, int max_splits, cudaStream_t stream) {
+  if (!part_acc || !part_ml || !out || n_rows < 0 || hd <= 0 || max_splits < 1) return HB_ERR_BAD_ARG;
+  if (n_rows == 0) return HB_OK;
+  if (dtype == HB_DTYPE_F32)
+    attention_merge_kernel<float><<<n_rows, 64, 0, stream>>>(part_acc, part_ml, (float*)out, hd, max_splits);
+  else if (dtype == HB_DTYPE_BF16)
+    attention_merge_kernel<__nv_bfloat16><<<n_rows, 64, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, hd,
+                                                                     max_splits);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();

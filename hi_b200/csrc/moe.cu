@@ -26,7 +26,17 @@ __global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restric
   for (int e = warp; e < experts; e += nwarps) {
     const TW* wr = w + (size_t)e * hidden;
     float s = 0.f;
-    for (int j = lane; j < hidden; j += 32) s += hb::to_f32(xr[j]) * hb::to_f32(wr[j]);
+    if ((hidden & 7) == 0) {   // rows are 16-byte aligned: 8 elements per load
+      for (int j = lane * 8; j < hidden; j += 256) {
+        float xv[8], wv[8];
+        hb::load8(xr + j, xv);
+        hb::load8(wr + j, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += xv[i] * wv[i];
+      }
+    } else {
+      for (int j = lane; j < hidden; j += 32) s += hb::to_f32(xr[j]) * hb::to_f32(wr[j]);
+    }
     s = hb::warp_sum(s);
     if (lane == 0) {
       lg[e] = s;
@@ -199,74 +209,111 @@ __global__ void grouped_gemm_kernel(const T* __restrict__ A, int lda, const int*
 }
 
 // ------------------------------------------------------------------ grouped products, few rows per expert
-// Decode shape: the weights are streamed once, each warp owns output columns and keeps up to
-// RMAX rows' partial sums; 16-byte loads along K. Needs K % 8 == 0.
-constexpr int RMAX = 4;
+// Decode shape: the weights are streamed once. One warp per output column (and per pair of
+// gate/up rows when DUAL), lanes stride K with 16-byte loads, UNROLL independent loads in flight
+// per lane; up to RMAX rows of A share each weight load. Needs K % 8 == 0.
+constexpr int RMAX = 8;
 constexpr int GEMV_WARPS = 8;
-constexpr int GEMV_COLS_PER_WARP = 4;
+constexpr int GEMV_UNROLL = 4;
 
-template <typename T, bool DUAL>
-__global__ void grouped_gemv_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry,
-                                    int top_k, const T* __restrict__ W0, const T* __restrict__ W1,
-                                    const int* __restrict__ offsets, const float* __restrict__ scores,
-                                    void* __restrict__ out, int n_out, int K) {
-  const int e = blockIdx.y;
-  const int begin = offsets[e], end = offsets[e + 1];
-  if (begin == end) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int colbase = (blockIdx.x * GEMV_WARPS + warp) * GEMV_COLS_PER_WARP;
-  for (int r0 = begin; r0 < end; r0 += RMAX) {
-    const int nr = min(RMAX, end - r0);
-    const T* arow[RMAX];
-    float sc[RMAX];
+template <typename T, bool DUAL, int R>
+__device__ __forceinline__ void gemv_rows(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry,
+                                          int top_k, const T* __restrict__ w0, const T* __restrict__ w1,
+                                          const float* __restrict__ scores, void* __restrict__ out, int n_out,
+                                          int K, int n, int r0, int lane) {
+  const T* arow[R];
+  float sc[R];
 #pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      const int slot = r0 + (r < nr ? r : 0);
-      const size_t ar = sorted_entry ? (size_t)(sorted_entry[slot] / top_k) : (size_t)slot;
-      arow[r] = A + ar * lda;
-      sc[r] = DUAL ? scores[sorted_entry ? sorted_entry[slot] : slot] : 1.f;
+  for (int r = 0; r < R; ++r) {
+    const int slot = r0 + r;
+    const size_t ar = sorted_entry ? (size_t)(sorted_entry[slot] / top_k) : (size_t)slot;
+    arow[r] = A + ar * lda;
+    sc[r] = DUAL ? scores[sorted_entry ? sorted_entry[slot] : slot] : 1.f;
+  }
+  float g[R], u[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) { g[r] = 0.f; u[r] = 0.f; }
+  const int step = 256 * GEMV_UNROLL;
+  int k = lane * 8;
+  for (; k + 256 * (GEMV_UNROLL - 1) < K; k += step) {
+    float wv[GEMV_UNROLL][8], wu[DUAL ? GEMV_UNROLL : 1][8];
+#pragma unroll
+    for (int q = 0; q < GEMV_UNROLL; ++q) {
+      hb::load8(w0 + k + 256 * q, wv[q]);
+      if (DUAL) hb::load8(w1 + k + 256 * q, wu[q]);
     }
-    for (int c = 0; c < GEMV_COLS_PER_WARP; ++c) {
-      const int n = colbase + c;
-      if (n >= n_out) break;
-      const T* w0 = W0 + ((size_t)e * n_out + n) * K;
-      const T* w1 = DUAL ? W1 + ((size_t)e * n_out + n) * K : nullptr;
-      float g[RMAX] = {}, u[RMAX] = {};
-      for (int k = lane * 8; k < K; k += 256) {
-        float wv[8], wu[8];
-        hb::load8(w0 + k, wv);
-        if (DUAL) hb::load8(w1 + k, wu);
 #pragma unroll
-        for (int r = 0; r < RMAX; ++r) {
-          if (r < nr) {
-            float av[8];
-            hb::load8(arow[r] + k, av);
+    for (int q = 0; q < GEMV_UNROLL; ++q) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              g[r] += av[i] * wv[i];
-              if (DUAL) u[r] += av[i] * wu[i];
-            }
-          }
-        }
-      }
+      for (int r = 0; r < R; ++r) {
+        float av[8];
+        hb::load8(arow[r] + k + 256 * q, av);
 #pragma unroll
-      for (int r = 0; r < RMAX; ++r) {
-        if (r < nr) {
-          const float gs = hb::warp_sum(g[r]);
-          const float us = DUAL ? hb::warp_sum(u[r]) : 0.f;
-          if (lane == 0) {
-            const size_t o = (size_t)(r0 + r) * n_out + n;
-            if (DUAL) {
-              const float gg = sc[r] * gs, uu = sc[r] * us;
-              reinterpret_cast<T*>(out)[o] = hb::from_f32<T>(gg / (1.f + expf(-gg)) * uu);
-            } else {
-              reinterpret_cast<float*>(out)[o] = gs;
-            }
-          }
+        for (int i = 0; i < 8; ++i) {
+          g[r] += av[i] * wv[q][i];
+          if (DUAL) u[r] += av[i] * wu[q][i];
         }
       }
     }
   }
+  for (; k < K; k += 256) {
+    float wv[8], wu[8];
+    hb::load8(w0 + k, wv);
+    if (DUAL) hb::load8(w1 + k, wu);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float av[8];
+      hb::load8(arow[r] + k, av);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        g[r] += av[i] * wv[i];
+        if (DUAL) u[r] += av[i] * wu[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const float gs = hb::warp_sum(g[r]);
+    const float us = DUAL ? hb::warp_sum(u[r]) : 0.f;
+    if (lane == 0) {
+      const size_t o = (size_t)(r0 + r) * n_out + n;
+      if (DUAL) {
+        const float gg = sc[r] * gs, uu = sc[r] * us;
+        reinterpret_cast<T*>(out)[o] = hb::from_f32<T>(gg / (1.f + expf(-gg)) * uu);
+      } else {
+        reinterpret_cast<float*>(out)[o] = gs;
+      }
+    }
+  }
+}
+
+template <typename T, bool DUAL>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+grouped_gemv_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry, int top_k,
+                    const T* __restrict__ W0, const T* __restrict__ W1, const int* __restrict__ offsets,
+                    const float* __restrict__ scores, void* __restrict__ out, int n_out, int K) {
+  const int e = blockIdx.y;
+  const int begin = offsets[e], end = offsets[e + 1];
+  if (begin == end) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * GEMV_WARPS + warp;
+  if (n >= n_out) return;
+  const T* w0 = W0 + ((size_t)e * n_out + n) * K;
+  const T* w1 = DUAL ? W1 + ((size_t)e * n_out + n) * K : nullptr;
+  int r0 = begin;
+  // rows in runs of 8, 4, 2, 1: every row count is covered, each weight element is reused by
+  // the whole run
+  for (; r0 + 8 <= end; r0 += 8)
+    gemv_rows<T, DUAL, 8>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
+  if (r0 + 4 <= end) {
+    gemv_rows<T, DUAL, 4>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
+    r0 += 4;
+  }
+  if (r0 + 2 <= end) {
+    gemv_rows<T, DUAL, 2>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
+    r0 += 2;
+  }
+  if (r0 < end) gemv_rows<T, DUAL, 1>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
 }
 
 template <typename T>
@@ -274,7 +321,7 @@ int launch_grouped(bool dual, const void* A, int lda, const int* sorted_entry, i
                    const void* W1, const int* offsets, int experts, const float* scores, void* out, int n_entries,
                    int n_out, int K, int few_rows, cudaStream_t stream) {
   if (few_rows && K % 8 == 0 && lda % 8 == 0) {
-    dim3 grid((n_out + GEMV_WARPS * GEMV_COLS_PER_WARP - 1) / (GEMV_WARPS * GEMV_COLS_PER_WARP), experts);
+    dim3 grid((n_out + GEMV_WARPS - 1) / GEMV_WARPS, experts);
     if (dual)
       grouped_gemv_kernel<T, true><<<grid, GEMV_WARPS * 32, 0, stream>>>(
           (const T*)A, lda, sorted_entry, top_k, (const T*)W0, (const T*)W1, offsets, scores, out, n_out, K);
@@ -306,14 +353,15 @@ extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_d
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
   if (n == 0) return HB_OK;
   const size_t smem = (size_t)experts * sizeof(float);
+  const int threads = experts >= 16 ? 512 : (experts >= 8 ? 256 : 128);   // a warp per expert where that fits
   if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_F32)
-    router_topk_kernel<float, float><<<n, 128, smem, stream>>>((const float*)x, (const float*)w, hidden, experts,
+    router_topk_kernel<float, float><<<n, threads, smem, stream>>>((const float*)x, (const float*)w, hidden, experts,
                                                                top_k, logits_out, ids, scores);
   else if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_BF16)
-    router_topk_kernel<float, __nv_bfloat16><<<n, 128, smem, stream>>>(
+    router_topk_kernel<float, __nv_bfloat16><<<n, threads, smem, stream>>>(
         (const float*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
   else if (x_dtype == HB_DTYPE_BF16 && w_dtype == HB_DTYPE_BF16)
-    router_topk_kernel<__nv_bfloat16, __nv_bfloat16><<<n, 128, smem, stream>>>(
+    router_topk_kernel<__nv_bfloat16, __nv_bfloat16><<<n, threads, smem, stream>>>(
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
   else
     return HB_ERR_BAD_ARG;

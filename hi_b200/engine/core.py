@@ -42,6 +42,12 @@ def _require_cuda(device) -> None:
     configure_matmul_precision()
 
 
+def _count_launches(n: int) -> None:
+    from ..kernels import ops
+
+    ops.LAUNCHES[0] += n
+
+
 def _pinned_int32(n: int) -> torch.Tensor:
     return torch.empty(n, dtype=torch.int32, pin_memory=True)
 
@@ -74,7 +80,7 @@ class Engine:
 
     def __init__(self, model: Model, *, kv_page_size: int = 64, kv_cache_tokens: int = 8192,
                  windowed_cache_tokens: Optional[int] = None, max_active_requests: int = 8,
-                 debug_poison: bool = False):
+                 debug_poison: bool = False, use_cuda_graphs: bool = True):
         _require_cuda(model.device)
         self.model = model
         self.device = model.device
@@ -91,6 +97,8 @@ class Engine:
         self.vocab_size = model.spec.vocab_size
         self.stats = EngineStats()
         self.debug_poison = debug_poison
+        self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
+        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -176,9 +184,17 @@ class Engine:
                 self.manager.close(rid)
             raise
 
-        ctx, logit_rows = self._build_context(entries)
-        ctx.tap = tap
-        logits = self.model.forward(ctx, self.cache.views, logit_rows)
+        graph = self._decode_graph_for(entries) if tap is None else None
+        if graph is not None:
+            self._build_context(entries, widths=graph.widths, static=graph)
+            graph.graph.replay()
+            _count_launches(graph.kernels)
+            logits = graph.logits.clone()
+            ctx, logit_rows = graph.ctx, graph.logit_rows
+        else:
+            ctx, logit_rows = self._build_context(entries)
+            ctx.tap = tap
+            logits = self.model.forward(ctx, self.cache.views, logit_rows)
         for e in entries:
             returned = self.manager.commit(e.request_id, len(e.tokens))
             if self.debug_poison and returned:
@@ -194,8 +210,10 @@ class Engine:
         st.logit_rows += 0 if logit_rows is None else int(logit_rows.numel())
         return logits
 
-    def _build_context(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, Optional[torch.Tensor]]:
-        """All of a step's integer inputs in one pinned buffer, one host-to-device copy."""
+    def _build_context(self, entries: Sequence[StepEntry], widths: Optional[List[int]] = None,
+                       static: Optional["_DecodeGraph"] = None) -> Tuple[StepContext, Optional[torch.Tensor]]:
+        """All of a step's integer inputs in one pinned buffer, one host-to-device copy.
+        With ``static`` the buffers of a captured decode graph are filled instead."""
         mgr = self.manager
         n_seqs = len(entries)
         n_tokens = sum(len(e.tokens) for e in entries)
@@ -203,7 +221,8 @@ class Engine:
         n_new = [len(e.tokens) for e in entries]
         slots = [mgr.slot(e.request_id) for e in entries]
         tables = [[mgr.table(g, e.request_id) for e in entries] for g in range(len(mgr.groups))]
-        widths = [max(len(t) for t in tg) for tg in tables]
+        if widths is None:
+            widths = [max(len(t) for t in tg) for tg in tables]
         n_want = sum(len(e.want) for e in entries)
 
         def pad4(n):
@@ -214,7 +233,11 @@ class Engine:
         for s in sizes:
             offsets.append(total)
             total += pad4(s)
-        host = _pinned_int32(max(total, 4))
+        if static is not None:
+            static.copied.synchronize()          # the previous step's copy has left the pinned buffer
+            host = static.host
+        else:
+            host = _pinned_int32(max(total, 4))
         buf = host.numpy()
         o_tok, o_pos, o_seq, o_cu, o_slot, o_want = offsets[:6]
         cursor, want_cursor = 0, 0
@@ -236,6 +259,10 @@ class Engine:
             view[:] = -1
             for s, t in enumerate(tg):
                 view[s, : len(t)] = t
+        if static is not None:
+            static.dev.copy_(host, non_blocking=True)
+            static.copied.record()
+            return static.ctx, static.logit_rows
         dev = host.to(self.device, non_blocking=True)
 
         def seg(off, n):
@@ -252,9 +279,83 @@ class Engine:
         logit_rows = seg(o_want, n_want) if n_want else None
         return ctx, logit_rows
 
+    # ------------------------------------------------------------------ captured decode steps
+    CONTEXT_BUCKET = 1024     # a decode graph serves contexts up to a multiple of this
+
+    def _decode_graph_for(self, entries: Sequence[StepEntry]) -> Optional["_DecodeGraph"]:
+        """A CUDA graph of the whole step for batches of single decoded tokens that all want
+        their logits: same kernels as the eager step, launched once. Keyed by batch size and the
+        context bucket (which fixes the block-table widths and the attention splits)."""
+        if not self.use_cuda_graphs or any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return None
+        longest = max(self.manager.length(e.request_id) for e in entries) + 1
+        bucket = -(-longest // self.CONTEXT_BUCKET) * self.CONTEXT_BUCKET
+        key = (len(entries), bucket)
+        graph = self._graphs.get(key)
+        if graph is None:
+            if len(self._graphs) >= 16:
+                self._graphs.pop(next(iter(self._graphs)))
+            graph = _DecodeGraph(self, len(entries), bucket)
+            self._graphs[key] = graph
+        if not graph.captured:
+            if graph.eager_runs < 1:          # the first step of a shape runs eagerly (library warm-up)
+                graph.eager_runs += 1
+                return None
+            graph.capture(entries)
+        return graph
+
     # ------------------------------------------------------------------ bookkeeping
     def snapshot(self) -> dict:
         s = self.manager.snapshot()
         s.update(steps=self.stats.steps, tokens=self.stats.tokens, prefill_tokens=self.stats.prefill_tokens,
                  decode_tokens=self.stats.decode_tokens, cache_bytes=self.cache.bytes)
         return s
+
+
+class _DecodeGraph:
+    """Static buffers and the captured graph of one decode-step shape."""
+
+    def __init__(self, engine: Engine, n_seqs: int, bucket: int):
+        self.engine, self.n_seqs, self.bucket = engine, n_seqs, bucket
+        self.widths = [-(-bucket // engine.page_size) for _ in engine.manager.groups]
+        pad4 = lambda n: (n + 3) // 4 * 4
+        sizes = [n_seqs, n_seqs, n_seqs, n_seqs + 1, n_seqs, n_seqs] + [n_seqs * w for w in self.widths]
+        offsets, total = [], 0
+        for sz in sizes:
+            offsets.append(total)
+            total += pad4(sz)
+        self.host = _pinned_int32(total)
+        self.dev = torch.zeros(total, dtype=torch.int32, device=engine.device)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+        seg = lambda off, n: self.dev[off: off + n]
+        tables = {g: seg(offsets[6 + g], n_seqs * w).view(n_seqs, w) for g, w in enumerate(self.widths)}
+        self.ctx = StepContext(
+            n_tokens=n_seqs, n_seqs=n_seqs, tokens=seg(offsets[0], n_seqs), positions=seg(offsets[1], n_seqs),
+            seq_of_token=seg(offsets[2], n_seqs), cu_seqlens=seg(offsets[3], n_seqs + 1), slots=seg(offsets[4], n_seqs),
+            start_pos=[0] * n_seqs, n_new=[1] * n_seqs, slot_ids=[0] * n_seqs, block_tables=tables,
+            page_size=engine.page_size, max_context=bucket)
+        self.logit_rows = seg(offsets[5], n_seqs)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.captured = False
+        self.eager_runs = 0
+
+    def capture(self, entries: Sequence[StepEntry]) -> None:
+        eng = self.engine
+        eng._build_context(entries, widths=self.widths, static=self)     # valid inputs for the capture run
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):                                   # once outside capture, on a side stream
+            eng.model.forward(self.ctx, eng.cache.views, self.logit_rows)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        from ..kernels import ops
+
+        before = ops.LAUNCHES[0]
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = eng.model.forward(self.ctx, eng.cache.views, self.logit_rows)
+        self.kernels = ops.LAUNCHES[0] - before      # this library's kernels in one replay
+        self.captured = True

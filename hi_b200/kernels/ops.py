@@ -22,7 +22,9 @@ _SIGNATURES = {
     "hb_swiglu": [P, P, I, I, I, P],
     "hb_moe_combine": [P, P, P, I, P, I, I, I, P],
     "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
-    "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
+    "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
+    "hb_attention_merge": [P, P, P, I, I, I, I, P],
+    "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P],
     "hb_moe_gate_up": [P, I, P, I, P, P, P, I, P, P, I, I, I, I, P],
@@ -198,10 +200,18 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
     return q
 
 
+ATTENTION_SPLIT = 256      # keys per split of the general attention kernel
+DECODE_TARGET_CTAS = 148 * 4   # the decode kernel's grid aims at a few blocks per SM
+
+
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                     seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int,
-                    scale: float) -> torch.Tensor:
-    """softmax(q k^T * scale) v over the keys each token may read; q [N, nh, hd] -> [N, nh, hd]."""
+                    scale: float, max_context: int = 0) -> torch.Tensor:
+    """softmax(q k^T * scale) v over the keys each token may read; q [N, nh, hd] -> [N, nh, hd].
+
+    ``max_context`` (an upper bound of position + 1 over the tokens) lets long ranges be cut into
+    splits of ``ATTENTION_SPLIT`` keys that run in parallel and are merged; a token's splits depend
+    on its own range only. 0 = one pass per (token, head)."""
     _need(q, "q"); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
     for t, nm in ((block_table, "block_table"), (seq_of_token, "seq_of_token"), (positions, "positions")):
         _need(t, nm, torch.int32)
@@ -214,10 +224,67 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     if hd % 16 != 0 or hd > 256:
         raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256)")
     out = torch.empty_like(q)
+    longest = max_context
+    if chunk > 0:
+        longest = min(longest, chunk)
+    if window > 0:
+        longest = min(longest, window)
+    splits = max(1, -(-longest // ATTENTION_SPLIT))
+    part_acc = part_ml = None
+    if splits > 1:
+        part_acc = torch.empty((n, nh, splits, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, nh, splits, 2), dtype=torch.float32, device=q.device)
     _check(lib().hb_paged_attention(_ptr(q), _dt(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                     block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv,
-                                    hd, page_size, int(chunk), int(window), float(scale), _stream()),
+                                    hd, page_size, int(chunk), int(window), float(scale), ATTENTION_SPLIT, splits,
+                                    _ptr(part_acc), _ptr(part_ml), _stream()),
            "paged_attention")
+    return out
+
+
+def decode_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int) -> bool:
+    """Shapes the tensor-core decode kernel takes; anything else goes to the general kernel."""
+    return q_dtype == torch.bfloat16 and hd in (64, 128) and nh % nkv == 0 and nh // nkv <= 16
+
+
+def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                     seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int, scale: float,
+                     max_context: int) -> torch.Tensor:
+    """Attention for a batch of single decoded tokens (every row of ``q`` is one request's
+    token), bfloat16, split over runs of ``ATTENTION_SPLIT`` keys. Uses scratch memory for the
+    partial results of the splits."""
+    _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
+    for t, nm in ((block_table, "block_table"), (seq_of_token, "seq_of_token"), (positions, "positions")):
+        _need(t, nm, torch.int32)
+    n, nh, hd = q.shape
+    _, nkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd or k_pages.shape != v_pages.shape:
+        raise KernelError("cache pages do not match the query's head_dim")
+    if not decode_attention_supported(q.dtype, nh, nkv, hd):
+        raise KernelError(f"decode attention does not take nh={nh} nkv={nkv} head_dim={hd}")
+    longest = max(int(max_context), 1)
+    if chunk > 0:
+        longest = min(longest, chunk)
+    if window > 0:
+        longest = min(longest, window)
+    # enough splits to fill the GPU a few times over, none shorter than ATTENTION_SPLIT keys;
+    # the cut moves results by rounding only
+    wanted = -(-DECODE_TARGET_CTAS // max(1, n * nkv))
+    splits = max(1, min(wanted, -(-longest // ATTENTION_SPLIT)))
+    split_size = -(-(-(-longest // splits)) // 64) * 64
+    splits = max(1, -(-longest // split_size))
+    out = torch.empty_like(q)
+    part_acc = part_ml = None
+    if splits > 1:
+        part_acc = torch.empty((n, nh, splits, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, nh, splits, 2), dtype=torch.float32, device=q.device)
+    _check(lib().hb_attention_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                                     _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size,
+                                     int(chunk), int(window), float(scale), split_size, splits, _ptr(part_acc),
+                                     _ptr(part_ml), _stream()), "attention_decode")
+    if splits > 1:
+        _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
+                                        _stream()), "attention_merge")
     return out
 
 

@@ -28,6 +28,8 @@ class AttentionMixer(Part):
     tensors: ``<prefix>.{q,k,v,o}_proj.weight``.
     """
 
+    graph_safe = True
+
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         p = params
@@ -80,6 +82,11 @@ class AttentionMixer(Part):
                          cache.v_pages, ctx.page_size, cache.writes)
         chunk = self.window[1] if self.window and self.window[0] == "chunk" else 0
         sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
-        o = ops.paged_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
-                                chunk, sliding, self.scale)
+        if ctx.max_new == 1 and ops.decode_attention_supported(q.dtype, self.nh, self.nkv, self.hd):
+            # every token of the step is one request's decoded token: the tensor-core kernel
+            o = ops.decode_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
+                                     chunk, sliding, self.scale, ctx.max_context)
+        else:
+            o = ops.paged_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
+                                    chunk, sliding, self.scale, ctx.max_context)
         return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o)

@@ -14,7 +14,13 @@ from .spec import PartSpec, TensorSpec
 
 
 class Part:
-    """Common shape of a part: parameters in, tensors by name, nothing model-specific."""
+    """Common shape of a part: parameters in, tensors by name, nothing model-specific.
+
+    ``graph_safe``: the part's forward only enqueues work whose shape depends on the number of
+    tokens and reads the step's device tensors, never its host-side lists; a decode step made of
+    such parts may be captured in a CUDA graph. A part that does not say so is never captured."""
+
+    graph_safe = False
 
     def __init__(self, params: dict, prefix: str, env: BuildEnv):
         self.params, self.prefix, self.env = params, prefix, env
@@ -35,6 +41,8 @@ class RMSNorm(Part):
     """y = x * rsqrt(mean(x^2) + eps) * w, statistics in float32
     (crates/hi-mlx/src/models.rs:1977-1979; crates/hi-cuda/src/kernels.cu:61-77).
     params: ``size``, ``eps``, ``name`` (tensor ``<prefix>.weight``)."""
+
+    graph_safe = True
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -84,6 +92,8 @@ class RotaryPosition(Part):
     params: ``head_dim``, ``theta``, ``scaling`` (dict or None), ``interleaved`` (pairs (2j, 2j+1)
     instead of (j, j + hd/2))."""
 
+    graph_safe = True
+
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.interleaved = bool(params.get("interleaved", False))
@@ -101,6 +111,8 @@ class RotaryPosition(Part):
 class NoPosition(Part):
     """NoPE: q and k are used as projected."""
 
+    graph_safe = True
+
     def rotary_table(self):
         return None
 
@@ -110,6 +122,8 @@ class NoPosition(Part):
 class TokenEmbedding(Part):
     """x[t] = table[token[t]], no multiplier (crates/hi-mlx/src/models.rs:6206, 1915-1917).
     params: ``vocab_size``, ``hidden_size``; tensor ``<prefix>.weight``."""
+
+    graph_safe = True
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -130,6 +144,8 @@ class LinearHead(Part):
     """logits = z W^T in float32. The separate head is used when its tensor exists, else the
     embedding table (decided by presence, crates/hi-mlx/src/models.rs:6186-6193, 6211-6214).
     params: ``vocab_size``, ``hidden_size``, ``tie`` (random weights: write no head tensor)."""
+
+    graph_safe = True
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -159,6 +175,8 @@ class PreNormBlock(Part):
     The residual stream is float32. A sub-layer's output is carried as ``pending`` and added
     inside the next norm kernel, so each residual sum is one fused read-modify-write.
     """
+
+    graph_safe = True
 
     def forward(self, layer, residual, pending, ctx, cache_view):
         h = layer.norm_mixer.forward(residual, pending)

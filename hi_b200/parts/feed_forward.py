@@ -41,6 +41,8 @@ class _SwiGLU:
 class DenseSwiGLU(Part):
     """params: ``hidden_size``, ``intermediate_size``; tensors ``<prefix>.{gate,up,down}_proj.weight``."""
 
+    graph_safe = True
+
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.mlp = _SwiGLU(prefix, int(params["hidden_size"]), int(params["intermediate_size"]))
@@ -66,6 +68,8 @@ class SigmoidRoutedExperts(Part):
     tensors: ``<prefix>.router.weight`` [E, H]; ``<prefix>.experts.{gate,up}_proj.weight`` [E, I, H];
     ``<prefix>.experts.down_proj.weight`` [E, H, I]; ``<prefix>.shared_expert.{gate,up,down}_proj.weight``.
     """
+
+    graph_safe = True
 
     FEW_ROWS = 128   # up to this many routed rows the weight-streaming kernel is used
     wants_f32_input = True   # the router reads the norm's float32 output

@@ -60,6 +60,8 @@ class Model:
             if slot not in writers:
                 raise ValueError(f"cache slot {slot} is read but no schedule entry writes it")
         self.loaded = False
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self.all_parts()) and \
+            all(getattr(l.arrangement, "graph_safe", False) for l in self.layers)
 
     # ---- weights
     def all_parts(self):

@@ -23,7 +23,7 @@ def engine_for(mdir, dtype, page, tokens=256, slots=4, **kw):
 
 def check(cfg, mdir, dtype, tol, steps, reqs, page, tokens, what, **kw):
     eng = engine_for(mdir, dtype, page, tokens, **kw)
-    got, forced = h.replay_in_process(eng, steps, record_routing=True)
+    got, forced = h.replay_in_process(eng, steps, record_routing=(dtype == "bfloat16"))
     h.compare_with_plain(cfg, h.read_weights(mdir), reqs, got, tol, forced=forced if dtype == "bfloat16" else None,
                          what=what, margin=0.1)
     assert not eng.manager.requests, "requests left open"
@@ -72,7 +72,7 @@ def peaky_overrides(cfg, mdir, scale=6.0):
 # their rotary layers, so the sharpening lands on the global layers (every earlier key, with
 # temperature); B has no such norm, its scores grow with the square of the scale and its float32
 # oracle loses five digits at scale 2, so it is left out here.
-SHARPEN = {("A", "float32"): 5.0, ("A", "bfloat16"): 2.5, ("C", "float32"): 3.0, ("C", "bfloat16"): 2.0}
+SHARPEN = {("A", "float32"): 5.0, ("A", "bfloat16"): 2.5, ("C", "float32"): 2.0, ("C", "bfloat16"): 2.0}
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)

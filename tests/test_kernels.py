@@ -57,7 +57,8 @@ def test_swiglu(dt, tol):
     close(o.swiglu(gu.to(DEV)), g * torch.sigmoid(g) * u, tol, "swiglu")
 
 
-def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, interleaved, qk_norm, temp, seed):
+def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, interleaved, qk_norm, temp, seed,
+               split=True):
     """Two phases: fill `starts` tokens of every sequence, then run `lens` new tokens; returns the
     kernel's q and attention output for the second phase and the plain reference's."""
     g = torch.Generator().manual_seed(seed)
@@ -84,7 +85,8 @@ def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, 
         sot = torch.cat([torch.full((b - a,), s) for s, (a, b) in enumerate(spans)]).to(torch.int32)
         q = o.qkv_post(qkv.to(DEV), nh, nkv, hd, pos.to(DEV), None if inv_freq is None else inv_freq.to(DEV),
                        interleaved, qk_norm, 1e-6, temp, sot.to(DEV), bt.to(DEV), kp, vp, page, True)
-        out = o.paged_attention(q, kp, vp, bt.to(DEV), sot.to(DEV), pos.to(DEV), chunk, window, hd ** -0.5)
+        out = o.paged_attention(q, kp, vp, bt.to(DEV), sot.to(DEV), pos.to(DEV), chunk, window, hd ** -0.5,
+                                max(total) if split else 0)
         got = (q, out)
     # plain: whole sequences
     want_q, want_o = [], []
@@ -130,10 +132,62 @@ def test_qkv_post_and_paged_attention(case, dt, tol):
     o = ops()
     nh, nkv, hd, page, chunk, window, inter, qkn, temp = case
     inv = None if temp else plain.rope_inverse_frequencies(hd, 10000.0, None)
-    got, want = paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens=[37, 1, 70, 1], starts=[0, 130, 23, 63],
-                           inv_freq=inv, interleaved=inter, qk_norm=qkn, temp=temp, seed=nh * hd)
-    close(got[0], want[0].reshape(got[0].shape), tol, f"q {case}")
-    close(got[1], want[1].reshape(got[1].shape), tol, f"attention {case}")
+    for lens, starts, split in (([37, 1, 70, 1], [0, 130, 23, 63], False), ([300, 1, 2, 1], [0, 700, 255, 256], True)):
+        got, want = paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens=lens, starts=starts,
+                               inv_freq=inv, interleaved=inter, qk_norm=qkn, temp=temp, seed=nh * hd, split=split)
+        close(got[0], want[0].reshape(got[0].shape), tol, f"q {case}")
+        close(got[1], want[1].reshape(got[1].shape), tol, f"attention {case} split={split}")
+
+
+@pytest.mark.parametrize("shape", [(40, 8, 128, 64, 0, 0), (8, 8, 64, 16, 0, 0), (32, 2, 128, 32, 512, 0), (10, 2, 64, 8, 0, 300),
+                                   (3, 1, 128, 64, 100, 0)])
+def test_decode_attention_on_tensor_cores(shape):
+    """The decode kernel (bfloat16, split over 256-key runs) against whole-sequence attention, for
+    requests of very different lengths in one batch, and against the general kernel."""
+    o = ops()
+    nh, nkv, hd, page, chunk, window = shape
+    lens = [1, 1, 1, 1, 1, 1]
+    starts = [0, 63, 255, 256, 1030, 2500]
+    inv = plain.rope_inverse_frequencies(hd, 10000.0, None)
+    g = torch.Generator().manual_seed(nh + hd)
+    S = len(lens)
+    total = [s + l for s, l in zip(starts, lens)]
+    n_pages = sum(-(-t // page) for t in total) + 2
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-t // page) for t in total)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    c = 0
+    for s in range(S):
+        for b in range(-(-total[s] // page)):
+            bt[s, b] = perm[c]; c += 1
+    dt = torch.bfloat16
+    kp = torch.zeros(n_pages, nkv, page, hd, dtype=dt)
+    vp = torch.zeros_like(kp)
+    ks = [torch.randn(t, nkv, hd, generator=g).to(dt) for t in total]
+    vs = [torch.randn(t, nkv, hd, generator=g).to(dt) for t in total]
+    for s in range(S):
+        for p in range(total[s]):
+            kp[bt[s, p // page], :, p % page] = ks[s][p]; vp[bt[s, p // page], :, p % page] = vs[s][p]
+    q = (torch.randn(S, nh, hd, generator=g) * 2).to(dt)
+    pos = torch.tensor([t - 1 for t in total], dtype=torch.int32)
+    sot = torch.arange(S, dtype=torch.int32)
+    args = (q.to(DEV), kp.to(DEV), vp.to(DEV), bt.to(DEV), sot.to(DEV), pos.to(DEV), chunk, window, hd ** -0.5, max(total))
+    got = o.decode_attention(*args)
+    general = o.paged_attention(*args)
+    want = torch.empty(S, nh, hd)
+    for s in range(S):
+        p = total[s] - 1
+        lo = (p // chunk) * chunk if chunk else 0
+        if window:
+            lo = max(lo, p - window + 1)
+        for hh in range(nh):
+            kv = hh // (nh // nkv)
+            sc = (ks[s][lo:p + 1, kv].float() @ q[s, hh].float()) * hd ** -0.5
+            want[s, hh] = torch.softmax(sc, 0) @ vs[s][lo:p + 1, kv].float()
+    close(got, want, 2e-2, f"decode attention {shape}")
+    close(general, want, 2e-2, f"general attention {shape}")
+    assert not o.decode_attention_supported(torch.float32, nh, nkv, hd)
+    assert not o.decode_attention_supported(torch.bfloat16, 40, 2, 128) and not o.decode_attention_supported(torch.bfloat16, 4, 2, 48)
 
 
 @pytest.mark.parametrize("dt,tol", DT)
@@ -158,9 +212,14 @@ def test_one_far_key_among_hundreds(dt, tol):
             kp[bt[0, p // page], :, p % page] = k[p]; vp[bt[0, p // page], :, p % page] = v[p]
         out = o.paged_attention(q.to(dt).to(DEV), kp.to(dt).to(DEV), vp.to(dt).to(DEV), bt.to(DEV),
                                 torch.zeros(1, dtype=torch.int32, device=DEV),
-                                torch.tensor([n - 1], dtype=torch.int32, device=DEV), 0, 0, hd ** -0.5)
+                                torch.tensor([n - 1], dtype=torch.int32, device=DEV), 0, 0, hd ** -0.5, n)
         want = v[far].to(dt).float().repeat_interleave(nh // nkv, 0)
         close(out[0], want, tol, f"far key at {far}")
+        if dt == torch.bfloat16:
+            fast = o.decode_attention(q.to(dt).to(DEV), kp.to(dt).to(DEV), vp.to(dt).to(DEV), bt.to(DEV),
+                                      torch.zeros(1, dtype=torch.int32, device=DEV),
+                                      torch.tensor([n - 1], dtype=torch.int32, device=DEV), 0, 0, hd ** -0.5, n)
+            close(fast[0], want, tol, f"far key at {far}, decode kernel")
 
 
 @pytest.mark.parametrize("dt,tol", DT)
