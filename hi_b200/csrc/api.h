@@ -10,9 +10,9 @@ extern "C" {
 
 int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int n, int hidden,
                     int vocab, cudaStream_t stream);
-int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w, int w_dtype, void* y,
-                   int y_dtype, float* y_f32, const int* row_map, int rows, int hidden, float eps,
-                   cudaStream_t stream);
+int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed, const int* slot_of_entry,
+                   int top_k, const void* w, int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
+                   int rows, int hidden, float eps, cudaStream_t stream);
 int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream);
 int hb_moe_combine(const float* y, const int* slot_of_entry, const void* shared, int shared_dtype, float* out,
                    int n, int hidden, int top_k, cudaStream_t stream);

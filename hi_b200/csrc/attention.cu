@@ -128,17 +128,31 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        T* __restrict__ out, int hd, int max_splits) {
+  extern __shared__ float wgt[];   // [max_splits] weight of each split, then 33 floats of scratch
+  float* scratch = wgt + max_splits;
   const size_t th = blockIdx.x;
   const float* ml = part_ml + th * max_splits * 2;
   float m = -INFINITY;
-  for (int s = 0; s < max_splits; ++s) m = fmaxf(m, ml[2 * s]);
+  for (int s = threadIdx.x; s < max_splits; s += blockDim.x) m = fmaxf(m, ml[2 * s]);
+  m = hb::block_max(m, scratch);
   float l = 0.f;
-  for (int s = 0; s < max_splits; ++s) l += ml[2 * s] == -INFINITY ? 0.f : ml[2 * s + 1] * expf(ml[2 * s] - m);
+  for (int s = threadIdx.x; s < max_splits; s += blockDim.x) {
+    const float ms = ml[2 * s];
+    const float e = ms == -INFINITY ? 0.f : expf(ms - m);
+    wgt[s] = e;
+    l += ml[2 * s + 1] * e;
+  }
+  l = hb::block_sum(l, scratch);      // fixed tree order: the same inputs give the same sum
   const float inv = l > 0.f ? 1.f / l : 0.f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
-    for (int s = 0; s < max_splits; ++s)
-      if (ml[2 * s] != -INFINITY) o += part_acc[(th * max_splits + s) * hd + d] * expf(ml[2 * s] - m);
+#pragma unroll 8
+    for (int s = 0; s < max_splits; ++s) {
+      // a split beyond the token's range has weight 0 and an unwritten row: it must not be read
+      // into the sum (whatever the scratch holds there, even NaN)
+      const float ws = wgt[s];
+      if (ws != 0.f) o += part_acc[(th * max_splits + s) * hd + d] * ws;
+    }
     out[th * hd + d] = hb::from_f32<T>(o * inv);
   }
 }
@@ -177,10 +191,10 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
   HB_LAUNCH_CHECK();
   if (max_splits > 1) {
     if (dtype == HB_DTYPE_F32)
-      attention_merge_kernel<float><<<n_tokens * nh, 64, 0, stream>>>(part_acc, part_ml, (float*)out, hd, max_splits);
+      attention_merge_kernel<float><<<n_tokens * nh, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits);
     else
-      attention_merge_kernel<__nv_bfloat16><<<n_tokens * nh, 64, 0, stream>>>(part_acc, part_ml,
-                                                                              (__nv_bfloat16*)out, hd, max_splits);
+      attention_merge_kernel<__nv_bfloat16><<<n_tokens * nh, 128, (max_splits + 33) * sizeof(float), stream>>>(
+          part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits);
     HB_LAUNCH_CHECK();
   }
   return HB_OK;
@@ -192,10 +206,10 @@ extern "C" int hb_attention_merge(const float* part_acc, const float* part_ml, v
   if (!part_acc || !part_ml || !out || n_rows < 0 || hd <= 0 || max_splits < 1) return HB_ERR_BAD_ARG;
   if (n_rows == 0) return HB_OK;
   if (dtype == HB_DTYPE_F32)
-    attention_merge_kernel<float><<<n_rows, 64, 0, stream>>>(part_acc, part_ml, (float*)out, hd, max_splits);
+    attention_merge_kernel<float><<<n_rows, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits);
   else if (dtype == HB_DTYPE_BF16)
-    attention_merge_kernel<__nv_bfloat16><<<n_rows, 64, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, hd,
-                                                                     max_splits);
+    attention_merge_kernel<__nv_bfloat16><<<n_rows, 128, (max_splits + 33) * sizeof(float), stream>>>(
+        part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();

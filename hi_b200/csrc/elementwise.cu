@@ -14,12 +14,37 @@ __device__ __forceinline__ void store_any(void* p, int dtype, size_t i, float v)
   else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
 }
 
+__device__ __forceinline__ float4 load4_any(const void* p, int dtype, size_t i) {   // i % 4 == 0
+  if (dtype == HB_DTYPE_F32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+  const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+  return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                     __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4_any(void* p, int dtype, size_t i, float4 v) {
+  if (dtype == HB_DTYPE_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = v;
+  } else {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned*>(&a);
+    raw.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p) + i) = raw;
+  }
+}
+
 // x[t, :] = table[token[t], :]   (crates/hi-mlx/src/models.rs:6206: no multiplier)
 __global__ void embed_gather_kernel(const void* table, int table_dtype, const int* tokens,
                                     float* out, int hidden, int vocab) {
   const int t = blockIdx.x;
   int id = tokens[t];
   const bool ok = id >= 0 && id < vocab;
+  if ((hidden & 3) == 0) {
+#pragma unroll 4
+    for (int j = threadIdx.x * 4; j < hidden; j += blockDim.x * 4)
+      *reinterpret_cast<float4*>(out + (size_t)t * hidden + j) =
+          ok ? load4_any(table, table_dtype, (size_t)id * hidden + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    return;
+  }
   for (int j = threadIdx.x; j < hidden; j += blockDim.x)
     out[(size_t)t * hidden + j] = ok ? load_any(table, table_dtype, (size_t)id * hidden + j) : 0.f;
 }
@@ -27,7 +52,8 @@ __global__ void embed_gather_kernel(const void* table, int table_dtype, const in
 // Row r of the output: src = row_map ? row_map[r] : r.
 //   s = x[src] (+ delta[src]);  if no row_map: x[src] = s  (the residual sum, float32)
 //   y[r] = s * rsqrt(mean(s^2) + eps) * w     (crates/hi-cuda/src/kernels.cu:61-77)
-__global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype, const void* w,
+__global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype, const float* routed,
+                                   const int* slot_of_entry, int top_k, const void* w,
                                    int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
                                    int hidden, float eps) {
   __shared__ float scratch[33];
@@ -38,6 +64,8 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
   for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
     float s = x[src * hidden + j];
     if (delta) s += load_any(delta, delta_dtype, src * hidden + j);
+    if (routed)
+      for (int q = 0; q < top_k; ++q) s += routed[(size_t)slot_of_entry[src * top_k + q] * hidden + j];
     row[j] = s;
     ss += s * s;
   }
@@ -45,10 +73,64 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
   const float inv = rsqrtf(total / (float)hidden + eps);
   for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
     const float s = row[j];
-    if (!row_map && delta) x[src * hidden + j] = s;
+    if (!row_map && (delta || routed)) x[src * hidden + j] = s;
     const float wv = w ? load_any(w, w_dtype, j) : 1.f;
     store_any(y, y_dtype, (size_t)r * hidden + j, s * inv * wv);
     if (y_f32) y_f32[(size_t)r * hidden + j] = s * inv * wv;
+  }
+}
+
+// The same, for hidden % 4 == 0 and hidden <= 4 * blockDim * NG: the row lives in registers, every
+// load is a 16-byte (or 8-byte bfloat16) vector issued before the first use, and the sum that the
+// residual takes may include the routed experts' rows:
+//   s = x[src] + delta[src] + sum_j routed[slot_of_entry[src*top_k + j]]
+// (the combine of crates/hi-cuda/src/kernels.cu:10661-10680, in rank order, fused into the norm).
+template <int NG>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __restrict__ delta, int delta_dtype,
+                                       const float* __restrict__ routed, const int* __restrict__ slot_of_entry,
+                                       int top_k, const void* __restrict__ w, int w_dtype, void* __restrict__ y,
+                                       int y_dtype, float* __restrict__ y_f32, const int* __restrict__ row_map,
+                                       int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const size_t src = row_map ? (size_t)row_map[r] : (size_t)r;
+  float4 v[NG];
+  float ss = 0.f;
+  int slots[8];
+  if (routed)
+    for (int j = 0; j < top_k; ++j) slots[j] = slot_of_entry[src * top_k + j];
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const int idx = (threadIdx.x + g * blockDim.x) * 4;
+    if (idx < hidden) {
+      float4 a = *reinterpret_cast<const float4*>(x + src * hidden + idx);
+      if (delta) {
+        const float4 d = load4_any(delta, delta_dtype, src * hidden + idx);
+        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+      }
+      if (routed) {
+        for (int j = 0; j < top_k; ++j) {
+          const float4 d = *reinterpret_cast<const float4*>(routed + (size_t)slots[j] * hidden + idx);
+          a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+        }
+      }
+      v[g] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+  const float total = hb::block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const int idx = (threadIdx.x + g * blockDim.x) * 4;
+    if (idx < hidden) {
+      const float4 a = v[g];
+      if (!row_map && (delta || routed)) *reinterpret_cast<float4*>(x + src * hidden + idx) = a;
+      const float4 wv = w ? load4_any(w, w_dtype, idx) : make_float4(1.f, 1.f, 1.f, 1.f);
+      const float4 o = make_float4(a.x * inv * wv.x, a.y * inv * wv.y, a.z * inv * wv.z, a.w * inv * wv.w);
+      store4_any(y, y_dtype, (size_t)r * hidden + idx, o);
+      if (y_f32) *reinterpret_cast<float4*>(y_f32 + (size_t)r * hidden + idx) = o;
+    }
   }
 }
 
@@ -92,13 +174,30 @@ extern "C" int hb_embed_gather(const void* table, int table_dtype, const int* to
   return HB_OK;
 }
 
-extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w,
-                              int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map, int rows,
-                              int hidden, float eps, cudaStream_t stream) {
+extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed,
+                              const int* slot_of_entry, int top_k, const void* w, int w_dtype, void* y, int y_dtype,
+                              float* y_f32, const int* row_map, int rows, int hidden, float eps,
+                              cudaStream_t stream) {
   if (!x || !y || rows < 0 || hidden <= 0 || !dtype_ok(y_dtype) || (delta && !dtype_ok(delta_dtype)) ||
       (w && !dtype_ok(w_dtype)))
     return HB_ERR_BAD_ARG;
+  if (routed && (!slot_of_entry || top_k < 1 || top_k > 8)) return HB_ERR_BAD_ARG;
   if (rows == 0) return HB_OK;
+  if (hidden % 4 == 0 && hidden <= 4 * 512 * 8) {
+    const int groups = hidden / 4;
+    const int threads = groups >= 512 ? 512 : ((groups + 31) / 32) * 32;
+    const int ng = (groups + threads - 1) / threads;
+#define HB_NORM_LAUNCH(NG)                                                                                   \
+    add_rmsnorm_vec_kernel<NG><<<rows, threads, 0, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, top_k, \
+                                                             w, w_dtype, y, y_dtype, y_f32, row_map, hidden, eps)
+    if (ng <= 1) HB_NORM_LAUNCH(1);
+    else if (ng <= 2) HB_NORM_LAUNCH(2);
+    else if (ng <= 4) HB_NORM_LAUNCH(4);
+    else HB_NORM_LAUNCH(8);
+#undef HB_NORM_LAUNCH
+    HB_LAUNCH_CHECK();
+    return HB_OK;
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return HB_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
@@ -106,8 +205,8 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = hidden >= 2048 ? 512 : 256;
-  add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, w, w_dtype, y, y_dtype,
-                                                      y_f32, row_map, hidden, eps);
+  add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, top_k, w, w_dtype,
+                                                      y, y_dtype, y_f32, row_map, hidden, eps);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

@@ -27,7 +27,20 @@ __global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restric
     const TW* wr = w + (size_t)e * hidden;
     float s = 0.f;
     if ((hidden & 7) == 0) {   // rows are 16-byte aligned: 8 elements per load
-      for (int j = lane * 8; j < hidden; j += 256) {
+      int j = lane * 8;
+      for (; j + 768 < hidden; j += 1024) {      // four independent pairs of loads in flight
+        float xv[4][8], wv[4][8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          hb::load8(xr + j + 256 * q, xv[q]);
+          hb::load8(wr + j + 256 * q, wv[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s += xv[q][i] * wv[q][i];
+      }
+      for (; j < hidden; j += 256) {
         float xv[8], wv[8];
         hb::load8(xr + j, xv);
         hb::load8(wr + j, wv);

@@ -18,7 +18,7 @@ P, I, F = c_void_p, c_int, c_float
 
 _SIGNATURES = {
     "hb_embed_gather": [P, I, P, P, I, I, I, P],
-    "hb_add_rmsnorm": [P, P, I, P, I, P, I, P, P, I, I, F, P],
+    "hb_add_rmsnorm": [P, P, I, P, P, I, P, I, P, I, P, P, I, I, F, P],
     "hb_swiglu": [P, P, I, I, I, P],
     "hb_moe_combine": [P, P, P, I, P, I, I, I, P],
     "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
@@ -101,8 +101,13 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
-                out_dtype: torch.dtype, row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
+                out_dtype: torch.dtype, row_map: Optional[torch.Tensor] = None, also_f32: bool = False,
+                routed: Optional[torch.Tensor] = None, slot_of_entry: Optional[torch.Tensor] = None,
+                top_k: int = 0):
     """``x += delta`` (float32, in place) then ``rmsnorm(x) * weight`` in ``out_dtype``.
+
+    ``routed`` (float32 [N*k, H], rows in expert-sorted order) with ``slot_of_entry`` adds each
+    token's k routed-expert rows into the same sum: the experts' combine, fused into the norm.
 
     ``also_f32`` returns ``(y, y_float32)``: the same normalised rows unrounded, for a consumer
     that computes in 32-bit (the router).
@@ -128,7 +133,12 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional
     y32 = None
     if also_f32 and out_dtype != torch.float32:
         y32 = torch.empty((rows, hidden), dtype=torch.float32, device=x.device)
-    _check(lib().hb_add_rmsnorm(_ptr(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(weight),
+    if routed is not None:
+        _need(routed, "routed", torch.float32); _need(slot_of_entry, "slot_of_entry", torch.int32)
+        if routed.shape[1] != hidden or not 1 <= top_k <= 8:
+            raise KernelError("routed rows do not match the residual, or top_k is outside 1..8")
+    _check(lib().hb_add_rmsnorm(_ptr(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(routed),
+                                _ptr(slot_of_entry), int(top_k), _ptr(weight),
                                 _dt(weight) if weight is not None else 0, _ptr(y), _dt(y), _ptr(y32), _ptr(row_map),
                                 rows, hidden, float(eps), _stream()), "add_rmsnorm")
     if also_f32:

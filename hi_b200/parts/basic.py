@@ -8,6 +8,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
+from .context import Pending
 from .linear import linear
 from .registry import BuildEnv, build, register
 from .spec import PartSpec, TensorSpec
@@ -55,8 +56,14 @@ class RMSNorm(Part):
     def load(self, fetch):
         self.weight = fetch(f"{self.prefix}.weight").contiguous()
 
-    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
-                row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
+    def forward(self, residual: torch.Tensor, delta, row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
+        """``delta``: None, a tensor, or a :class:`~hi_b200.parts.context.Pending`."""
+        if isinstance(delta, Pending):
+            if delta.top_k > 8:
+                delta = delta.materialize(residual.shape[0])
+            else:
+                return ops.add_rmsnorm(residual, delta.dense, self.weight, self.eps, self.env.dtype, row_map, also_f32,
+                                       delta.routed, delta.slot_of_entry, delta.top_k)
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.env.dtype, row_map, also_f32)
 
 

@@ -45,3 +45,24 @@ class CacheView:
     v_pages: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None         # [max_slots, *state_shape]
     writes: bool = True                          # False: read another entry's cache, do not append
+
+
+@dataclass
+class Pending:
+    """A sub-layer's output that has not yet been added to the residual stream: a dense part
+    (engine dtype or float32, [N, H]) and/or the routed experts' rows (float32 [N*k, H] in
+    expert-sorted order, with the slot of every (token, rank) entry). The next norm adds all of
+    it in one pass."""
+
+    dense: Optional[torch.Tensor] = None
+    routed: Optional[torch.Tensor] = None
+    slot_of_entry: Optional[torch.Tensor] = None
+    top_k: int = 0
+
+    def materialize(self, n_tokens: int) -> torch.Tensor:
+        """The sum as one float32 tensor, for a consumer that is not a norm."""
+        from ..kernels import ops
+
+        if self.routed is None:
+            return self.dense
+        return ops.moe_combine(self.routed, self.slot_of_entry, self.dense, n_tokens, self.top_k)

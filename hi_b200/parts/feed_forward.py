@@ -7,6 +7,7 @@ import torch
 
 from ..kernels import ops
 from .basic import Part
+from .context import Pending
 from .linear import linear
 from .registry import register
 from .spec import TensorSpec
@@ -120,4 +121,5 @@ class SigmoidRoutedExperts(Part):
         act = ops.moe_gate_up(normed, sorted_entry, self.top_k, self.w_gate, self.w_up, offsets, scores, few)
         y = ops.moe_down(act, self.w_down, offsets, few)
         shared = self.shared.forward(normed) if self.shared else None
-        return ops.moe_combine(y, slot_of_entry, shared, n, self.top_k)
+        # the sum shared + routed rows is taken inside the next norm's residual add
+        return Pending(dense=shared, routed=y, slot_of_entry=slot_of_entry, top_k=self.top_k)

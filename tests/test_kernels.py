@@ -32,7 +32,7 @@ def test_embed_and_norm(dt, tol):
     table = torch.randn(331, 120, generator=g).to(dt)
     toks = torch.randint(0, 331, (29,), generator=g, dtype=torch.int32)
     close(o.embed_gather(table.to(DEV), toks.to(DEV)), table.float()[toks.long()], 1e-7, "embed")
-    for hidden in (48, 120, 1000, 5120, 7168):
+    for hidden in (48, 120, 1000, 1001, 5120, 7168, 20000):
         x = torch.randn(11, hidden, generator=g) * 3
         d = torch.randn(11, hidden, generator=g).to(dt)
         w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dt)
@@ -42,6 +42,14 @@ def test_embed_and_norm(dt, tol):
         close(y, want, tol, f"rmsnorm hidden {hidden}")
         close(y32, want, 2e-6, "rmsnorm float32 output")
         close(xg, x + d.float(), 1e-7, "residual sum")
+        # the routed experts' rows join the same sum (top-2 of 5 sorted rows per token)
+        routed = torch.randn(22, hidden, generator=g)
+        slots = torch.randperm(22, generator=g).to(torch.int32)
+        xr = x.clone().to(DEV)
+        yr = o.add_rmsnorm(xr, d.to(DEV), w.to(DEV), 1e-5, dt, None, False, routed.to(DEV), slots.to(DEV), 2)
+        summed = x + d.float() + routed[slots.long()].view(11, 2, hidden).sum(1)
+        close(yr, plain.rms_norm(summed, w, 1e-5), tol, f"rmsnorm with routed rows, hidden {hidden}")
+        close(xr, summed, 1e-6, "residual sum with routed rows")
         rows = torch.tensor([10, 0, 4], dtype=torch.int32)
         before = xg.clone()
         y2 = o.add_rmsnorm(xg, d.to(DEV), w.to(DEV), 1e-5, dt, rows.to(DEV))

@@ -150,7 +150,7 @@ def test_feed_forward_parts(dt, tol):
     w = fill(moe, dt, 4, std=0.2)
     seen = {}
     ctx.tap = lambda name, t: seen.__setitem__(name, t.cpu())
-    got = moe.forward(x.to(DEV), ctx, normed_f32=x.float().to(DEV))
+    got = moe.forward(x.to(DEV), ctx, normed_f32=x.float().to(DEV)).materialize(37)
     cfg = {"num_experts_per_tok": 2}
     want = plain.moe_feed_forward(cfg, w, "e", x.float(), forced_ids=seen["e.router_ids"])
     close(got, want, tol, "experts")
