@@ -310,3 +310,71 @@ extern "C" int hb_attention_decode(const void* q, const void* k_pages, const voi
                              nh, nkv, page_size, chunk, window, scale, split_size, max_splits, part_acc, part_ml, stream);
   return HB_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (see attention_decode_static.h): the same kernel, its
+// split partials kept in a file-scope device array instead of caller-provided scratch.
+#include <stdio.h>
+
+#include "attention_decode_static.h"
+
+namespace {
+
+// [acc: HB_STATIC_SCRATCH_ACC_FLOATS][ml: HB_STATIC_SCRATCH_ML_FLOATS]
+static __device__ __align__(256) float g_static_scratch[HB_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_ptr[kMaxDevices] = {};   // device address of the array, per device
+
+// In host code `g_static_scratch` is only a handle; the address the kernels need comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch(float** acc, float** ml) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return HB_ERR_UNSUPPORTED;
+  if (!g_static_scratch_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!p) return HB_ERR_BAD_ARG;
+    g_static_scratch_ptr[dev] = p;
+  }
+  *acc = g_static_scratch_ptr[dev];
+  *ml = g_static_scratch_ptr[dev] + HB_STATIC_SCRATCH_ACC_FLOATS;
+  return HB_OK;
+}
+
+}  // namespace
+
+extern "C" long long hb_attention_decode_static_need(int n_tokens, int nh, int hd, int max_splits) {
+  if (max_splits <= 1) return 0;
+  return (long long)n_tokens * nh * max_splits * ((long long)hd + 2);
+}
+
+extern "C" int hb_attention_decode_static(const void* q, const void* k_pages, const void* v_pages,
+                                          const int* block_table, int table_stride, const int* seq_of_token,
+                                          const int* positions, void* out, int n_tokens, int nh, int nkv, int hd,
+                                          int page_size, int chunk, int window, float scale, int split_size,
+                                          int max_splits, cudaStream_t stream) {
+  if (n_tokens < 0 || nh <= 0 || hd <= 0 || max_splits < 1) return HB_ERR_BAD_ARG;
+  float *acc = nullptr, *ml = nullptr;
+  if (max_splits > 1) {
+    const long long acc_need = (long long)n_tokens * nh * max_splits * hd;
+    const long long ml_need = (long long)n_tokens * nh * max_splits * 2;
+    if (acc_need > HB_STATIC_SCRATCH_ACC_FLOATS || ml_need > HB_STATIC_SCRATCH_ML_FLOATS) {
+      fprintf(stderr,
+              "hb_attention_decode_static: %d tokens x %d heads x %d splits x head_dim %d need %lld + %lld floats of "
+              "scratch; the built-in array holds %d + %d. Use fewer splits or hb_attention_decode.\n",
+              n_tokens, nh, max_splits, hd, acc_need, ml_need, HB_STATIC_SCRATCH_ACC_FLOATS,
+              HB_STATIC_SCRATCH_ML_FLOATS);
+      return HB_ERR_SCRATCH_CAPACITY;
+    }
+    const int rc = static_scratch(&acc, &ml);
+    if (rc != HB_OK) return rc;
+  }
+  int rc = hb_attention_decode(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
+                               nh, nkv, hd, page_size, chunk, window, scale, split_size, max_splits, acc, ml, stream);
+  if (rc != HB_OK || max_splits == 1 || n_tokens == 0) return rc;
+  return hb_attention_merge(acc, ml, out, HB_DTYPE_BF16, n_tokens * nh, hd, max_splits, stream);
+}
