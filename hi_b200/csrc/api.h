@@ -39,12 +39,12 @@ int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages,
 int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
                    int top_k, float* logits_out, int* ids, float* scores, cudaStream_t stream);
 int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
-                int* slot_of_entry, cudaStream_t stream);
+                int* slot_of_entry, int* active, cudaStream_t stream);
 int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,
-                   const void* w_up, const int* offsets, int experts, const float* scores, void* act,
-                   int n_entries, int inter, int hidden, int few_rows, cudaStream_t stream);
-int hb_moe_down(const void* act, int dtype, const void* w_down, const int* offsets, int experts, float* y,
-                int n_entries, int hidden, int inter, int few_rows, cudaStream_t stream);
+                   const void* w_up, const int* offsets, const int* active, int experts, const float* scores,
+                   void* act, int n_entries, int inter, int hidden, int few_rows, cudaStream_t stream);
+int hb_moe_down(const void* act, int dtype, const void* w_down, const int* offsets, const int* active, int experts,
+                float* y, int n_entries, int hidden, int inter, int few_rows, cudaStream_t stream);
 
 int hb_sample_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* uniforms,
                    int* out, cudaStream_t stream);

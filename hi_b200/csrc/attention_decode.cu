@@ -63,8 +63,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);             // [ROWS][STRIDE]
   __nv_bfloat16* k_s = q_s + ROWS * STRIDE;                                     // [2][TILE][STRIDE]
   __nv_bfloat16* v_s = k_s + 2 * TILE * STRIDE;                                 // [2][TILE][STRIDE]
-  float* o_s = reinterpret_cast<float*>(v_s + 2 * TILE * STRIDE);               // [ROWS][HD]
-  float* ml_s = o_s + ROWS * HD;                                                // [NWARPS][ROWS][2]
+  float* ml_s = reinterpret_cast<float*>(v_s + 2 * TILE * STRIDE);              // [NWARPS][ROWS][2]
+  float* o_s = reinterpret_cast<float*>(k_s);   // [ROWS][HD], reuses the K tiles once the key loop is over
 
   const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -92,20 +92,41 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const bool ok = r < G;
     cp_async16(q_s + r * STRIDE + ch * 8, q + (th0 + (ok ? r : 0)) * HD + ch * 8, ok);
   }
+  // thread -> one 16-byte chunk column and every (128 / CHUNKS)-th row of a tile. When a tile
+  // never straddles a page (page_size a multiple of TILE and the range starts on a TILE
+  // boundary) one table lookup serves the whole tile.
+  constexpr int ROWS_PER_PASS = NWARPS * 32 / CHUNKS;
+  const int ld_ch = tid % CHUNKS, ld_r0 = tid / CHUNKS;
+  const bool tile_in_page = (page_size % TILE == 0) && (first % TILE == 0);
   auto load_tile = [&](int tile, int buf) {
     const int base = first + tile * TILE;
-    for (int c = tid; c < TILE * CHUNKS; c += NWARPS * 32) {
-      const int r = c / CHUNKS, ch = c % CHUNKS;
-      const int key = base + r;
-      bool ok = key <= last;
-      size_t off = 0;
-      if (ok) {
-        const int page = table[key / page_size];
-        ok = page >= 0;
-        off = (((size_t)(ok ? page : 0) * nkv + kvh) * page_size + (key % page_size)) * HD + ch * 8;
+    __nv_bfloat16* kd = k_s + (buf * TILE + ld_r0) * STRIDE + ld_ch * 8;
+    __nv_bfloat16* vd = v_s + (buf * TILE + ld_r0) * STRIDE + ld_ch * 8;
+    if (tile_in_page) {
+      const int page = table[base / page_size];
+      const size_t off0 = (((size_t)(page >= 0 ? page : 0) * nkv + kvh) * page_size + (base % page_size) + ld_r0) * HD + ld_ch * 8;
+      const __nv_bfloat16* ks = k_pages + off0;
+      const __nv_bfloat16* vs = v_pages + off0;
+#pragma unroll
+      for (int i = 0; i < TILE / ROWS_PER_PASS; ++i) {
+        const bool ok = page >= 0 && base + ld_r0 + i * ROWS_PER_PASS <= last;
+        cp_async16(kd + i * ROWS_PER_PASS * STRIDE, ks + (size_t)i * ROWS_PER_PASS * HD, ok);
+        cp_async16(vd + i * ROWS_PER_PASS * STRIDE, vs + (size_t)i * ROWS_PER_PASS * HD, ok);
       }
-      cp_async16(k_s + (buf * TILE + r) * STRIDE + ch * 8, k_pages + off, ok);
-      cp_async16(v_s + (buf * TILE + r) * STRIDE + ch * 8, v_pages + off, ok);
+    } else {
+#pragma unroll
+      for (int i = 0; i < TILE / ROWS_PER_PASS; ++i) {
+        const int key = base + ld_r0 + i * ROWS_PER_PASS;
+        bool ok = key <= last;
+        size_t off = 0;
+        if (ok) {
+          const int page = table[key / page_size];
+          ok = page >= 0;
+          off = (((size_t)(ok ? page : 0) * nkv + kvh) * page_size + (key % page_size)) * HD + ld_ch * 8;
+        }
+        cp_async16(kd + i * ROWS_PER_PASS * STRIDE, k_pages + off, ok);
+        cp_async16(vd + i * ROWS_PER_PASS * STRIDE, v_pages + off, ok);
+      }
     }
   };
   load_tile(0, 0);
@@ -164,7 +185,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m_run[r], mx);
-      corr[r] = (m_run[r] == -INFINITY) ? 0.f : expf(m_run[r] - m_new);
+      corr[r] = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - m_new);
       m_run[r] = m_new;
     }
     float row_sum[2] = {0.f, 0.f};
@@ -176,7 +197,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int r = e >> 1;
-          const float v = (s_acc[nt][e] == -INFINITY) ? 0.f : expf(s_acc[nt][e] - m_run[r]);
+          const float v = (s_acc[nt][e] == -INFINITY) ? 0.f : __expf(s_acc[nt][e] - m_run[r]);
           p[nt][e] = v;
           row_sum[r] += v;
         }
@@ -192,10 +213,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
       l_run[r] = l_run[r] * corr[r] + sum;
     }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // the running max rarely moves
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) {
-      o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0];
-      o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
+      for (int j = 0; j < HD / 8; ++j) {
+        o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0];
+        o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
+      }
     }
     // O += P V : V rows are keys (k), columns dims (n): transposed 8x8 loads give the B fragments
 #pragma unroll
@@ -273,7 +296,8 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
                   float* part_ml, cudaStream_t stream) {
   constexpr int STRIDE = HD + 8;
   const size_t smem = (size_t)(ROWS * STRIDE + 4 * TILE * STRIDE) * sizeof(__nv_bfloat16) +
-                      (size_t)(ROWS * HD + NWARPS * ROWS * 2) * sizeof(float);
+                      (size_t)(NWARPS * ROWS * 2) * sizeof(float);
+  static_assert(2 * TILE * STRIDE * sizeof(__nv_bfloat16) >= ROWS * HD * sizeof(float), "o_s aliases the K tiles");
   cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(max_splits, nkv, n_tokens);

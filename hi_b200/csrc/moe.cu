@@ -77,8 +77,10 @@ __global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restric
 // ------------------------------------------------------------------ plan
 // Stable counting sort of the n = tokens*top_k routing entries by expert, in one block:
 // offsets[e]..offsets[e+1] are the sorted slots of expert e, in entry order.
+// active[0] = number of experts with at least one row, active[1..] = their ids in order.
 __global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int experts, int* __restrict__ offsets,
-                                int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry) {
+                                int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry,
+                                int* __restrict__ active) {
   extern __shared__ int sm[];  // cnt[experts], base[experts]
   int* cnt = sm;
   int* base = sm + experts;
@@ -90,13 +92,15 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int experts,
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int run = 0;
+    int run = 0, n_active = 0;
     for (int e = 0; e < experts; ++e) {
       offsets[e] = run;
       base[e] = run;
       run += cnt[e];
+      if (cnt[e] > 0) active[1 + n_active++] = e;
     }
     offsets[experts] = run;
+    active[0] = n_active;
   }
   __syncthreads();
   if (threadIdx.x < 32) {
@@ -304,8 +308,11 @@ template <typename T, bool DUAL>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 grouped_gemv_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry, int top_k,
                     const T* __restrict__ W0, const T* __restrict__ W1, const int* __restrict__ offsets,
-                    const float* __restrict__ scores, void* __restrict__ out, int n_out, int K) {
-  const int e = blockIdx.y;
+                    const int* __restrict__ active, const float* __restrict__ scores, void* __restrict__ out,
+                    int n_out, int K) {
+  // blockIdx.y counts the experts that have rows; the grid has min(experts, entries) of them
+  if ((int)blockIdx.y >= active[0]) return;
+  const int e = active[1 + blockIdx.y];
   const int begin = offsets[e], end = offsets[e + 1];
   if (begin == end) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -331,16 +338,16 @@ grouped_gemv_kernel(const T* __restrict__ A, int lda, const int* __restrict__ so
 
 template <typename T>
 int launch_grouped(bool dual, const void* A, int lda, const int* sorted_entry, int top_k, const void* W0,
-                   const void* W1, const int* offsets, int experts, const float* scores, void* out, int n_entries,
-                   int n_out, int K, int few_rows, cudaStream_t stream) {
+                   const void* W1, const int* offsets, const int* active, int experts, const float* scores, void* out,
+                   int n_entries, int n_out, int K, int few_rows, cudaStream_t stream) {
   if (few_rows && K % 8 == 0 && lda % 8 == 0) {
-    dim3 grid((n_out + GEMV_WARPS - 1) / GEMV_WARPS, experts);
+    dim3 grid((n_out + GEMV_WARPS - 1) / GEMV_WARPS, experts < n_entries ? experts : n_entries);
     if (dual)
       grouped_gemv_kernel<T, true><<<grid, GEMV_WARPS * 32, 0, stream>>>(
-          (const T*)A, lda, sorted_entry, top_k, (const T*)W0, (const T*)W1, offsets, scores, out, n_out, K);
+          (const T*)A, lda, sorted_entry, top_k, (const T*)W0, (const T*)W1, offsets, active, scores, out, n_out, K);
     else
       grouped_gemv_kernel<T, false><<<grid, GEMV_WARPS * 32, 0, stream>>>(
-          (const T*)A, lda, sorted_entry, top_k, (const T*)W0, nullptr, offsets, scores, out, n_out, K);
+          (const T*)A, lda, sorted_entry, top_k, (const T*)W0, nullptr, offsets, active, scores, out, n_out, K);
   } else {
     const int max_tiles = (n_entries + BM - 1) / BM + (experts < n_entries ? experts : n_entries);
     dim3 grid((n_out + BN - 1) / BN, max_tiles);
@@ -383,43 +390,46 @@ extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_d
 }
 
 extern "C" int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
-                           int* slot_of_entry, cudaStream_t stream) {
-  if (!ids || !offsets || !sorted_entry || !slot_of_entry || n_entries < 0 || experts <= 0) return HB_ERR_BAD_ARG;
+                           int* slot_of_entry, int* active, cudaStream_t stream) {
+  if (!ids || !offsets || !sorted_entry || !slot_of_entry || !active || n_entries < 0 || experts <= 0)
+    return HB_ERR_BAD_ARG;
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
   moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, n_entries, experts, offsets,
-                                                                          sorted_entry, slot_of_entry);
+                                                                          sorted_entry, slot_of_entry, active);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
 
 // gate/up with SwiGLU: act[slot, :] (engine dtype, [n_entries, inter]).
 extern "C" int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,
-                              const void* w_up, const int* offsets, int experts, const float* scores, void* act,
-                              int n_entries, int inter, int hidden, int few_rows, cudaStream_t stream) {
-  if (!x || !sorted_entry || !w_gate || !w_up || !offsets || !scores || !act || n_entries < 0 || inter <= 0 ||
+                              const void* w_up, const int* offsets, const int* active, int experts,
+                              const float* scores, void* act, int n_entries, int inter, int hidden, int few_rows,
+                              cudaStream_t stream) {
+  if (!x || !sorted_entry || !w_gate || !w_up || !offsets || !active || !scores || !act || n_entries < 0 || inter <= 0 ||
       hidden <= 0 || experts <= 0 || top_k <= 0)
     return HB_ERR_BAD_ARG;
   if (n_entries == 0) return HB_OK;
   if (dtype == HB_DTYPE_F32)
-    return launch_grouped<float>(true, x, hidden, sorted_entry, top_k, w_gate, w_up, offsets, experts, scores, act,
+    return launch_grouped<float>(true, x, hidden, sorted_entry, top_k, w_gate, w_up, offsets, active, experts, scores, act,
                                  n_entries, inter, hidden, few_rows, stream);
   if (dtype == HB_DTYPE_BF16)
-    return launch_grouped<__nv_bfloat16>(true, x, hidden, sorted_entry, top_k, w_gate, w_up, offsets, experts, scores,
+    return launch_grouped<__nv_bfloat16>(true, x, hidden, sorted_entry, top_k, w_gate, w_up, offsets, active, experts, scores,
                                          act, n_entries, inter, hidden, few_rows, stream);
   return HB_ERR_BAD_ARG;
 }
 
 // down projection: y[slot, :] float32 [n_entries, hidden].
-extern "C" int hb_moe_down(const void* act, int dtype, const void* w_down, const int* offsets, int experts, float* y,
-                           int n_entries, int hidden, int inter, int few_rows, cudaStream_t stream) {
-  if (!act || !w_down || !offsets || !y || n_entries < 0 || inter <= 0 || hidden <= 0 || experts <= 0)
+extern "C" int hb_moe_down(const void* act, int dtype, const void* w_down, const int* offsets, const int* active,
+                           int experts, float* y, int n_entries, int hidden, int inter, int few_rows,
+                           cudaStream_t stream) {
+  if (!act || !w_down || !offsets || !active || !y || n_entries < 0 || inter <= 0 || hidden <= 0 || experts <= 0)
     return HB_ERR_BAD_ARG;
   if (n_entries == 0) return HB_OK;
   if (dtype == HB_DTYPE_F32)
-    return launch_grouped<float>(false, act, inter, nullptr, 1, w_down, nullptr, offsets, experts, nullptr, y,
+    return launch_grouped<float>(false, act, inter, nullptr, 1, w_down, nullptr, offsets, active, experts, nullptr, y,
                                  n_entries, hidden, inter, few_rows, stream);
   if (dtype == HB_DTYPE_BF16)
-    return launch_grouped<__nv_bfloat16>(false, act, inter, nullptr, 1, w_down, nullptr, offsets, experts, nullptr, y,
+    return launch_grouped<__nv_bfloat16>(false, act, inter, nullptr, 1, w_down, nullptr, offsets, active, experts, nullptr, y,
                                          n_entries, hidden, inter, few_rows, stream);
   return HB_ERR_BAD_ARG;
 }

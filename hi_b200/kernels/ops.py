@@ -26,9 +26,9 @@ _SIGNATURES = {
     "hb_attention_merge": [P, P, P, I, I, I, I, P],
     "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
-    "hb_moe_plan": [P, I, I, P, P, P, P],
-    "hb_moe_gate_up": [P, I, P, I, P, P, P, I, P, P, I, I, I, I, P],
-    "hb_moe_down": [P, I, P, P, I, P, I, I, I, I, P],
+    "hb_moe_plan": [P, I, I, P, P, P, P, P],
+    "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, P],
+    "hb_moe_down": [P, I, P, P, P, I, P, I, I, I, I, P],
     "hb_sample_rows": [P, I, I, P, P, P, P],
 }
 
@@ -211,7 +211,7 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
 
 
 ATTENTION_SPLIT = 256      # keys per split of the general attention kernel
-DECODE_TARGET_CTAS = 148 * 4   # the decode kernel's grid aims at a few blocks per SM
+DECODE_RESIDENT_BLOCKS = 148 * 3   # blocks of the decode kernel resident at a time
 
 
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
@@ -252,6 +252,21 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     return out
 
 
+def _decode_splits(longest: int, groups: int) -> Tuple[int, int]:
+    """How to cut ``longest`` keys for ``groups`` (token, kv head) pairs: the number of splits
+    that minimises waves x (tiles per block + a block's fixed cost) on 148 SMs x 3 resident
+    blocks, none shorter than ATTENTION_SPLIT keys. The cut moves results by rounding only."""
+    best = (None, 1, longest)
+    for s in range(1, max(1, -(-longest // ATTENTION_SPLIT)) + 1):
+        size = -(-(-(-longest // s)) // 64) * 64
+        real = -(-longest // size)
+        waves = -(-(real * groups) // DECODE_RESIDENT_BLOCKS)
+        cost = waves * (size // 64 + 1.5)
+        if best[0] is None or cost < best[0]:
+            best = (cost, real, size)
+    return best[2], best[1]
+
+
 def decode_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int) -> bool:
     """Shapes the tensor-core decode kernel takes; anything else goes to the general kernel."""
     return q_dtype == torch.bfloat16 and hd in (64, 128) and nh % nkv == 0 and nh // nkv <= 16
@@ -277,12 +292,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         longest = min(longest, chunk)
     if window > 0:
         longest = min(longest, window)
-    # enough splits to fill the GPU a few times over, none shorter than ATTENTION_SPLIT keys;
-    # the cut moves results by rounding only
-    wanted = -(-DECODE_TARGET_CTAS // max(1, n * nkv))
-    splits = max(1, min(wanted, -(-longest // ATTENTION_SPLIT)))
-    split_size = -(-(-(-longest // splits)) // 64) * 64
-    splits = max(1, -(-longest // split_size))
+    split_size, splits = _decode_splits(longest, n * nkv)
     out = torch.empty_like(q)
     part_acc = part_ml = None
     if splits > 1:
@@ -314,21 +324,35 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool 
     return ids, scores, logits
 
 
-def moe_plan(ids: torch.Tensor, experts: int):
-    """Group the routing entries by expert: (offsets [E+1], sorted_entry [n], slot_of_entry [n])."""
+class MoePlan:
+    """Rows grouped by expert: ``offsets`` [E+1], ``sorted_entry`` [n] (entry of each sorted slot),
+    ``slot_of_entry`` [n], ``active`` [E+1] (count, then the ids of the experts that have rows)."""
+
+    __slots__ = ("offsets", "sorted_entry", "slot_of_entry", "active")
+
+    def __init__(self, offsets, sorted_entry, slot_of_entry, active):
+        self.offsets, self.sorted_entry, self.slot_of_entry, self.active = offsets, sorted_entry, slot_of_entry, active
+
+    def __iter__(self):       # (offsets, sorted_entry, slot_of_entry) for callers that unpack
+        return iter((self.offsets, self.sorted_entry, self.slot_of_entry))
+
+
+def moe_plan(ids: torch.Tensor, experts: int) -> MoePlan:
+    """Group the routing entries by expert, on the device."""
     _need(ids, "ids", torch.int32)
     n = ids.numel()
     dev = ids.device
     offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
     sorted_entry = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
     slot_of_entry = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    active = torch.empty(experts + 1, dtype=torch.int32, device=dev)
     _check(lib().hb_moe_plan(_ptr(ids), n, experts, _ptr(offsets), _ptr(sorted_entry), _ptr(slot_of_entry),
-                             _stream()), "moe_plan")
-    return offsets, sorted_entry, slot_of_entry
+                             _ptr(active), _stream()), "moe_plan")
+    return MoePlan(offsets, sorted_entry, slot_of_entry, active)
 
 
-def moe_gate_up(x: torch.Tensor, sorted_entry: torch.Tensor, top_k: int, w_gate: torch.Tensor,
-                w_up: torch.Tensor, offsets: torch.Tensor, scores: torch.Tensor, few_rows: bool) -> torch.Tensor:
+def moe_gate_up(x: torch.Tensor, plan: MoePlan, top_k: int, w_gate: torch.Tensor,
+                w_up: torch.Tensor, scores: torch.Tensor, few_rows: bool) -> torch.Tensor:
     """act[slot] = silu(s * x Wg[e]^T) * (s * x Wu[e]^T), [N*k, I] in the engine dtype."""
     _need(x, "x"); _need(w_gate, "w_gate", x.dtype); _need(w_up, "w_up", x.dtype)
     _need(scores, "scores", torch.float32)
@@ -338,13 +362,13 @@ def moe_gate_up(x: torch.Tensor, sorted_entry: torch.Tensor, top_k: int, w_gate:
         raise KernelError("expert gate/up weights do not match the hidden size")
     n_entries = n * top_k
     act = torch.empty((n_entries, inter), dtype=x.dtype, device=x.device)
-    _check(lib().hb_moe_gate_up(_ptr(x), _dt(x), _ptr(sorted_entry), top_k, _ptr(w_gate), _ptr(w_up), _ptr(offsets),
-                                experts, _ptr(scores), _ptr(act), n_entries, inter, hidden, int(few_rows), _stream()),
-           "moe_gate_up")
+    _check(lib().hb_moe_gate_up(_ptr(x), _dt(x), _ptr(plan.sorted_entry), top_k, _ptr(w_gate), _ptr(w_up),
+                                _ptr(plan.offsets), _ptr(plan.active), experts, _ptr(scores), _ptr(act), n_entries,
+                                inter, hidden, int(few_rows), _stream()), "moe_gate_up")
     return act
 
 
-def moe_down(act: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, few_rows: bool) -> torch.Tensor:
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan, few_rows: bool) -> torch.Tensor:
     """y[slot] = act[slot] Wd[e]^T, float32 [N*k, H]."""
     _need(act, "act"); _need(w_down, "w_down", act.dtype)
     n_entries, inter = act.shape
@@ -352,8 +376,8 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, few
     if i2 != inter:
         raise KernelError("expert down weights do not match the intermediate size")
     y = torch.empty((n_entries, hidden), dtype=torch.float32, device=act.device)
-    _check(lib().hb_moe_down(_ptr(act), _dt(act), _ptr(w_down), _ptr(offsets), experts, _ptr(y), n_entries, hidden,
-                             inter, int(few_rows), _stream()), "moe_down")
+    _check(lib().hb_moe_down(_ptr(act), _dt(act), _ptr(w_down), _ptr(plan.offsets), _ptr(plan.active), experts,
+                             _ptr(y), n_entries, hidden, inter, int(few_rows), _stream()), "moe_down")
     return y
 
 

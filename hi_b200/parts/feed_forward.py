@@ -116,10 +116,10 @@ class SigmoidRoutedExperts(Part):
         ids, scores, _ = ops.router_topk(normed if normed_f32 is None else normed_f32, self.w_router, self.top_k)
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.router_ids", ids)
-        offsets, sorted_entry, slot_of_entry = ops.moe_plan(ids, self.experts)
+        plan = ops.moe_plan(ids, self.experts)
         few = n * self.top_k <= self.FEW_ROWS
-        act = ops.moe_gate_up(normed, sorted_entry, self.top_k, self.w_gate, self.w_up, offsets, scores, few)
-        y = ops.moe_down(act, self.w_down, offsets, few)
+        act = ops.moe_gate_up(normed, plan, self.top_k, self.w_gate, self.w_up, scores, few)
+        y = ops.moe_down(act, self.w_down, plan, few)
         shared = self.shared.forward(normed) if self.shared else None
         # the sum shared + routed rows is taken inside the next norm's residual add
-        return Pending(dense=shared, routed=y, slot_of_entry=slot_of_entry, top_k=self.top_k)
+        return Pending(dense=shared, routed=y, slot_of_entry=plan.slot_of_entry, top_k=self.top_k)

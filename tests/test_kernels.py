@@ -260,6 +260,10 @@ def test_window_edges(dt, tol):
         assert hit == visible, f"chunk {chunk} window {window}: key {key} should be {'seen' if visible else 'masked'}"
 
 
+def counts_of(ids, experts):
+    return torch.bincount(ids.cpu().view(-1).long(), minlength=experts).tolist()
+
+
 @pytest.mark.parametrize("dt,tol", DT)
 @pytest.mark.parametrize("shape", [(64, 4, 1, 128, 50), (192, 8, 2, 96, 33), (120, 5, 3, 72, 300), (120, 5, 5, 72, 1),
                                    (256, 16, 1, 512, 8), (200, 128, 1, 64, 64), (104, 3, 2, 40, 700), (100, 4, 2, 36, 20)])
@@ -279,7 +283,10 @@ def test_router_plan_and_experts(shape, dt, tol):
     ref_ids, ref_scores = plain.router_top_k(logits.cpu(), k)
     assert torch.equal(ids.cpu().long(), ref_ids), "top-k choice or its order differs"
     close(scores, ref_scores, 1e-6, "sigmoid scores")
-    offsets, sorted_entry, slot_of_entry = o.moe_plan(ids, E)
+    plan = o.moe_plan(ids, E)
+    offsets, sorted_entry, slot_of_entry = plan
+    live = [e for e in range(E) if counts_of(ids, E)[e] > 0]
+    assert plan.active.cpu().tolist()[: 1 + len(live)] == [len(live)] + live
     flat = ids.cpu().view(-1).long()
     order = torch.sort(flat, stable=True).indices
     counts = torch.bincount(flat, minlength=E)
@@ -294,10 +301,10 @@ def test_router_plan_and_experts(shape, dt, tol):
     up = torch.einsum("rh,rih->ri", x.float()[token_of_slot], wu.float()[expert_of_slot]) * s[:, None]
     act_ref = gate * torch.sigmoid(gate) * up
     for few in (True, False):
-        act = o.moe_gate_up(x.to(DEV), sorted_entry, k, wg.to(DEV), wu.to(DEV), offsets, scores, few)
+        act = o.moe_gate_up(x.to(DEV), plan, k, wg.to(DEV), wu.to(DEV), scores, few)
         close(act, act_ref, tol, f"gate/up few={few}")
         a = act_ref.to(dt)
-        y = o.moe_down(a.to(DEV), wd.to(DEV), offsets, few)
+        y = o.moe_down(a.to(DEV), wd.to(DEV), plan, few)
         y_ref = torch.einsum("ri,rhi->rh", a.float(), wd.float()[expert_of_slot])
         close(y, y_ref, 1e-5 if dt == torch.float32 else 1e-5, f"down few={few}")
     shared = torch.randn(n, H, generator=g).to(dt)
