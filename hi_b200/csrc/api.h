@@ -46,6 +46,14 @@ int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k,
 int hb_moe_down(const void* act, int dtype, const void* w_down, const int* offsets, const int* active, int experts,
                 float* y, int n_entries, int hidden, int inter, int few_rows, cudaStream_t stream);
 
+int hb_gather_rows(const void* x, const int* sorted_entry, int top_k, void* xs, int rows, int hidden,
+                   cudaStream_t stream);
+int hb_moe_gate_up_tc(const void* xs, const int* sorted_entry, const void* w_gate, const void* w_up,
+                      const int* offsets, int experts, const float* scores, void* act, int rows, int inter,
+                      int hidden, int* status, cudaStream_t stream);
+int hb_moe_down_tc(const void* act, const void* w_down, const int* offsets, int experts, float* y, int rows,
+                   int hidden, int inter, int* status, cudaStream_t stream);
+
 int hb_sample_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* uniforms,
                    int* out, cudaStream_t stream);
 

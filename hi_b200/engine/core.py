@@ -42,6 +42,14 @@ def _require_cuda(device) -> None:
     configure_matmul_precision()
 
 
+def _check_kernel_status() -> None:
+    """A tensor-core kernel that gave up a bounded wait makes the step fail loudly."""
+    from ..kernels import ops
+
+    if ops.TC_USED[0]:
+        ops.check_tc_status()
+
+
 def _count_launches(n: int) -> None:
     from ..kernels import ops
 
@@ -195,6 +203,7 @@ class Engine:
             ctx, logit_rows = self._build_context(entries)
             ctx.tap = tap
             logits = self.model.forward(ctx, self.cache.views, logit_rows)
+            _check_kernel_status()
         for e in entries:
             returned = self.manager.commit(e.request_id, len(e.tokens))
             if self.debug_poison and returned:

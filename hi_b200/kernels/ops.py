@@ -29,6 +29,9 @@ _SIGNATURES = {
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
     "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, P],
     "hb_moe_down": [P, I, P, P, P, I, P, I, I, I, I, P],
+    "hb_gather_rows": [P, P, I, P, I, I, P],
+    "hb_moe_gate_up_tc": [P, P, P, P, P, I, P, P, I, I, I, P, P],
+    "hb_moe_down_tc": [P, P, P, I, P, I, I, I, P, P],
     "hb_sample_rows": [P, I, I, P, P, P, P],
 }
 
@@ -378,6 +381,76 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan, few_rows: b
     y = torch.empty((n_entries, hidden), dtype=torch.float32, device=act.device)
     _check(lib().hb_moe_down(_ptr(act), _dt(act), _ptr(w_down), _ptr(plan.offsets), _ptr(plan.active), experts,
                              _ptr(y), n_entries, hidden, inter, int(few_rows), _stream()), "moe_down")
+    return y
+
+
+# --------------------------------------------------------------------------- experts on tcgen05
+_TC_STATUS = {}          # device -> int32[1]: nonzero after a tensor-core kernel gave up a bounded wait
+TC_USED = [False]
+
+
+def _tc_status(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index)
+    if key not in _TC_STATUS:
+        _TC_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _TC_STATUS[key]
+
+
+def check_tc_status(device=None) -> None:
+    """Raise if a tcgen05 kernel timed out on one of its barriers since the last check
+    (synchronises; skipped while a stream is being captured)."""
+    TC_USED[0] = False
+    if torch.cuda.is_current_stream_capturing():
+        return
+    for key, st in _TC_STATUS.items():
+        code = int(st.item())
+        if code != 0:
+            st.zero_()
+            where = {1: "the TMA producer waiting for a free stage", 2: "the MMA issuer waiting for a loaded stage",
+                     3: "the epilogue waiting for the accumulator"}.get(code, f"code {code}")
+            raise KernelError(f"tcgen05 grouped product gave up a bounded wait: {where}; its output is invalid")
+
+
+def moe_tc_supported(x: torch.Tensor, w_gate: torch.Tensor) -> bool:
+    """The tensor-core expert kernels take bfloat16 with hidden and intermediate sizes that are
+    multiples of 8 (TMA needs 16-byte row strides)."""
+    return x.dtype == torch.bfloat16 and w_gate.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and \
+        w_gate.shape[1] % 8 == 0
+
+
+def moe_gate_up_tc(x: torch.Tensor, plan: MoePlan, top_k: int, w_gate: torch.Tensor, w_up: torch.Tensor,
+                   scores: torch.Tensor) -> torch.Tensor:
+    """As :func:`moe_gate_up`, on tcgen05: gathers the rows into expert order, then one grouped
+    product with the SwiGLU epilogue."""
+    _need(x, "x", torch.bfloat16); _need(w_gate, "w_gate", torch.bfloat16); _need(w_up, "w_up", torch.bfloat16)
+    _need(scores, "scores", torch.float32)
+    n, hidden = x.shape
+    experts, inter, h2 = w_gate.shape
+    if h2 != hidden or w_up.shape != w_gate.shape:
+        raise KernelError("expert gate/up weights do not match the hidden size")
+    rows = n * top_k
+    xs = torch.empty((rows, hidden), dtype=x.dtype, device=x.device)
+    _check(lib().hb_gather_rows(_ptr(x), _ptr(plan.sorted_entry), top_k, _ptr(xs), rows, hidden, _stream()),
+           "gather_rows")
+    act = torch.empty((rows, inter), dtype=x.dtype, device=x.device)
+    _check(lib().hb_moe_gate_up_tc(_ptr(xs), _ptr(plan.sorted_entry), _ptr(w_gate), _ptr(w_up), _ptr(plan.offsets),
+                                   experts, _ptr(scores), _ptr(act), rows, inter, hidden, _ptr(_tc_status(x.device)),
+                                   _stream()), "moe_gate_up_tc")
+    TC_USED[0] = True
+    return act
+
+
+def moe_down_tc(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan) -> torch.Tensor:
+    """As :func:`moe_down`, on tcgen05."""
+    _need(act, "act", torch.bfloat16); _need(w_down, "w_down", torch.bfloat16)
+    rows, inter = act.shape
+    experts, hidden, i2 = w_down.shape
+    if i2 != inter:
+        raise KernelError("expert down weights do not match the intermediate size")
+    y = torch.empty((rows, hidden), dtype=torch.float32, device=act.device)
+    _check(lib().hb_moe_down_tc(_ptr(act), _ptr(w_down), _ptr(plan.offsets), experts, _ptr(y), rows, hidden, inter,
+                                _ptr(_tc_status(act.device)), _stream()), "moe_down_tc")
+    TC_USED[0] = True
     return y
 
 

@@ -118,8 +118,13 @@ class SigmoidRoutedExperts(Part):
             ctx.tap(f"{self.prefix}.router_ids", ids)
         plan = ops.moe_plan(ids, self.experts)
         few = n * self.top_k <= self.FEW_ROWS
-        act = ops.moe_gate_up(normed, plan, self.top_k, self.w_gate, self.w_up, scores, few)
-        y = ops.moe_down(act, self.w_down, plan, few)
+        if not few and ops.moe_tc_supported(normed, self.w_gate):
+            # many rows per expert: the grouped products run on tcgen05
+            act = ops.moe_gate_up_tc(normed, plan, self.top_k, self.w_gate, self.w_up, scores)
+            y = ops.moe_down_tc(act, self.w_down, plan)
+        else:
+            act = ops.moe_gate_up(normed, plan, self.top_k, self.w_gate, self.w_up, scores, few)
+            y = ops.moe_down(act, self.w_down, plan, few)
         shared = self.shared.forward(normed) if self.shared else None
         # the sum shared + routed rows is taken inside the next norm's residual add
         return Pending(dense=shared, routed=y, slot_of_entry=plan.slot_of_entry, top_k=self.top_k)

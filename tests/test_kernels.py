@@ -313,6 +313,45 @@ def test_router_plan_and_experts(shape, dt, tol):
     close(out, want, 1e-5, "combine")
 
 
+@pytest.mark.parametrize("shape", [(256, 4, 1, 128, 300), (5120, 16, 1, 512, 2048), (192, 8, 2, 96, 700), (136, 3, 2, 72, 50),
+                                   (1024, 5, 1, 1032, 1000), (64, 2, 1, 64, 129)])
+def test_expert_products_on_tcgen05(shape):
+    """The tcgen05 grouped products (TMA + tensor memory) against float32 references: row counts
+    per expert above and below a tile, widths that are no multiple of the tile, K tails."""
+    o = ops()
+    H, E, k, I, n = shape
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(H + n)
+    x = torch.randn(n, H, generator=g).to(dt)
+    wg, wu = ((torch.randn(E, I, H, generator=g) * 0.1).to(dt) for _ in range(2))
+    wd = (torch.randn(E, H, I, generator=g) * 0.1).to(dt)
+    logits = torch.randn(n, E, generator=g)
+    logits[:, 0] += 1.5                                        # uneven load: expert 0 gets most rows
+    ids, ref_scores = plain.router_top_k(logits, k)
+    ids_d = ids.to(torch.int32).to(DEV)
+    scores = ref_scores.float().to(DEV).contiguous()
+    plan = o.moe_plan(ids_d, E)
+    assert o.moe_tc_supported(x.to(DEV), wg.to(DEV))
+    flat = ids.view(-1)
+    order = torch.sort(flat, stable=True).indices
+    expert_of_slot, token_of_slot = flat[order], order // k
+    s = ref_scores.reshape(-1)[order].float()
+    gate = torch.einsum("rh,rih->ri", x.float()[token_of_slot], wg.float()[expert_of_slot]) * s[:, None]
+    up = torch.einsum("rh,rih->ri", x.float()[token_of_slot], wu.float()[expert_of_slot]) * s[:, None]
+    act_ref = gate * torch.sigmoid(gate) * up
+    act = o.moe_gate_up_tc(x.to(DEV), plan, k, wg.to(DEV), wu.to(DEV), scores)
+    o.check_tc_status()
+    close(act, act_ref, 2e-2, f"tcgen05 gate/up {shape}")
+    a = act_ref.to(dt)
+    y = o.moe_down_tc(a.to(DEV), wd.to(DEV), plan)
+    o.check_tc_status()
+    y_ref = torch.einsum("ri,rhi->rh", a.float(), wd.float()[expert_of_slot])
+    close(y, y_ref, 2e-5, f"tcgen05 down {shape}")
+    # and against the general kernels on the same inputs
+    close(o.moe_gate_up(x.to(DEV), plan, k, wg.to(DEV), wu.to(DEV), scores, False), act_ref, 2e-2, "general gate/up")
+    assert not o.moe_tc_supported(x.float().to(DEV), wg.float().to(DEV))
+
+
 def test_router_ties_go_to_the_lower_id():
     o = ops()
     x = torch.zeros(3, 16); x[:, 0] = 1.0
