@@ -86,6 +86,10 @@ class AttentionMixer(Part):
             # every token of the step is one request's decoded token: the tensor-core kernel
             o = ops.decode_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
                                      chunk, sliding, self.scale, ctx.max_context)
+        elif ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, self.nh, self.nkv, self.hd):
+            # portions of prompts (single tokens of other requests ride along as one-row tiles)
+            o = ops.prefill_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
+                                      ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale)
         else:
             o = ops.paged_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
                                     chunk, sliding, self.scale, ctx.max_context)

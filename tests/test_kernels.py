@@ -96,6 +96,11 @@ def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, 
         out = o.paged_attention(q, kp, vp, bt.to(DEV), sot.to(DEV), pos.to(DEV), chunk, window, hd ** -0.5,
                                 max(total) if split else 0)
         got = (q, out)
+        if o.prefill_attention_supported(dt, nh, nkv, hd):
+            cu = torch.tensor([0] + list(torch.tensor([b - a for a, b in spans]).cumsum(0)), dtype=torch.int32)
+            fast = o.prefill_attention(q, kp, vp, bt.to(DEV), cu.to(DEV), pos.to(DEV), S, max(b - a for a, b in spans),
+                                       chunk, window, hd ** -0.5)
+            got = (q, out, fast)
     # plain: whole sequences
     want_q, want_o = [], []
     for s in range(S):
@@ -145,6 +150,8 @@ def test_qkv_post_and_paged_attention(case, dt, tol):
                                inv_freq=inv, interleaved=inter, qk_norm=qkn, temp=temp, seed=nh * hd, split=split)
         close(got[0], want[0].reshape(got[0].shape), tol, f"q {case}")
         close(got[1], want[1].reshape(got[1].shape), tol, f"attention {case} split={split}")
+        if len(got) > 2:
+            close(got[2], want[1].reshape(got[2].shape), tol, f"tensor-core prefill attention {case}")
 
 
 @pytest.mark.parametrize("shape", [(40, 8, 128, 64, 0, 0), (8, 8, 64, 16, 0, 0), (32, 2, 128, 32, 512, 0), (10, 2, 64, 8, 0, 300),
