@@ -1,0 +1,92 @@
+"""Runs one kernel of hi_b200 alone on a small, fixed case, for `ncu -k regex:<kernel>`.
+
+    python -m hi_b200.kernels.cases decode_attention [batch] [context]
+    python -m hi_b200.kernels.cases expert_gemv [batch]
+    python -m hi_b200.kernels.cases expert_tc [tokens] [experts]
+    python -m hi_b200.kernels.cases prefill_attention [tokens]
+
+Sizes are the Scout layer's (40 heads, 8 kv heads, head_dim 128; hidden 5120, 16 experts of
+intermediate 8192); inputs are larger than L2 and well under a few GB.
+"""
+import sys
+
+import torch
+
+from . import ops
+
+DEV = "cuda:0"
+
+
+def decode_attention(batch=8, context=8192, page=64):
+    nh, nkv, hd = 40, 8, 128
+    blocks = -(-context // page)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    kp = torch.randn(batch * blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    vp = torch.randn(batch * blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    bt = torch.randperm(batch * blocks, device=DEV, generator=g).to(torch.int32).view(batch, blocks).contiguous()
+    q = torch.randn(batch, nh, hd, device=DEV, generator=g).to(torch.bfloat16)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+    sot = torch.arange(batch, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        out = ops.decode_attention(q, kp, vp, bt, sot, pos, 0, 0, hd ** -0.5, context)
+    torch.cuda.synchronize()
+    return out
+
+
+def expert_gemv(batch=8):
+    hidden, experts, inter = 5120, 16, 8192
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(batch, hidden, device=DEV, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(experts, inter, hidden, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    wu = (torch.randn(experts, inter, hidden, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(experts, hidden, inter, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    ids = torch.randint(0, experts, (batch, 1), device=DEV, generator=g).to(torch.int32)
+    scores = torch.rand(batch, 1, device=DEV, generator=g)
+    plan = ops.moe_plan(ids, experts)
+    for _ in range(3):
+        act = ops.moe_gate_up(x, plan, 1, wg, wu, scores, True)
+        y = ops.moe_down(act, wd, plan, True)
+    torch.cuda.synchronize()
+    return y
+
+
+def expert_tc(tokens=1024, experts=8):
+    """The tcgen05 grouped products at prefill shape: about 128 rows per expert."""
+    hidden, inter = 5120, 8192
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(tokens, hidden, device=DEV, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(experts, inter, hidden, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    wu = (torch.randn(experts, inter, hidden, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(experts, hidden, inter, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    ids = torch.randint(0, experts, (tokens, 1), device=DEV, generator=g).to(torch.int32)
+    scores = torch.rand(tokens, 1, device=DEV, generator=g)
+    plan = ops.moe_plan(ids, experts)
+    for _ in range(3):
+        act = ops.moe_gate_up_tc(x, plan, 1, wg, wu, scores)
+        y = ops.moe_down_tc(act, wd, plan)
+    ops.check_tc_status()
+    return y
+
+
+def prefill_attention(tokens=2048, page=64):
+    nh, nkv, hd = 40, 8, 128
+    blocks = -(-tokens // page)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    kp = torch.randn(blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    vp = torch.randn(blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    bt = torch.randperm(blocks, device=DEV, generator=g).to(torch.int32).view(1, blocks).contiguous()
+    q = torch.randn(tokens, nh, hd, device=DEV, generator=g).to(torch.bfloat16)
+    pos = torch.arange(tokens, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        out = ops.prefill_attention(q, kp, vp, bt, cu, pos, 1, tokens, 0, 0, hd ** -0.5)
+    torch.cuda.synchronize()
+    return out
+
+
+if __name__ == "__main__":
+    what = sys.argv[1]
+    args = [int(a) for a in sys.argv[2:]]
+    {"decode_attention": decode_attention, "expert_gemv": expert_gemv, "expert_tc": expert_tc,
+     "prefill_attention": prefill_attention}[what](*args)
+    print("ok")
