@@ -211,9 +211,32 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
   return HB_OK;
 }
 
+// The same, 4 columns per thread with vector loads (inter % 4 == 0).
+__global__ void swiglu_vec_kernel(const void* __restrict__ in, void* __restrict__ out, int dtype, size_t rows,
+                                  int inter) {
+  const int groups = inter / 4;
+  const size_t total = rows * (size_t)groups;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / groups;
+    const int j = (int)(i - t * groups) * 4;
+    const float4 g = load4_any(in, dtype, t * 2 * inter + j);
+    const float4 u = load4_any(in, dtype, t * 2 * inter + inter + j);
+    store4_any(out, dtype, t * inter + j,
+               make_float4(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y,
+                           g.z / (1.f + expf(-g.z)) * u.z, g.w / (1.f + expf(-g.w)) * u.w));
+  }
+}
+
 extern "C" int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream) {
   if (!in || !out || rows < 0 || inter <= 0 || !dtype_ok(dtype)) return HB_ERR_BAD_ARG;
   if (rows == 0) return HB_OK;
+  if (inter % 4 == 0) {
+    const size_t groups = (size_t)rows * (inter / 4);
+    const int blocks = (int)((groups + 255) / 256 < 148 * 32 ? (groups + 255) / 256 : 148 * 32);
+    swiglu_vec_kernel<<<blocks, 256, 0, stream>>>(in, out, dtype, (size_t)rows, inter);
+    HB_LAUNCH_CHECK();
+    return HB_OK;
+  }
   const size_t total = (size_t)rows * inter;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   swiglu_kernel<<<blocks, 256, 0, stream>>>(in, out, dtype, (size_t)rows, inter);

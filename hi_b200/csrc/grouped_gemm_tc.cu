@@ -2,13 +2,14 @@
 // accumulation in tensor memory:
 //     C[r, n] = sum_k A[r, k] * W[e(r), n, k]      for the expert-sorted rows r
 // A is [rows, K] with rows already in expert order (the caller gathers the activations), W is
-// [experts, n_out, K]; both K-major. One block computes a 128 x BN tile of one expert:
+// [experts, n_out, K]; both K-major. Persistent blocks (one per SM) walk 128 x BN tiles:
 //   warp 0      one lane issues the TMA loads (A tile 128x64, W tile BNx64, 128-byte swizzle)
-//               into a 4-stage ring, signalled by mbarrier transaction counts;
+//               into a ring of stages, signalled by mbarrier transaction counts;
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M 128, N BN, K 16, four
 //               per stage) and tcgen05.commit, which frees the stage / publishes the accumulator;
 //   warps 2..5  read the accumulator back with tcgen05.ld (each warp its 32 lanes = 32 rows)
-//               and write the epilogue:
+//               and write the epilogue, while the next tile already accumulates into the second
+//               buffer of tensor memory:
 //     DUAL   two weight stacks (gate, up), two accumulators: act = silu(s*g) * (s*u), bfloat16,
 //            where s is the row's router score (crates/hi-mlx/src/models.rs:6086-6100: the score
 //            scales the expert input, which is the same by linearity);
@@ -29,7 +30,6 @@ namespace {
 constexpr int BM = 128;          // rows of a tile (UMMA M)
 constexpr int BK = 64;           // k elements per stage: 128 bytes, one swizzle span
 constexpr int UK = 16;           // k of one tcgen05.mma
-constexpr int STAGES = 4;
 constexpr int THREADS = 192;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
@@ -119,48 +119,62 @@ struct Params {
   int experts, n_out, K, rows;
 };
 
-template <int BN, bool DUAL>
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Tile t of the launch, in the order (expert, column tile, row tile of the expert): tiles that
+// share a weight tile are neighbours, so they run at the same time and the weight tile comes from
+// HBM once. Returns false past the last tile. `n_tiles` = column tiles.
+struct Tile { int expert, row0, rows, n0; };
+template <int BN>
+__device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t, int n_tiles, Tile& out) {
+  for (int e = 0; e < experts; ++e) {
+    const int begin = offsets[e], cnt = offsets[e + 1] - begin;
+    const int m_tiles = (cnt + BM - 1) / BM;
+    const int here = m_tiles * n_tiles;
+    if (t < here) {
+      const int nt = t / m_tiles, mt = t - nt * m_tiles;
+      out.expert = e;
+      out.row0 = begin + mt * BM;
+      out.rows = min(BM, cnt - mt * BM);
+      out.n0 = nt * BN;
+      return true;
+    }
+    t -= here;
+  }
+  return false;
+}
+
+// Persistent: each block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... The shared-memory
+// ring runs on across tiles; tensor memory holds TWO accumulator buffers, so the epilogue of one
+// tile overlaps the loads and MMAs of the next.
+template <int BN, bool DUAL, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w0,
                        const __grid_constant__ CUtensorMap map_w1, const Params p) {
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + (DUAL ? 2 : 1) * B_BYTES;
-  constexpr int TMEM_COLS = DUAL ? 2 * BN : BN;
-  static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "");
+  constexpr int ACC_COLS = DUAL ? 2 * BN : BN;       // columns of one accumulator buffer
+  constexpr int TMEM_COLS = 2 * ACC_COLS;
+  static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* accum = empty + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
-  int* tile_info = reinterpret_cast<int*>(tmem_slot + 1);      // expert, row0, rows
+  uint64_t* acc_full = empty + STAGES;               // [2]
+  uint64_t* acc_empty = acc_full + 2;                // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  int* s_offsets = reinterpret_cast<int*>(tmem_slot + 2);   // [experts + 1]: the tile search never waits on global memory
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = threadIdx.x; e <= p.experts; e += THREADS) s_offsets[e] = p.offsets[e];
   if (threadIdx.x == 0) {
-    int want = blockIdx.y, found = -1, r0 = 0, rows = 0;
-    for (int e = 0; e < p.experts; ++e) {
-      const int c = p.offsets[e + 1] - p.offsets[e];
-      const int tiles = (c + BM - 1) / BM;
-      if (want < tiles) {
-        found = e;
-        r0 = p.offsets[e] + want * BM;
-        rows = min(BM, p.offsets[e + 1] - r0);
-        break;
-      }
-      want -= tiles;
-    }
-    tile_info[0] = found; tile_info[1] = r0; tile_info[2] = rows;
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    mbar_init(accum, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
-  const int expert = tile_info[0], row0 = tile_info[1], rows = tile_info[2];
-  if (expert < 0) return;                       // uniform: no tensor memory was taken yet
-  const int n0 = blockIdx.x * BN;
-  const int num_kb = (p.K + BK - 1) / BK;
-
-  if (warp == 1) {                              // tensor memory for the accumulators
+  if (warp == 1) {                              // tensor memory for the two accumulator buffers
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"((uint32_t)TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -169,51 +183,76 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const int n_tiles = (p.n_out + BN - 1) / BN;
+  const int num_kb = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
     if (lane == 0) {                            // ---- TMA producer
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) { atomicExch(p.status, 1); break; }
-        uint8_t* st = smem + s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_2d(st, &map_a, kb * BK, row0, &full[s]);
-        tma_load_2d(st + A_BYTES, &map_w0, kb * BK, expert * p.n_out + n0, &full[s]);
-        if (DUAL) tma_load_2d(st + A_BYTES + B_BYTES, &map_w1, kb * BK, expert * p.n_out + n0, &full[s]);
+      uint32_t it = 0;                          // stages filled so far, over all tiles
+      bool ok = true;
+      Tile tile;
+      for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) { atomicExch(p.status, 1); ok = false; break; }
+          uint8_t* st = smem + s * STAGE_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(st, &map_a, kb * BK, tile.row0, &full[s]);
+          tma_load_2d(st + A_BYTES, &map_w0, kb * BK, tile.expert * p.n_out + tile.n0, &full[s]);
+          if (DUAL) tma_load_2d(st + A_BYTES + B_BYTES, &map_w1, kb * BK, tile.expert * p.n_out + tile.n0, &full[s]);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {                            // ---- MMA issuer
       constexpr uint32_t idesc = instr_desc(BM, BN);
+      uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&full[s], (kb / STAGES) & 1)) { atomicExch(p.status, 2); ok = false; break; }
+      Tile tile;
+      for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x, ++local) {
+        const int b = local & 1;
+        const uint32_t use = local >> 1;
+        if (use > 0 && !mbar_wait(&acc_empty[b], (use - 1) & 1)) { atomicExch(p.status, 4); ok = false; break; }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-        const uint32_t b_addr = a_addr + A_BYTES;
+        const uint32_t acc = tmem + b * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full[s], (it / STAGES) & 1)) { atomicExch(p.status, 2); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UK; ++k) {
-          const uint64_t ad = smem_desc(a_addr + k * UK * 2);
-          tc_mma(tmem, ad, smem_desc(b_addr + k * UK * 2), idesc, (kb | k) != 0);
-          if (DUAL) tc_mma(tmem + BN, ad, smem_desc(b_addr + B_BYTES + k * UK * 2), idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t ad = smem_desc(a_addr + k * UK * 2);
+            tc_mma(acc, ad, smem_desc(b_addr + k * UK * 2), idesc, (kb | k) != 0);
+            if (DUAL) tc_mma(acc + BN, ad, smem_desc(b_addr + B_BYTES + k * UK * 2), idesc, (kb | k) != 0);
+          }
+          tc_commit(&empty[s]);                 // the stage is free once these MMAs have read it
         }
-        tc_commit(&empty[s]);                   // the stage is free once these MMAs have read it
+        tc_commit(&acc_full[b]);                // this tile's accumulator is complete (also on the error path)
       }
-      tc_commit(accum);                         // the accumulator is complete (also on the error path)
     }
   } else {                                      // ---- epilogue: warps 2..5, lanes 32*(warp % 4) ..
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;          // row of the tile = lane of tensor memory
-    const bool waited = __all_sync(0xffffffffu, mbar_wait(accum, 0));
-    if (!waited && lane == 0) atomicExch(p.status, 3);
-    tc_fence_after();
-    const bool row_ok = waited && r < rows;
-    const size_t grow = (size_t)(row0 + r);
-    float score = 1.f;
-    if (DUAL && row_ok) score = p.scores[p.sorted_entry[row0 + r]];
-    const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-    if (waited) {
+    uint32_t local = 0;
+    bool ok = true;
+    Tile tile;
+    for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x, ++local) {
+      const int b = local & 1;
+      const bool waited = __all_sync(0xffffffffu, mbar_wait(&acc_full[b], (local >> 1) & 1));
+      if (!waited) {
+        if (lane == 0) atomicExch(p.status, 3);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool row_ok = r < tile.rows;
+      const size_t grow = (size_t)(tile.row0 + r);
+      float score = 1.f;
+      if (DUAL && row_ok) score = p.scores[p.sorted_entry[tile.row0 + r]];
+      const uint32_t lane_base = tmem + b * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      const int n0 = tile.n0;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         float g[32];
@@ -248,6 +287,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
               *reinterpret_cast<float4*>(dst + i) = make_float4(g[i], g[i + 1], g[i + 2], g[i + 3]);
         }
       }
+      // this warp is done reading the buffer: the MMA issuer may overwrite it two tiles on
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);
     }
   }
   tc_fence_before();
@@ -297,7 +340,7 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint
   return r == CUDA_SUCCESS ? HB_OK : HB_ERR_BAD_ARG;
 }
 
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, int STAGES>
 int launch(const void* a, const void* w0, const void* w1, const Params& p, int max_tiles, cudaStream_t stream) {
   CUtensorMap ma, mw0, mw1;
   int rc = make_map(&ma, a, (uint64_t)p.rows, (uint64_t)p.K, BM);
@@ -307,12 +350,17 @@ int launch(const void* a, const void* w0, const void* w1, const Params& p, int m
   rc = make_map(&mw1, DUAL ? w1 : w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BN);
   if (rc != HB_OK) return rc;
   constexpr int STAGE_BYTES = BM * BK * 2 + (DUAL ? 2 : 1) * BN * BK * 2;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + 4 * ((size_t)p.experts + 1);
+  if (smem > 227 * 1024) return HB_ERR_UNSUPPORTED;
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<BN, DUAL, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((p.n_out + BN - 1) / BN, max_tiles);
-  grouped_gemm_tc_kernel<BN, DUAL><<<grid, THREADS, smem, stream>>>(ma, mw0, mw1, p);
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return HB_ERR_BAD_ARG;
+  const long long upper = (long long)max_tiles * ((p.n_out + BN - 1) / BN);    // tiles there can be at most
+  const int grid = (int)(upper < sms ? upper : sms);                            // one persistent block per SM
+  grouped_gemm_tc_kernel<BN, DUAL, STAGES><<<grid, THREADS, smem, stream>>>(ma, mw0, mw1, p);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -340,7 +388,7 @@ extern "C" int hb_moe_gate_up_tc(const void* xs, const int* sorted_entry, const 
   const int max_tiles = (rows + BM - 1) / BM + (experts < rows ? experts : rows);
   if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
   Params p{offsets, sorted_entry, scores, act, status, experts, inter, hidden, rows};
-  return launch<128, true>(xs, w_gate, w_up, p, max_tiles, stream);
+  return launch<128, true, 4>(xs, w_gate, w_up, p, max_tiles, stream);
 }
 
 // down projection on tensor cores: act [rows, inter] -> y float32 [rows, hidden].
@@ -352,5 +400,5 @@ extern "C" int hb_moe_down_tc(const void* act, const void* w_down, const int* of
   const int max_tiles = (rows + BM - 1) / BM + (experts < rows ? experts : rows);
   if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
   Params p{offsets, nullptr, nullptr, y, status, experts, hidden, inter, rows};
-  return launch<256, false>(act, w_down, nullptr, p, max_tiles, stream);
+  return launch<256, false, 4>(act, w_down, nullptr, p, max_tiles, stream);
 }

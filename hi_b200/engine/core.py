@@ -42,11 +42,11 @@ def _require_cuda(device) -> None:
     configure_matmul_precision()
 
 
-def _check_kernel_status() -> None:
+def _check_kernel_status(force: bool = False) -> None:
     """A tensor-core kernel that gave up a bounded wait makes the step fail loudly."""
     from ..kernels import ops
 
-    if ops.TC_USED[0]:
+    if ops.TC_USED[0] or force:
         ops.check_tc_status()
 
 
@@ -197,6 +197,8 @@ class Engine:
             self._build_context(entries, widths=graph.widths, static=graph)
             graph.graph.replay()
             _count_launches(graph.kernels)
+            if graph.uses_tensor_core_experts:
+                _check_kernel_status(force=True)
             logits = graph.logits.clone()
             ctx, logit_rows = graph.ctx, graph.logit_rows
         else:
@@ -349,6 +351,8 @@ class _DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.captured = False
         self.eager_runs = 0
+        self.kernels = 0
+        self.uses_tensor_core_experts = False
 
     def capture(self, entries: Sequence[StepEntry]) -> None:
         eng = self.engine
@@ -363,8 +367,11 @@ class _DecodeGraph:
         from ..kernels import ops
 
         before = ops.LAUNCHES[0]
+        ops.TC_USED[0] = False
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.logits = eng.model.forward(self.ctx, eng.cache.views, self.logit_rows)
         self.kernels = ops.LAUNCHES[0] - before      # this library's kernels in one replay
+        self.uses_tensor_core_experts = ops.TC_USED[0]
+        ops.TC_USED[0] = False
         self.captured = True

@@ -72,7 +72,8 @@ class SigmoidRoutedExperts(Part):
 
     graph_safe = True
 
-    FEW_ROWS = 128   # up to this many routed rows the weight-streaming kernel is used
+    FEW_ROWS = 16    # up to this many routed rows the weight-streaming kernel is used (measured: above
+                     # it the tcgen05 kernel streams the expert weights faster, even with nearly empty tiles)
     wants_f32_input = True   # the router reads the norm's float32 output
 
     def __init__(self, params, prefix, env):
@@ -117,8 +118,9 @@ class SigmoidRoutedExperts(Part):
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.router_ids", ids)
         plan = ops.moe_plan(ids, self.experts)
-        few = n * self.top_k <= self.FEW_ROWS
-        if not few and ops.moe_tc_supported(normed, self.w_gate):
+        tc = ops.moe_tc_supported(normed, self.w_gate)
+        few = n * self.top_k <= (self.FEW_ROWS if tc else 128)
+        if not few and tc:
             # many rows per expert: the grouped products run on tcgen05
             act = ops.moe_gate_up_tc(normed, plan, self.top_k, self.w_gate, self.w_up, scores)
             y = ops.moe_down_tc(act, self.w_down, plan)
