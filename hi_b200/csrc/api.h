@@ -39,7 +39,7 @@ int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages,
 int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                          int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_seqs,
                          int max_new, int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,
-                         cudaStream_t stream);
+                         int skip_single, cudaStream_t stream);
 
 int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
                    int top_k, float* logits_out, int* ids, float* scores, cudaStream_t stream);

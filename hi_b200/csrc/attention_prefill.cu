@@ -23,7 +23,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
                     int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
                     __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int chunk, int window,
-                    float scale) {
+                    float scale, int skip_single) {
   constexpr int STRIDE = HD + 8;
   constexpr int CHUNKS = HD / 8;
   constexpr int ROWS_PER_PASS = NWARPS * 32 / CHUNKS;
@@ -37,6 +37,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int tok0 = cu_seqlens[seq] + qt * BQ;
   const int n_valid = min(BQ, cu_seqlens[seq + 1] - tok0);
   if (n_valid <= 0) return;
+  // requests that bring one token are left to the decode kernel when the caller says so
+  if (skip_single && cu_seqlens[seq + 1] - cu_seqlens[seq] == 1) return;
   const int kvh = h / (nh / nkv);
   const int p_first = positions[tok0];           // the rows of a tile are consecutive positions
   const int p_last = p_first + n_valid - 1;
@@ -220,7 +222,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 template <int HD>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                    const int* cu_seqlens, const int* positions, void* out, int n_seqs, int max_new, int nh, int nkv,
-                   int page_size, int chunk, int window, float scale, cudaStream_t stream) {
+                   int page_size, int chunk, int window, float scale, int skip_single, cudaStream_t stream) {
   constexpr int STRIDE = HD + 8;
   const size_t smem = (size_t)(BQ * STRIDE + 4 * TILE * STRIDE) * sizeof(__nv_bfloat16);
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -228,7 +230,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
   dim3 grid((max_new + BQ - 1) / BQ, nh, n_seqs);
   attn_prefill_kernel<HD><<<grid, NWARPS * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
-      cu_seqlens, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale);
+      cu_seqlens, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, skip_single);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -241,7 +243,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
 extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                     int table_stride, const int* cu_seqlens, const int* positions, void* out,
                                     int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
-                                    int window, float scale, cudaStream_t stream) {
+                                    int window, float scale, int skip_single, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out) return HB_ERR_BAD_ARG;
   if (n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 ||
       chunk < 0 || window < 0)
@@ -250,9 +252,9 @@ extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const vo
   if (n_seqs == 0 || max_new == 0) return HB_OK;
   if (hd == 128)
     return launch_prefill<128>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
-                               max_new, nh, nkv, page_size, chunk, window, scale, stream);
+                               max_new, nh, nkv, page_size, chunk, window, scale, skip_single, stream);
   if (hd == 64)
     return launch_prefill<64>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
-                              max_new, nh, nkv, page_size, chunk, window, scale, stream);
+                              max_new, nh, nkv, page_size, chunk, window, scale, skip_single, stream);
   return HB_ERR_UNSUPPORTED;
 }

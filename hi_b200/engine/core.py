@@ -287,6 +287,12 @@ class Engine:
             start_pos=starts, n_new=n_new, slot_ids=slots, block_tables=block_tables, page_size=self.page_size,
             max_context=max(s + n for s, n in zip(starts, n_new)))
         ctx._host_buffer = host       # keep the pinned buffer alive until the copy has run
+        singles = [s for s, n in enumerate(n_new) if n == 1]
+        if singles and len(singles) < n_seqs:
+            # rows of cu_seqlens for the single-token requests, picked on the device (no second copy)
+            idx = torch.tensor(singles, dtype=torch.int64).to(self.device, non_blocking=True)
+            ctx.decode_rows = ctx.cu_seqlens.index_select(0, idx).to(torch.int64)
+            ctx.decode_max_context = max(starts[s] + 1 for s in singles)
         logit_rows = seg(o_want, n_want) if n_want else None
         return ctx, logit_rows
 

@@ -25,7 +25,7 @@ _SIGNATURES = {
     "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "hb_attention_merge": [P, P, P, I, I, I, I, P],
     "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
-    "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
     "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, P],
@@ -319,9 +319,12 @@ def prefill_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int
 
 def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                       cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, max_new: int, chunk: int,
-                      window: int, scale: float) -> torch.Tensor:
+                      window: int, scale: float, skip_single: bool = False,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention for portions of prompts: request ``s`` owns rows ``cu_seqlens[s]..cu_seqlens[s+1]``
-    of ``q`` [N, nh, hd], at consecutive positions; bfloat16, flash attention on tensor cores."""
+    of ``q`` [N, nh, hd], at consecutive positions; bfloat16, flash attention on tensor cores.
+    ``skip_single`` leaves the rows of requests that bring one token unwritten (the caller runs
+    the decode kernel for them and passes the same ``out``)."""
     _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
         _need(t, nm, torch.int32)
@@ -333,10 +336,11 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise KernelError(f"prefill attention does not take nh={nh} nkv={nkv} head_dim={hd}")
     if cu_seqlens.numel() != n_seqs + 1 or block_table.shape[0] < n_seqs:
         raise KernelError("cu_seqlens / block_table do not match the number of requests")
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
     _check(lib().hb_attention_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                                       _ptr(cu_seqlens), _ptr(positions), _ptr(out), n_seqs, int(max_new), nh, nkv, hd,
-                                      page_size, int(chunk), int(window), float(scale), _stream()),
+                                      page_size, int(chunk), int(window), float(scale), int(skip_single), _stream()),
            "attention_prefill")
     return out
 

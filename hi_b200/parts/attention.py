@@ -88,8 +88,16 @@ class AttentionMixer(Part):
                                      chunk, sliding, self.scale, ctx.max_context)
         elif ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, self.nh, self.nkv, self.hd):
             # portions of prompts (single tokens of other requests ride along as one-row tiles)
+            single = ctx.decode_rows is not None and ops.decode_attention_supported(q.dtype, self.nh, self.nkv, self.hd)
             o = ops.prefill_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
-                                      ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale)
+                                      ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale, skip_single=single)
+            if single:
+                # single tokens beside portions: their long key ranges go through the split decode kernel
+                rows = ctx.decode_rows
+                od = ops.decode_attention(q.index_select(0, rows), cache.k_pages, cache.v_pages, block_table,
+                                          ctx.seq_of_token.index_select(0, rows), positions.index_select(0, rows),
+                                          chunk, sliding, self.scale, ctx.decode_max_context)
+                o.index_copy_(0, rows, od)
         else:
             o = ops.paged_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
                                     chunk, sliding, self.scale, ctx.max_context)

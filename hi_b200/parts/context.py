@@ -30,6 +30,10 @@ class StepContext:
     page_size: int = 0
     max_context: int = 0          # longest start_pos + n_new in the step
     tap: Optional[Callable[[str, torch.Tensor], None]] = None   # debug: parts report named tensors
+    # mixed steps only: flat rows of the requests that bring ONE token (int64 [D]) and the longest
+    # context among them; None when the step is all portions or all single tokens
+    decode_rows: Optional[torch.Tensor] = None
+    decode_max_context: int = 0
 
     @property
     def max_new(self) -> int:

@@ -17,11 +17,11 @@ def pytest_configure(config):
 def model_dirs(tmp_path_factory):
     """Model folders of the tiny configurations, written once per session into a temp folder."""
     from harness import make_model
-    from tiny_configs import TINY_A, TINY_B, TINY_C
+    from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
     base = tmp_path_factory.mktemp("models")
     out = {}
-    for name, cfg in (("A", TINY_A), ("B", TINY_B), ("C", TINY_C)):
+    for name, cfg in (("A", TINY_A), ("B", TINY_B), ("C", TINY_C), ("D", TINY_D)):
         out[name] = (cfg, make_model(str(base / name), cfg, seed=11, std=0.08))
         out[name + "_small_std"] = (cfg, make_model(str(base / (name + "s")), cfg, seed=12, std=0.02))
     return out

@@ -44,3 +44,16 @@ TINY_C = {
     "intermediate_size": 72, "intermediate_size_mlp": 200,
     "tie_word_embeddings": False, "max_position_embeddings": 1024,
 }
+
+# head_dim 64 with 4 query heads per kv head: the shapes the tensor-core attention kernels take
+TINY_D = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 300, "hidden_size": 128, "num_hidden_layers": 3,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64,
+    "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None,
+    "attention_chunk_size": 48, "nope_layer_interval": 3,
+    "use_qk_norm": True, "attn_temperature_tuning": True, "floor_scale": 32, "attn_scale": 0.1,
+    "interleave_moe_layer_step": 1, "num_local_experts": 4, "num_experts_per_tok": 2,
+    "intermediate_size": 64, "intermediate_size_mlp": 128,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
