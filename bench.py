@@ -41,7 +41,9 @@ SCOUT = {
     "intermediate_size": 8192, "intermediate_size_mlp": 16384, "tie_word_embeddings": False,
     "max_position_embeddings": 262144,
 }
-FULL_LAYERS = 16
+MAVERICK = dict(SCOUT, num_hidden_layers=4, rope_scaling=None, use_qk_norm=False, interleave_moe_layer_step=2,
+                num_local_experts=128)
+MODELS = {"scout": (SCOUT, 16), "maverick": (MAVERICK, 4)}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -99,17 +101,31 @@ class ClockSampler:
                 "reasons": sorted(self.reasons)}
 
 
-def layer_bytes_and_flops(cfg, distinct_experts, tokens):
-    """Bytes of weights one layer's step must read, and flops per token, bfloat16."""
-    h, nh, nkv, hd = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
-    e, k, i = cfg["num_local_experts"], cfg["num_experts_per_tok"], cfg["intermediate_size"]
-    attn = (nh + 2 * nkv) * hd * h + h * nh * hd
-    shared = 3 * h * i
-    expert = 3 * h * i
-    router = e * h
-    weight_bytes = 2 * (attn + shared + router + distinct_experts * expert + 2 * h)
-    flops_per_token = 2 * (attn + shared + router + k * expert)
-    return weight_bytes, flops_per_token
+def model_bytes_and_flops(model, distinct_by_layer, context):
+    """From the built model: bytes of weights and cache one decode step must read for ONE request
+    at ``context`` tokens (weights counted once, experts by how many distinct ones the step
+    touched), the cache bytes per request, and the matrix flops per token."""
+    weight_bytes, kv_bytes, flops = 0, 0, 0
+    for i, layer in enumerate(model.layers):
+        mix, ff = layer.mixer, layer.feed_forward
+        attn = mix.w_qkv.numel() + mix.w_o.numel()
+        weight_bytes += 2 * attn + 2 * 2 * model.spec.hidden_size
+        flops += 2 * attn
+        visible = context
+        if mix.window:
+            visible = ((context - 1) % mix.window[1]) + 1 if mix.window[0] == "chunk" else min(context, mix.window[1])
+        kv_bytes += 2 * 2 * mix.nkv * mix.hd * visible
+        if hasattr(ff, "w_gate"):
+            expert = 3 * ff.hidden * ff.inter
+            shared = ff.shared.w_gate_up.numel() + ff.shared.w_down.numel() if ff.shared else 0
+            weight_bytes += 2 * (ff.w_router.numel() + shared + distinct_by_layer.get(i, ff.experts) * expert)
+            flops += 2 * (ff.w_router.numel() + shared + ff.top_k * expert)
+        else:
+            dense = ff.mlp.w_gate_up.numel() + ff.mlp.w_down.numel()
+            weight_bytes += 2 * dense
+            flops += 2 * dense
+    head = 2 * model.spec.vocab_size * model.spec.hidden_size
+    return weight_bytes + head, kv_bytes, flops
 
 
 def main(argv=None) -> int:
@@ -118,7 +134,8 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--model", default="scout", choices=sorted(MODELS))
+    ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
@@ -144,15 +161,21 @@ def main(argv=None) -> int:
     from hi_b200.sampling import SamplingParams
 
     pk = peaks()
-    cfg = dict(SCOUT, num_hidden_layers=args.layers)
+    base_cfg, FULL_LAYERS = MODELS[args.model]
+    if args.layers is None:
+        args.layers = FULL_LAYERS
+    cfg = dict(base_cfg, num_hidden_layers=args.layers)
     points = sorted({int(p) for p in args.points.split(",") if p} | {args.batch})
     max_batch = max(points)
     page = 64
     ctx_len = args.context
     cache_tokens = max_batch * (ctx_len + page) + args.prefill_tokens + 4 * page
+    # rotary layers keep one attention chunk per request (plus the pages being written)
+    chunk_tokens = max_batch * (min(ctx_len, cfg["attention_chunk_size"]) + 2 * page) + args.prefill_tokens + 4 * page
     t0 = time.time()
     engine = Engine.from_config(cfg, seed=0, std=0.02, dtype="bfloat16", kv_page_size=page,
-                                kv_cache_tokens=cache_tokens, max_active_requests=max_batch + 2)
+                                kv_cache_tokens=cache_tokens, windowed_cache_tokens=chunk_tokens,
+                                max_active_requests=max_batch + 2)
     torch.cuda.synchronize()
     load_s = time.time() - t0
     gen = torch.Generator(device="cuda").manual_seed(1)
@@ -177,7 +200,8 @@ def main(argv=None) -> int:
         taps = {}
         engine.step([StepEntry(r, [toks[total - 1][i]], [0]) for i, r in enumerate(ids)],
                     tap=lambda n, t: taps.__setitem__(n, t))
-        distinct = [len(set(t.flatten().tolist())) for n, t in taps.items() if n.endswith("router_ids")]
+        distinct = {int(n.split(".")[2]): len(set(t.flatten().tolist())) for n, t in taps.items()
+                    if n.endswith("router_ids")}
         for s in range(args.warmup):
             engine.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
         torch.cuda.synchronize()
@@ -192,19 +216,17 @@ def main(argv=None) -> int:
         launches = ops.LAUNCHES[0] - launches0
         for rid in ids:
             engine.finish(rid)
-        return ms, launches, (sum(distinct) / len(distinct) if distinct else 0.0)
+        return ms, launches, distinct
 
-    def decode_bytes(batch, mean_distinct):
-        wb, _ = layer_bytes_and_flops(cfg, mean_distinct, batch)
-        kv_per_token_layer = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
-        kv = batch * ctx_len * kv_per_token_layer * args.layers      # chunk == context here: every layer reads all
-        head = 2 * vocab * cfg["hidden_size"]
-        return wb * args.layers + kv + head
+    def decode_bytes(batch, distinct):
+        wb, kv, _ = model_bytes_and_flops(engine.model, distinct, ctx_len)
+        return wb + batch * kv
 
     results = {}
     for b in points:
         ms, launches, distinct = timed_decode(b)
-        results[b] = {"ms": ms, "tok_s": b * 1000.0 / ms, "launches": launches, "distinct": distinct,
+        results[b] = {"ms": ms, "tok_s": b * 1000.0 / ms, "launches": launches,
+                      "distinct": (sum(distinct.values()) / len(distinct) if distinct else 0.0),
                       "bytes": decode_bytes(b, distinct)}
     main_r = results[args.batch]
 
@@ -226,9 +248,9 @@ def main(argv=None) -> int:
             if r > 0:
                 times.append(start.elapsed_time(end))
         ms = statistics.median(times)
-        _, fpt = layer_bytes_and_flops(cfg, cfg["num_local_experts"], T)
+        _, _, fpt = model_bytes_and_flops(engine.model, {}, T)
         nh, hd = cfg["num_attention_heads"], cfg["head_dim"]
-        flops = args.layers * (fpt * T + 4 * nh * hd * T * T / 2) + 2 * vocab * cfg["hidden_size"]
+        flops = fpt * T + args.layers * 4 * nh * hd * T * T / 2 + 2 * vocab * cfg["hidden_size"]
         prefill = {"value": T * 1000.0 / ms, "tokens": T, "ms": ms, "frac": flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12),
                    "peak_tflops": pk["bf16_tflops"], "peak_source": pk["source"]}
 
@@ -260,16 +282,15 @@ def main(argv=None) -> int:
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t_wall) * 1000.0
     e2e_tok_s = args.batch * n_steps * 1000.0 / max(wall_ms, start.elapsed_time(end))
-    h2d = 4 * (3 * args.batch + (args.batch + 1) + 2 * args.batch +
-               sum(args.batch * (-(-ctx_len // page)) for _ in engine.manager.groups))
+    h2d = engine.last_step_h2d_bytes          # the packed step inputs (tokens, positions, block tables, ...)
     clocks = sampler.stop()
 
     line = {
-        "metric": "decode tokens/s (Llama 4 Scout layer sizes, bf16)", "value": main_r["tok_s"], "unit": "tokens/s",
+        "metric": f"decode tokens/s (Llama 4 {args.model.capitalize()} layer sizes, bf16)", "value": main_r["tok_s"], "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_r["ms"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0,0.02), uniform random token ids, noise-filled KV cache",
-        "config": {"model": "llama4-scout-layers", "layers": args.layers, "layers_full": FULL_LAYERS,
+        "config": {"model": f"llama4-{args.model}-layers", "layers": args.layers, "layers_full": FULL_LAYERS,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "experts": cfg["num_local_experts"], "top_k": cfg["num_experts_per_tok"],
                    "expert_inter": cfg["intermediate_size"], "vocab": vocab, "chunk": cfg["attention_chunk_size"],

@@ -107,6 +107,7 @@ class Engine:
         self.debug_poison = debug_poison
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
         self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
+        self.last_step_h2d_bytes = 0
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -144,8 +145,12 @@ class Engine:
         (pages are taken; their contents are whatever the pools hold). Lets a decode step at a
         long context be timed without running the prefill that would produce it."""
         self.open(request_id)
-        self.manager.reserve(request_id, length)
-        self.manager.commit(request_id, length)
+        done = 0
+        while done < length:          # in runs, so that windowed groups never hold more than a window
+            n = min(4096, length - done)
+            self.manager.reserve(request_id, n)
+            self.manager.commit(request_id, n)
+            done += n
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], tap=None) -> Optional[torch.Tensor]:
@@ -270,6 +275,7 @@ class Engine:
             view[:] = -1
             for s, t in enumerate(tg):
                 view[s, : len(t)] = t
+        self.last_step_h2d_bytes = host.numel() * 4     # the one host-to-device copy of this step
         if static is not None:
             static.dev.copy_(host, non_blocking=True)
             static.copied.record()
