@@ -86,6 +86,7 @@ class RequestCache:
     slot: int
     length: int = 0                                   # tokens whose keys are in the cache
     tables: List[List[int]] = field(default_factory=list)   # per group: block -> page or FREED
+    version: int = 0                                  # bumped whenever a table changes
 
 
 class CacheManager:
@@ -180,6 +181,8 @@ class CacheManager:
         for g, spec in enumerate(self.groups):
             table = rc.tables[g]
             first_live = spec.first_live_position(rc.length) // self.page_size
+            if len(table) < need_blocks:
+                rc.version += 1
             while len(table) < need_blocks:
                 # blocks wholly before the window of the first new token are never read
                 table.append(FREED if len(table) < first_live else self.pools[g].take(request_id))
@@ -198,10 +201,14 @@ class CacheManager:
                     self.pools[g].give(table[b], request_id)
                     returned.append((g, table[b]))
                     table[b] = FREED
+                    rc.version += 1
         return returned
 
     def table(self, group: int, request_id: Hashable) -> List[int]:
         return self.requests[request_id].tables[group]
+
+    def table_version(self, request_id: Hashable) -> int:
+        return self.requests[request_id].version
 
     def held_pages(self, request_id: Hashable) -> List[int]:
         return [sum(1 for p in t if p != FREED) for t in self.requests[request_id].tables]

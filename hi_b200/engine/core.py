@@ -108,6 +108,8 @@ class Engine:
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
         self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
         self.last_step_h2d_bytes = 0
+        self._status = None            # ops.PendingStatus, made when a captured step uses the tcgen05 kernels
+        self._status_pending = False
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -159,6 +161,7 @@ class Engine:
         tensor)``, if given, is called by parts that report intermediate tensors (router ids),
         in the step's flat token order (crates/hi-cuda/src/lib.rs:87-201 has such a dump hook)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self._resolve_status()
         if not entries:
             return None
         seen = set()
@@ -203,7 +206,13 @@ class Engine:
             graph.graph.replay()
             _count_launches(graph.kernels)
             if graph.uses_tensor_core_experts:
-                _check_kernel_status(force=True)
+                # no sync here: the status word follows the kernels to pinned memory and is read
+                # at the start of the next step (or when the engine is asked for its state)
+                if self._status is None:
+                    from ..kernels import ops
+                    self._status = ops.PendingStatus(self.device)
+                self._status.enqueue()
+                self._status_pending = True
             logits = graph.logits.clone()
             ctx, logit_rows = graph.ctx, graph.logit_rows
         else:
@@ -269,12 +278,20 @@ class Engine:
             cursor += n
             buf[o_cu + s + 1] = cursor
             buf[o_slot + s] = slots[s]
+        # a captured decode step keeps its table rows between steps: a row is rewritten only when
+        # another request sits in it or the request's tables changed (a new page, a freed chunk)
+        fresh = [True] * n_seqs
+        if static is not None:
+            sigs = [(e.request_id, mgr.table_version(e.request_id)) for e in entries]
+            fresh = [static.row_sig[s] != sigs[s] for s in range(n_seqs)]
+            static.row_sig = sigs
         for g, tg in enumerate(tables):
             o, w = offsets[6 + g], widths[g]
             view = buf[o: o + n_seqs * w].reshape(n_seqs, w)
-            view[:] = -1
             for s, t in enumerate(tg):
-                view[s, : len(t)] = t
+                if fresh[s]:
+                    view[s, : len(t)] = t
+                    view[s, len(t):] = -1
         self.last_step_h2d_bytes = host.numel() * 4     # the one host-to-device copy of this step
         if static is not None:
             static.dev.copy_(host, non_blocking=True)
@@ -327,8 +344,14 @@ class Engine:
             graph.capture(entries)
         return graph
 
+    def _resolve_status(self) -> None:
+        if self._status_pending:
+            self._status_pending = False
+            self._status.resolve()
+
     # ------------------------------------------------------------------ bookkeeping
     def snapshot(self) -> dict:
+        self._resolve_status()
         s = self.manager.snapshot()
         s.update(steps=self.stats.steps, tokens=self.stats.tokens, prefill_tokens=self.stats.prefill_tokens,
                  decode_tokens=self.stats.decode_tokens, cache_bytes=self.cache.bytes)
@@ -363,6 +386,7 @@ class _DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.captured = False
         self.eager_runs = 0
+        self.row_sig = [None] * n_seqs      # (request, table version) last written into each table row
         self.kernels = 0
         self.uses_tensor_core_experts = False
 

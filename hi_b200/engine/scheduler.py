@@ -46,7 +46,7 @@ class SchedulerConfig:
             raise ValueError("max_prefill_portion must be positive")
 
 
-@dataclass
+@dataclass(eq=False)          # requests are compared by identity
 class Request:
     request_id: Hashable
     prompt: List[int]
@@ -69,6 +69,19 @@ class Request:
     @property
     def pending(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed
+
+    @property
+    def last_token(self) -> int:
+        return self.output[-1] if self.output else self.prompt[-1]
+
+    def span(self, begin: int, end: int) -> List[int]:
+        """Tokens ``begin .. end`` of prompt + output, without building the whole list."""
+        n = len(self.prompt)
+        if end <= n:
+            return self.prompt[begin:end]
+        if begin >= n:
+            return self.output[begin - n:end - n]
+        return self.prompt[begin:] + self.output[:end - n]
 
 
 @dataclass
@@ -186,15 +199,17 @@ class Scheduler:
 
         # 1. every running request that has one token pending decodes, oldest first
         decoding = [r for r in self.running if r.pending == 1 and r.computed >= len(r.prompt)]
+        planned = set()                        # ids of requests with an entry in this plan
         i = 0
         while i < len(decoding) and budget > 0 and len(plan.entries) < cfg.max_batch_size:
             r = decoding[i]
-            if r not in self.running:           # preempted meanwhile
+            if r.status != RUNNING:             # preempted meanwhile
                 i += 1
                 continue
             if self._fits(r, 1, promised, True):
                 self._promise(r, 1, promised, True)
-                plan.entries.append(PlannedEntry(r, [r.tokens[-1]], True))
+                plan.entries.append(PlannedEntry(r, [r.last_token], True))
+                planned.add(id(r))
                 budget -= 1
                 i += 1
                 continue
@@ -205,7 +220,8 @@ class Scheduler:
                 i += 1
                 continue
             # the victim's promised pages, if it was planned, come back with it
-            if any(e.request is victim for e in plan.entries):
+            if id(victim) in planned:
+                planned.discard(id(victim))
                 promised = [0] * len(self.manager.groups)
                 self._preempt(victim, plan)
                 budget = cfg.max_batched_tokens
@@ -220,7 +236,7 @@ class Scheduler:
         for r in self.running:
             if budget <= 0 or len(plan.entries) >= cfg.max_batch_size:
                 break
-            if any(e.request is r for e in plan.entries) or r.pending <= 0:
+            if id(r) in planned or r.pending <= 0:
                 continue
             self._plan_portion(r, plan, promised, budget, opened=True)
             budget = cfg.max_batched_tokens - plan.n_tokens
@@ -255,7 +271,7 @@ class Scheduler:
         if n < want:
             self.counters["shrunk_portions"] += 1
         self._promise(r, n, promised, opened)
-        toks = r.tokens[r.computed: r.computed + n]
+        toks = r.span(r.computed, r.computed + n)
         plan.entries.append(PlannedEntry(r, toks, samples=(r.computed + n == len(r.prompt) + len(r.output))))
 
     # ------------------------------------------------------------------ after the step

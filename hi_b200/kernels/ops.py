@@ -445,6 +445,24 @@ def check_tc_status(device=None) -> None:
             raise KernelError(f"tcgen05 grouped product gave up a bounded wait: {where}; its output is invalid")
 
 
+class PendingStatus:
+    """The status word copied to pinned memory behind the step's kernels; read it later."""
+
+    def __init__(self, device: torch.device):
+        self.host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self.event = torch.cuda.Event()
+        self.device = device
+
+    def enqueue(self) -> None:
+        self.host.copy_(_tc_status(self.device), non_blocking=True)
+        self.event.record()
+
+    def resolve(self) -> None:
+        self.event.synchronize()
+        if int(self.host[0]) != 0:
+            check_tc_status()          # raises with the reason, and clears the word
+
+
 def moe_tc_supported(x: torch.Tensor, w_gate: torch.Tensor) -> bool:
     """The tensor-core expert kernels take bfloat16 with hidden and intermediate sizes that are
     multiples of 8 (TMA needs 16-byte row strides)."""

@@ -75,6 +75,7 @@ class SigmoidRoutedExperts(Part):
     FEW_ROWS = 16    # up to this many routed rows the weight-streaming kernel is used (measured: above
                      # it the tcgen05 kernel streams the expert weights faster, even with nearly empty tiles)
     wants_f32_input = True   # the router reads the norm's float32 output
+    OVERLAP_SHARED = True    # run the shared expert on a second stream beside the routed path
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -85,6 +86,7 @@ class SigmoidRoutedExperts(Part):
         self.shared = _SwiGLU(f"{prefix}.shared_expert", self.hidden, self.inter) \
             if params.get("shared_expert", True) else None
         self.w_router = self.w_gate = self.w_up = self.w_down = None
+        self._side_stream = None
 
     def tensor_specs(self):
         e, i, h, p = self.experts, self.inter, self.hidden, self.prefix
@@ -112,8 +114,26 @@ class SigmoidRoutedExperts(Part):
         if self.shared:
             self.shared.load(fetch)
 
+    def _shared_on_side_stream(self, normed):
+        """The shared expert has no dependency on the routing: it runs on a second stream beside
+        the router, the plan and the routed experts (in a captured step: a parallel branch), and
+        joins before the sum. Both paths stream weights; together they keep HBM busier than in turn."""
+        cur = torch.cuda.current_stream()
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=normed.device)
+        side = self._side_stream
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            shared = self.shared.forward(normed)
+        normed.record_stream(side)
+        shared.record_stream(cur)
+        return shared, side
+
     def forward(self, normed, ctx, normed_f32=None):
         n = normed.shape[0]
+        side = None
+        if self.shared and self.OVERLAP_SHARED:
+            shared, side = self._shared_on_side_stream(normed)
         ids, scores, _ = ops.router_topk(normed if normed_f32 is None else normed_f32, self.w_router, self.top_k)
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.router_ids", ids)
@@ -127,6 +147,9 @@ class SigmoidRoutedExperts(Part):
         else:
             act = ops.moe_gate_up(normed, plan, self.top_k, self.w_gate, self.w_up, scores, few)
             y = ops.moe_down(act, self.w_down, plan, few)
-        shared = self.shared.forward(normed) if self.shared else None
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+        else:
+            shared = self.shared.forward(normed) if self.shared else None
         # the sum shared + routed rows is taken inside the next norm's residual add
         return Pending(dense=shared, routed=y, slot_of_entry=plan.slot_of_entry, top_k=self.top_k)

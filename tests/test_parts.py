@@ -177,3 +177,42 @@ def test_embedding_and_head(dt, tol):
     own = build("head", PartSpec("linear_head", {"vocab_size": V, "hidden_size": H}), env(dt, H), "head")
     wh = fill(own, dt, 7)["head.weight"]
     close(own.forward(z.to(DEV), emb), z.float() @ wh.float().T, 1e-5 if dt == torch.float32 else 2e-3, "own head")
+
+
+@pytest.mark.parametrize("dt,tol", DT)
+def test_block_arrangement(dt, tol):
+    """One pre-norm block built from a LayerSpec (attention + dense SwiGLU + two norms), with a pending
+    sum carried in, against h = x + attn(norm(x)); y = h + ffn(norm(h))."""
+    from hi_b200.parts.context import CacheView
+    from hi_b200.parts.model import Layer
+    from hi_b200.parts.spec import LayerSpec, PartSpec
+
+    H, nh, nkv, hd, page, T = 64, 4, 2, 16, 8, 21
+    norm = lambda n: PartSpec("rmsnorm", {"name": n, "size": H, "eps": 1e-5})
+    spec = LayerSpec(prefix="L", norm_mixer=norm("n1"), norm_feed_forward=norm("n2"),
+                     mixer=PartSpec("attention", {"name": "att", "hidden_size": H, "num_heads": nh, "num_kv_heads": nkv,
+                                                  "head_dim": hd, "window": None}),
+                     feed_forward=PartSpec("dense_swiglu", {"name": "ff", "hidden_size": H, "intermediate_size": 96}))
+    layer = Layer(spec, env(dt, H))
+    w = {}
+    for part in layer.parts():
+        w.update(fill(part, dt, 9, std=0.12))
+    x = torch.randn(T, H)
+    carried = (torch.randn(T, H) * 0.5).to(dt)
+    blocks = -(-T // page)
+    view = CacheView(group=0, k_pages=torch.zeros(blocks, nkv, page, hd, dtype=dt, device=DEV),
+                     v_pages=torch.zeros(blocks, nkv, page, hd, dtype=dt, device=DEV))
+    ctx = ctx_for([T], [0], page, {0: torch.arange(blocks, dtype=torch.int32).reshape(1, blocks)})
+    residual = x.clone().to(DEV)
+    residual, pending = layer.arrangement.forward(layer, residual, carried.to(DEV), ctx, view)
+    got = residual.cpu() + pending.float().cpu()
+    # plain
+    x0 = x + carried.float()
+    q = (plain.rms_norm(x0, w["L.n1.weight"], 1e-5) @ w["L.att.q_proj.weight"].float().T).view(T, nh, hd)
+    n1 = plain.rms_norm(x0, w["L.n1.weight"], 1e-5)
+    k = (n1 @ w["L.att.k_proj.weight"].float().T).view(T, nkv, hd)
+    v = (n1 @ w["L.att.v_proj.weight"].float().T).view(T, nkv, hd)
+    a = plain.attention_core(q, k, v, None) @ w["L.att.o_proj.weight"].float().T
+    hmid = x0 + a
+    want = hmid + plain.dense_feed_forward(w, "L.ff", plain.rms_norm(hmid, w["L.n2.weight"], 1e-5))
+    close(got, want, tol, "pre-norm block")
