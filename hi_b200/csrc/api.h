@@ -41,6 +41,11 @@ int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages
                          int max_new, int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,
                          int skip_single, cudaStream_t stream);
 
+int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                            int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_tokens,
+                            int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
+                            int window, float scale, int skip_single, int* status, cudaStream_t stream);
+
 int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
                    int top_k, float* logits_out, int* ids, float* scores, cudaStream_t stream);
 int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,

@@ -1,0 +1,463 @@
+// Prefill attention on the 5th-generation tensor cores (tcgen05), bfloat16: portions of prompts of
+// at least a tile of new tokens against the paged cache. One block = 128 consecutive new tokens
+// of one request and one query head:
+//   warp 0      one lane issues TMA loads: the Q tile once, then K and V tiles of 128 key positions
+//               (one box per page, 128-byte swizzle) into a 2-stage ring;
+//   warp 1      allocates tensor memory; one lane issues S = Q K^T (tcgen05.mma, M 128, N 128) into
+//               one of two S buffers and, a tile behind, O += P V (P from shared memory, V as the
+//               MN-major operand), so the next S is computed while the softmax works on this one;
+//   warps 2..5  softmax: thread r owns row r (tensor-memory lane r): it reads its S row with
+//               tcgen05.ld, masks by absolute position (causal, chunk, sliding window), keeps the
+//               running max and sum in float32, rescales its O row in tensor memory when the max
+//               moved, and writes P as bfloat16 into shared memory in the swizzled K-major layout.
+// Every mbarrier wait is bounded; on a time-out a code goes to `status` and the block leaves
+// through the common exit, where tensor memory is freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int BQ = 128;          // query rows per block (UMMA M)
+constexpr int BKEYS = 128;       // key positions per tile
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) __nanosleep(40);
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory descriptors, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
+//   K-major (Q, K, P): the 16 k-elements of one MMA are 32 bytes inside a row; advance by 32 bytes.
+//   MN-major (V): rows are key positions (the MMA's k), the 64 contiguous elements of a row are
+//   head dims (the MMA's n); the second block of 64 dims lies `lbo_bytes` further on.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo_bytes) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+
+struct Args {
+  const int* block_table;
+  const int* cu_seqlens;
+  const int* positions;
+  __nv_bfloat16* out;
+  int* status;
+  int table_stride, nh, nkv, page_size, chunk, window, skip_single, box_rows;
+  float scale_log2;          // softmax scale * log2(e)
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const Args a) {
+  constexpr int DBLK = HD / 64;                 // 64-dim blocks of a row
+  constexpr int QBYTES = BQ * HD * 2, KBYTES = BKEYS * HD * 2, PBYTES = BQ * BKEYS * 2;
+  constexpr int BLOCK64 = 128 * 128;            // bytes of one [128 rows x 64 elements] swizzled block
+  constexpr int S_COLS = BKEYS;                 // columns of one S buffer
+  constexpr int TMEM_COLS = 512;                // S0, S1, O
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = q_s + QBYTES;                 // [2 stages][K | V]
+  uint8_t* p_s = kv_s + 4 * KBYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + PBYTES);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* kv_full = bars + 1;       // 2
+  uint64_t* kv_empty = bars + 3;      // 2
+  uint64_t* s_full = bars + 5;        // 2
+  uint64_t* s_free = bars + 7;        // 2
+  uint64_t* p_ready = bars + 9;       // 1
+  uint64_t* pv_done = bars + 10;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+
+  const int seq = blockIdx.z, h = blockIdx.y;
+  const int qt = gridDim.x - 1 - blockIdx.x;    // later tiles read more keys: start them first
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq_begin = a.cu_seqlens[seq], seq_end = a.cu_seqlens[seq + 1];
+  const int tok0 = seq_begin + qt * BQ;
+  const int n_valid = min(BQ, seq_end - tok0);
+  if (n_valid <= 0) return;
+  if (a.skip_single && seq_end - seq_begin == 1) return;
+  const int kvh = h / (a.nh / a.nkv);
+  const int p_first = a.positions[tok0];
+  const int p_last = p_first + n_valid - 1;
+  auto first_visible = [&](int pos) {
+    int lo = 0;
+    if (a.chunk > 0) lo = (pos / a.chunk) * a.chunk;
+    if (a.window > 0 && pos - a.window + 1 > lo) lo = pos - a.window + 1;
+    return lo;
+  };
+  const int tile_begin = first_visible(p_first) / BKEYS;
+  const int nt = p_last / BKEYS - tile_begin + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4);
+    }
+    mbar_init(p_ready, 4);
+    mbar_init(pv_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_o = tmem + 2 * S_COLS;
+
+  if (warp == 0) {
+    if (lane == 0) {                            // ---- TMA producer
+      const int* table = a.block_table + (size_t)seq * a.table_stride;
+      mbar_expect_tx(q_full, QBYTES);
+      for (int c = 0; c < DBLK; ++c) tma_load_2d(q_s + c * BLOCK64, &map_q, h * HD + c * 64, tok0, q_full);
+      const int boxes = BKEYS / a.box_rows;
+      for (int j = 0; j < nt; ++j) {
+        const int s = j & 1;
+        if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) - 1) & 1)) { atomicExch(a.status, 11); break; }
+        uint8_t* ks = kv_s + s * 2 * KBYTES;
+        uint8_t* vs = ks + KBYTES;
+        mbar_expect_tx(&kv_full[s], 2 * KBYTES);
+        for (int b = 0; b < boxes; ++b) {
+          const int key0 = (tile_begin + j) * BKEYS + b * a.box_rows;
+          int page = key0 <= p_last ? table[key0 / a.page_size] : -1;
+          // keys past the portion's last position (or without a page) are masked: any row will do
+          const int row = page >= 0 ? (page * a.nkv + kvh) * a.page_size + key0 % a.page_size : 0;
+          for (int c = 0; c < DBLK; ++c) {
+            tma_load_2d(ks + c * BLOCK64 + b * a.box_rows * 128, &map_k, c * 64, row, &kv_full[s]);
+            tma_load_2d(vs + c * BLOCK64 + b * a.box_rows * 128, &map_v, c * 64, row, &kv_full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {                            // ---- MMA issuer: S_j = Q K_j^T, then O += P_{j-1} V_{j-1}
+      constexpr uint32_t idesc_qk = idesc_f16(BQ, BKEYS, false);
+      constexpr uint32_t idesc_pv = idesc_f16(BQ, HD, true);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) atomicExch(a.status, 12);
+      tc_fence_after();
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      for (int j = 0; j <= nt && ok; ++j) {
+        if (j < nt) {
+          const int s = j & 1;
+          if (!mbar_wait(&kv_full[s], (j >> 1) & 1)) { atomicExch(a.status, 13); ok = false; break; }
+          if (j >= 2 && !mbar_wait(&s_free[s], ((j >> 1) - 1) & 1)) { atomicExch(a.status, 14); ok = false; break; }
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(kv_s + s * 2 * KBYTES);
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k) {
+            const uint32_t off = (k / 4) * BLOCK64 + (k % 4) * 32;
+            tc_mma(tmem + s * S_COLS, desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_qk, k != 0);
+          }
+          tc_commit(&s_full[s]);
+        }
+        if (j >= 1) {
+          const int i = j - 1, s = i & 1;
+          if (!mbar_wait(p_ready, i & 1)) { atomicExch(a.status, 15); ok = false; break; }
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(kv_s + s * 2 * KBYTES + KBYTES);
+#pragma unroll
+          for (int k = 0; k < BKEYS / 16; ++k) {
+            const uint32_t p_off = (k / 4) * BLOCK64 + (k % 4) * 32;
+            tc_mma(tmem_o, desc_kmajor(p_addr + p_off), desc_mnmajor(v_addr + k * 2048, BLOCK64), idesc_pv,
+                   (i | k) != 0);
+          }
+          tc_commit(&kv_empty[s]);
+          tc_commit(pv_done);
+        }
+      }
+    }
+  } else {                                      // ---- softmax: thread = row = tensor-memory lane
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const bool row_ok = r < n_valid;
+    const int pos = p_first + r;
+    const int lo = first_visible(pos);
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nt && ok; ++j) {
+      const int sb = j & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1))) {
+        if (lane == 0) atomicExch(a.status, 16);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int key_base = (tile_begin + j) * BKEYS;
+      float sv[BKEYS];
+      float mx = m;
+#pragma unroll
+      for (int c = 0; c < BKEYS; c += 32) {
+        float v[32];
+        tc_ld32(tmem + lane_addr + sb * S_COLS + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key_base + c + i;
+          const float s = (row_ok && key <= pos && key >= lo) ? v[i] * a.scale_log2 : -INFINITY;
+          sv[c + i] = s;
+          mx = fmaxf(mx, s);
+        }
+      }
+      // the S buffer may be overwritten by the MMA two tiles on
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[sb]);
+      const float corr = (m == -INFINITY) ? 0.f : exp2f(m - mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < BKEYS; ++i) {
+        const float p = (sv[i] == -INFINITY) ? 0.f : exp2f(sv[i] - mx);
+        sv[i] = p;
+        sum += p;
+      }
+      l = l * corr + sum;
+      m = mx;
+      if (j > 0) {
+        // the previous P V product must have finished: O is stable and the P buffer is free
+        if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1))) {
+          if (lane == 0) atomicExch(a.status, 17);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < HD; c += 32) {
+            float o[32];
+            tc_ld32(tmem_o + lane_addr + c, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= corr;
+            tc_st32(tmem_o + lane_addr + c, o);
+          }
+        }
+      }
+      // P row r, bfloat16, K-major with the 128-byte swizzle: 16-byte chunk q of row r sits at chunk q ^ (r % 8)
+      uint8_t* prow = p_s + (r / 8) * 1024 + (r % 8) * 128;
+#pragma unroll
+      for (int q = 0; q < BKEYS / 8; ++q) {
+        uint4 pack;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&pack);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 hh = __floats2bfloat162_rn(sv[q * 8 + 2 * i], sv[q * 8 + 2 * i + 1]);
+          w[i] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        const int blk = q / 8, cq = q % 8;
+        *reinterpret_cast<uint4*>(prow + blk * BLOCK64 + ((cq ^ (r % 8)) * 16)) = pack;
+      }
+      if (j == nt - 1 && key_base + r > p_last) {
+        // Value rows of positions past the portion's end hold whatever the page held before
+        // (another request's numbers, possibly not finite): P is zero there, but 0 x NaN is NaN.
+        // The tile has landed (its S has been computed from it); zero this thread's row.
+        uint8_t* vrow = kv_s + sb * 2 * KBYTES + KBYTES + (r / 8) * 1024 + (r % 8) * 128;
+#pragma unroll
+        for (int blk = 0; blk < DBLK; ++blk)
+#pragma unroll
+          for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(vrow + blk * BLOCK64 + q * 16) = make_uint4(0, 0, 0, 0);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    if (ok) {
+      if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (nt - 1) & 1))) {
+        if (lane == 0) atomicExch(a.status, 18);
+      } else {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst = a.out + ((size_t)(tok0 + r) * a.nh + h) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          float o[32];
+          tc_ld32(tmem_o + lane_addr + c, o);
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 pack;
+              uint32_t* w = reinterpret_cast<uint32_t*>(&pack);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(o[i + 2 * e] * inv, o[i + 2 * e + 1] * inv);
+                w[e] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+              *reinterpret_cast<uint4*>(dst + c + i) = pack;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+// [rows, cols] bfloat16 row-major, box [box_rows, 64 elements], 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return HB_ERR_UNSUPPORTED;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? HB_OK : HB_ERR_BAD_ARG;
+}
+
+template <int HD>
+int launch(const void* q, const void* k_pages, const void* v_pages, const Args& a, int n_tokens, long long pool_rows,
+           int n_seqs, int max_new, cudaStream_t stream) {
+  CUtensorMap mq, mk, mv;
+  int rc = make_map(&mq, q, (uint64_t)n_tokens, (uint64_t)a.nh * HD, BQ);
+  if (rc != HB_OK) return rc;
+  rc = make_map(&mk, k_pages, (uint64_t)pool_rows, HD, a.box_rows);
+  if (rc != HB_OK) return rc;
+  rc = make_map(&mv, v_pages, (uint64_t)pool_rows, HD, a.box_rows);
+  if (rc != HB_OK) return rc;
+  const size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKEYS * HD * 2 + (size_t)BQ * BKEYS * 2 + 1024 + 256;
+  cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid((max_new + BQ - 1) / BQ, a.nh, n_seqs);
+  attn_prefill_tc_kernel<HD><<<grid, THREADS, smem, stream>>>(mq, mk, mv, a);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+}  // namespace
+
+// bfloat16, head_dim 64 or 128, page_size a multiple of 16 that divides 128 or is a multiple of it.
+// Arguments as hb_attention_prefill, plus the number of rows of `q`, the number of pages of the
+// pools, and `status` (one int on the device, zero before the call; nonzero afterwards = a wait
+// timed out). HB_ERR_UNSUPPORTED for other shapes: the caller uses hb_attention_prefill.
+extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                       int table_stride, const int* cu_seqlens, const int* positions, void* out,
+                                       int n_tokens, int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd,
+                                       int page_size, int chunk, int window, float scale, int skip_single, int* status,
+                                       cudaStream_t stream) {
+  if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out || !status) return HB_ERR_BAD_ARG;
+  if (n_tokens < 0 || n_pages <= 0 || n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 ||
+      page_size <= 0 || table_stride <= 0 || chunk < 0 || window < 0)
+    return HB_ERR_BAD_ARG;
+  if (page_size % 16 != 0 || !(BKEYS % page_size == 0 || page_size % BKEYS == 0)) return HB_ERR_UNSUPPORTED;
+  if (n_seqs > 65535 || nh > 65535) return HB_ERR_UNSUPPORTED;
+  if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return HB_OK;
+  Args a{block_table, cu_seqlens, positions, (__nv_bfloat16*)out, status, table_stride, nh, nkv, page_size, chunk,
+         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f};
+  const long long pool_rows = (long long)n_pages * nkv * page_size;
+  if (hd == 128) return launch<128>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
+  if (hd == 64) return launch<64>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
+  return HB_ERR_UNSUPPORTED;
+}

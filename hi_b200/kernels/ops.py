@@ -26,6 +26,7 @@ _SIGNATURES = {
     "hb_attention_merge": [P, P, P, I, I, I, I, P],
     "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
     "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, P],
@@ -345,6 +346,43 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     return out
 
 
+PREFILL_TC_MIN_TOKENS = 128     # a request needs at least a tile of new tokens for the tcgen05 kernel to pay
+
+
+def prefill_attention_tc_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:
+    """Shapes the tcgen05 prefill kernel takes: bfloat16, head_dim 64 or 128, pages of 16, 32, 64
+    or a multiple of 128 positions (a 128-key tile is loaded page by page with TMA)."""
+    return q_dtype == torch.bfloat16 and hd in (64, 128) and nh % nkv == 0 and page_size % 16 == 0 and \
+        (128 % page_size == 0 or page_size % 128 == 0)
+
+
+def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                         cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, max_new: int, chunk: int,
+                         window: int, scale: float, skip_single: bool = False,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """As :func:`prefill_attention`, on tcgen05 (S, P V and O in tensor memory, TMA page loads)."""
+    _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
+    for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
+        _need(t, nm, torch.int32)
+    n, nh, hd = q.shape
+    n_pages, nkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd or k_pages.shape != v_pages.shape:
+        raise KernelError("cache pages do not match the query's head_dim")
+    if not prefill_attention_tc_supported(q.dtype, nh, nkv, hd, page_size):
+        raise KernelError(f"tcgen05 prefill attention does not take nh={nh} nkv={nkv} head_dim={hd} page={page_size}")
+    if cu_seqlens.numel() != n_seqs + 1 or block_table.shape[0] < n_seqs:
+        raise KernelError("cu_seqlens / block_table do not match the number of requests")
+    if out is None:
+        out = torch.empty_like(q)
+    _check(lib().hb_attention_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                         block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(out), n, n_pages,
+                                         n_seqs, int(max_new), nh, nkv, hd, page_size, int(chunk), int(window),
+                                         float(scale), int(skip_single), _ptr(_tc_status(q.device)), _stream()),
+           "attention_prefill_tc")
+    TC_USED[0] = True
+    return out
+
+
 # --------------------------------------------------------------------------- experts
 def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool = False):
     """Router logits (float32), the top-k expert ids (ties to the lower id) and sigmoid scores."""
@@ -440,9 +478,12 @@ def check_tc_status(device=None) -> None:
         code = int(st.item())
         if code != 0:
             st.zero_()
-            where = {1: "the TMA producer waiting for a free stage", 2: "the MMA issuer waiting for a loaded stage",
-                     3: "the epilogue waiting for the accumulator"}.get(code, f"code {code}")
-            raise KernelError(f"tcgen05 grouped product gave up a bounded wait: {where}; its output is invalid")
+            where = {1: "grouped product: the TMA producer waiting for a free stage",
+                     2: "grouped product: the MMA issuer waiting for a loaded stage",
+                     3: "grouped product: the epilogue waiting for the accumulator",
+                     4: "grouped product: the MMA issuer waiting for a free accumulator"}.get(
+                code, f"prefill attention, wait {code}" if code >= 11 else f"code {code}")
+            raise KernelError(f"a tcgen05 kernel gave up a bounded wait ({where}); its output is invalid")
 
 
 class PendingStatus:

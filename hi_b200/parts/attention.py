@@ -89,8 +89,12 @@ class AttentionMixer(Part):
         elif ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, self.nh, self.nkv, self.hd):
             # portions of prompts (single tokens of other requests ride along as one-row tiles)
             single = ctx.decode_rows is not None and ops.decode_attention_supported(q.dtype, self.nh, self.nkv, self.hd)
-            o = ops.prefill_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
-                                      ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale, skip_single=single)
+            # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync
+            tc = ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS and ops.prefill_attention_tc_supported(
+                q.dtype, self.nh, self.nkv, self.hd, ctx.page_size)
+            kernel = ops.prefill_attention_tc if tc else ops.prefill_attention
+            o = kernel(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
+                       ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale, skip_single=single)
             if single:
                 # single tokens beside portions: their long key ranges go through the split decode kernel
                 rows = ctx.decode_rows

@@ -66,7 +66,7 @@ def test_swiglu(dt, tol):
 
 
 def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, interleaved, qk_norm, temp, seed,
-               split=True):
+               split=True, tc=False):
     """Two phases: fill `starts` tokens of every sequence, then run `lens` new tokens; returns the
     kernel's q and attention output for the second phase and the plain reference's."""
     g = torch.Generator().manual_seed(seed)
@@ -101,6 +101,9 @@ def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, 
             fast = o.prefill_attention(q, kp, vp, bt.to(DEV), cu.to(DEV), pos.to(DEV), S, max(b - a for a, b in spans),
                                        chunk, window, hd ** -0.5)
             got = (q, out, fast)
+            if tc:
+                got = got + (o.prefill_attention_tc(q, kp, vp, bt.to(DEV), cu.to(DEV), pos.to(DEV), S,
+                                                    max(b - a for a, b in spans), chunk, window, hd ** -0.5),)
     # plain: whole sequences
     want_q, want_o = [], []
     for s in range(S):
@@ -203,6 +206,23 @@ def test_decode_attention_on_tensor_cores(shape):
     close(general, want, 2e-2, f"general attention {shape}")
     assert not o.decode_attention_supported(torch.float32, nh, nkv, hd)
     assert not o.decode_attention_supported(torch.bfloat16, 40, 2, 128) and not o.decode_attention_supported(torch.bfloat16, 4, 2, 48)
+
+
+@pytest.mark.parametrize("shape", [(4, 2, 128, 64, 0, 0), (4, 2, 128, 16, 100, 0), (8, 2, 64, 32, 0, 50),
+                                   (2, 1, 128, 128, 0, 0), (2, 2, 64, 256, 300, 0), (5, 1, 128, 64, 256, 0)])
+def test_prefill_attention_on_tcgen05(shape):
+    """The tcgen05 prefill kernel (TMA page loads, S / P V / O in tensor memory) against whole-sequence
+    attention: portions that start inside a sequence, straddle chunks and pages, and end off a tile."""
+    o = ops()
+    nh, nkv, hd, page, chunk, window = shape
+    dt = torch.bfloat16
+    assert o.prefill_attention_tc_supported(dt, nh, nkv, hd, page)
+    inv = plain.rope_inverse_frequencies(hd, 10000.0, None)
+    got, want = paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens=[300, 140, 1, 129], starts=[0, 77, 500, 128],
+                           inv_freq=inv, interleaved=False, qk_norm=True, temp=None, seed=hd + page, split=True, tc=True)
+    o.check_tc_status()
+    close(got[3], want[1].reshape(got[3].shape), 2e-2, f"tcgen05 prefill attention {shape}")
+    close(got[1], want[1].reshape(got[1].shape), 2e-2, f"general attention {shape}")
 
 
 @pytest.mark.parametrize("dt,tol", DT)
