@@ -1,9 +1,9 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05), bfloat16: portions of prompts of
 // at least a tile of new tokens against the paged cache. One block = 128 consecutive new tokens
 // of one request and one query head:
-//   warp 0      one lane issues TMA loads: the Q tile once, then K and V tiles of 128 key positions
+//   warp 0      one lane issues TMA loads: the Q tile once, then K and V tiles of 64 key positions
 //               (one box per page, 128-byte swizzle) into a 2-stage ring;
-//   warp 1      allocates tensor memory; one lane issues S = Q K^T (tcgen05.mma, M 128, N 128) into
+//   warp 1      allocates tensor memory; one lane issues S = Q K^T (tcgen05.mma, M 128, N 64) into
 //               one of two S buffers and, a tile behind, O += P V (P from shared memory, V as the
 //               MN-major operand), so the next S is computed while the softmax works on this one;
 //   warps 2..5  softmax: thread r owns row r (tensor-memory lane r): it reads its S row with
@@ -22,7 +22,7 @@
 namespace {
 
 constexpr int BQ = 128;          // query rows per block (UMMA M)
-constexpr int BKEYS = 128;       // key positions per tile
+constexpr int BKEYS = 64;        // key positions per tile (two blocks per SM then fit: one does MMAs while the other's softmax runs)
 constexpr int THREADS = 192;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
@@ -56,6 +56,11 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -133,16 +138,24 @@ struct Args {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const Args a) {
   constexpr int DBLK = HD / 64;                 // 64-dim blocks of a row
   constexpr int QBYTES = BQ * HD * 2, KBYTES = BKEYS * HD * 2, PBYTES = BQ * BKEYS * 2;
-  constexpr int BLOCK64 = 128 * 128;            // bytes of one [128 rows x 64 elements] swizzled block
+  constexpr int QBLOCK = BQ * 128;              // bytes of one [128 rows x 64 elements] swizzled block of Q
+  constexpr int KVBLOCK = BKEYS * 128;          // the same for a K or V tile (rows = key positions)
   constexpr int S_COLS = BKEYS;                 // columns of one S buffer
-  constexpr int TMEM_COLS = 512;                // S0, S1, O
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int TMEM_COLS = 256;                // S0, S1 (64 columns each), O (HD columns)
+  // No slack for aligning by hand: two blocks per SM only fit without it. The swizzled tiles need
+  // a 1024-byte aligned base, which dynamic shared memory has when the kernel has no static
+  // shared memory; if it ever has not, the block reports it and leaves.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(a.status, 19);
+    return;
+  }
   uint8_t* q_s = smem;
   uint8_t* kv_s = q_s + QBYTES;                 // [2 stages][K | V]
   uint8_t* p_s = kv_s + 4 * KBYTES;
@@ -201,7 +214,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {                            // ---- TMA producer
       const int* table = a.block_table + (size_t)seq * a.table_stride;
       mbar_expect_tx(q_full, QBYTES);
-      for (int c = 0; c < DBLK; ++c) tma_load_2d(q_s + c * BLOCK64, &map_q, h * HD + c * 64, tok0, q_full);
+      for (int c = 0; c < DBLK; ++c) tma_load_2d(q_s + c * QBLOCK, &map_q, h * HD + c * 64, tok0, q_full);
       const int boxes = BKEYS / a.box_rows;
       for (int j = 0; j < nt; ++j) {
         const int s = j & 1;
@@ -215,8 +228,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // keys past the portion's last position (or without a page) are masked: any row will do
           const int row = page >= 0 ? (page * a.nkv + kvh) * a.page_size + key0 % a.page_size : 0;
           for (int c = 0; c < DBLK; ++c) {
-            tma_load_2d(ks + c * BLOCK64 + b * a.box_rows * 128, &map_k, c * 64, row, &kv_full[s]);
-            tma_load_2d(vs + c * BLOCK64 + b * a.box_rows * 128, &map_v, c * 64, row, &kv_full[s]);
+            tma_load_2d(ks + c * KVBLOCK + b * a.box_rows * 128, &map_k, c * 64, row, &kv_full[s]);
+            tma_load_2d(vs + c * KVBLOCK + b * a.box_rows * 128, &map_v, c * 64, row, &kv_full[s]);
           }
         }
       }
@@ -238,8 +251,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const uint32_t k_addr = smem_u32(kv_s + s * 2 * KBYTES);
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) {
-            const uint32_t off = (k / 4) * BLOCK64 + (k % 4) * 32;
-            tc_mma(tmem + s * S_COLS, desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_qk, k != 0);
+            tc_mma(tmem + s * S_COLS, desc_kmajor(q_addr + (k / 4) * QBLOCK + (k % 4) * 32),
+                   desc_kmajor(k_addr + (k / 4) * KVBLOCK + (k % 4) * 32), idesc_qk, k != 0);
           }
           tc_commit(&s_full[s]);
         }
@@ -250,8 +263,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const uint32_t v_addr = smem_u32(kv_s + s * 2 * KBYTES + KBYTES);
 #pragma unroll
           for (int k = 0; k < BKEYS / 16; ++k) {
-            const uint32_t p_off = (k / 4) * BLOCK64 + (k % 4) * 32;
-            tc_mma(tmem_o, desc_kmajor(p_addr + p_off), desc_mnmajor(v_addr + k * 2048, BLOCK64), idesc_pv,
+            tc_mma(tmem_o, desc_kmajor(p_addr + k * 32), desc_mnmajor(v_addr + k * 2048, KVBLOCK), idesc_pv,
                    (i | k) != 0);
           }
           tc_commit(&kv_empty[s]);
@@ -295,16 +307,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[sb]);
-      const float corr = (m == -INFINITY) ? 0.f : exp2f(m - mx);
+      // The exponentials are taken against `m`, which follows the true running max lazily: it
+      // moves (and O and l are rescaled) only when some row of the warp has grown by more than
+      // 2^8, so P stays below 256 and most tiles skip the pass over O. The result is the same
+      // sum, scaled by a common factor that the final division removes.
+      const bool move = __any_sync(0xffffffffu, mx > m + 8.f || m == -INFINITY);
+      float corr = 1.f;
+      if (move) {
+        corr = (m == -INFINITY) ? 0.f : fast_exp2(m - mx);
+        m = mx;
+      }
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < BKEYS; ++i) {
-        const float p = (sv[i] == -INFINITY) ? 0.f : exp2f(sv[i] - mx);
+        const float p = (sv[i] == -INFINITY) ? 0.f : fast_exp2(sv[i] - m);
         sv[i] = p;
         sum += p;
       }
       l = l * corr + sum;
-      m = mx;
       if (j > 0) {
         // the previous P V product must have finished: O is stable and the P buffer is free
         if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1))) {
@@ -313,7 +333,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           break;
         }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, corr != 1.f)) {
+        if (move) {
 #pragma unroll 1
           for (int c = 0; c < HD; c += 32) {
             float o[32];
@@ -335,10 +355,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           __nv_bfloat162 hh = __floats2bfloat162_rn(sv[q * 8 + 2 * i], sv[q * 8 + 2 * i + 1]);
           w[i] = *reinterpret_cast<uint32_t*>(&hh);
         }
-        const int blk = q / 8, cq = q % 8;
-        *reinterpret_cast<uint4*>(prow + blk * BLOCK64 + ((cq ^ (r % 8)) * 16)) = pack;
+        *reinterpret_cast<uint4*>(prow + ((q ^ (r % 8)) * 16)) = pack;
       }
-      if (j == nt - 1 && key_base + r > p_last) {
+      if (j == nt - 1 && r < BKEYS && key_base + r > p_last) {
         // Value rows of positions past the portion's end hold whatever the page held before
         // (another request's numbers, possibly not finite): P is zero there, but 0 x NaN is NaN.
         // The tile has landed (its S has been computed from it); zero this thread's row.
@@ -346,7 +365,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int blk = 0; blk < DBLK; ++blk)
 #pragma unroll
-          for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(vrow + blk * BLOCK64 + q * 16) = make_uint4(0, 0, 0, 0);
+          for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(vrow + blk * KVBLOCK + q * 16) = make_uint4(0, 0, 0, 0);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
       tc_fence_before();
@@ -427,7 +446,7 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const Args& 
   if (rc != HB_OK) return rc;
   rc = make_map(&mv, v_pages, (uint64_t)pool_rows, HD, a.box_rows);
   if (rc != HB_OK) return rc;
-  const size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKEYS * HD * 2 + (size_t)BQ * BKEYS * 2 + 1024 + 256;
+  const size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKEYS * HD * 2 + (size_t)BQ * BKEYS * 2 + 256;
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid((max_new + BQ - 1) / BQ, a.nh, n_seqs);
@@ -438,7 +457,7 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const Args& 
 
 }  // namespace
 
-// bfloat16, head_dim 64 or 128, page_size a multiple of 16 that divides 128 or is a multiple of it.
+// bfloat16, head_dim 64 or 128, page_size a multiple of 16 that divides 64 or is a multiple of it.
 // Arguments as hb_attention_prefill, plus the number of rows of `q`, the number of pages of the
 // pools, and `status` (one int on the device, zero before the call; nonzero afterwards = a wait
 // timed out). HB_ERR_UNSUPPORTED for other shapes: the caller uses hb_attention_prefill.

@@ -350,10 +350,10 @@ PREFILL_TC_MIN_TOKENS = 128     # a request needs at least a tile of new tokens 
 
 
 def prefill_attention_tc_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int, page_size: int) -> bool:
-    """Shapes the tcgen05 prefill kernel takes: bfloat16, head_dim 64 or 128, pages of 16, 32, 64
-    or a multiple of 128 positions (a 128-key tile is loaded page by page with TMA)."""
+    """Shapes the tcgen05 prefill kernel takes: bfloat16, head_dim 64 or 128, pages of 16, 32 or a
+    multiple of 64 positions (a 64-key tile is loaded page by page with TMA)."""
     return q_dtype == torch.bfloat16 and hd in (64, 128) and nh % nkv == 0 and page_size % 16 == 0 and \
-        (128 % page_size == 0 or page_size % 128 == 0)
+        (64 % page_size == 0 or page_size % 64 == 0)
 
 
 def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
