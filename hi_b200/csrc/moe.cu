@@ -74,6 +74,103 @@ __global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restric
   }
 }
 
+// Many tokens: a block stages TOK float32 rows of x in shared memory and walks the router rows
+// once for all of them (the one-token kernel re-reads the whole router per token). Per-token
+// arithmetic and its order (lane-strided partial sums, then the warp tree) do not depend on TOK.
+template <typename TW, int TOK>
+__global__ void router_topk_tiled_kernel(const float* __restrict__ x, const TW* __restrict__ w, int n, int hidden,
+                                         int experts, int top_k, float* __restrict__ logits_out,
+                                         int* __restrict__ ids, float* __restrict__ scores) {
+  extern __shared__ float tile_sm[];     // [TOK][hidden] rows, then [TOK][experts] logits
+  float* xs = tile_sm;
+  float* lg = tile_sm + (size_t)TOK * hidden;
+  const int t0 = blockIdx.x * TOK;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x * 4; i < TOK * hidden; i += blockDim.x * 4) {
+    const int tt = i / hidden, j = i - tt * hidden;          // hidden % 8 == 0: a float4 stays in its row
+    const float4 v = t0 + tt < n ? *reinterpret_cast<const float4*>(x + (size_t)(t0 + tt) * hidden + j)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(xs + i) = v;
+  }
+  __syncthreads();
+  for (int e = warp; e < experts; e += nwarps) {
+    const TW* wr = w + (size_t)e * hidden;
+    float acc[TOK];
+#pragma unroll
+    for (int tt = 0; tt < TOK; ++tt) acc[tt] = 0.f;
+    auto fma_chunk = [&](int j, const float (&wv)[8]) {
+#pragma unroll
+      for (int tt = 0; tt < TOK; ++tt) {
+        const float4 a = *reinterpret_cast<const float4*>(xs + tt * hidden + j);
+        const float4 b = *reinterpret_cast<const float4*>(xs + tt * hidden + j + 4);
+        acc[tt] += a.x * wv[0]; acc[tt] += a.y * wv[1]; acc[tt] += a.z * wv[2]; acc[tt] += a.w * wv[3];
+        acc[tt] += b.x * wv[4]; acc[tt] += b.y * wv[5]; acc[tt] += b.z * wv[6]; acc[tt] += b.w * wv[7];
+      }
+    };
+    int j = lane * 8;
+    for (; j + 768 < hidden; j += 1024) {        // four router loads in flight per lane
+      float wv[4][8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) hb::load8(wr + j + 256 * q, wv[q]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) fma_chunk(j + 256 * q, wv[q]);
+    }
+    for (; j < hidden; j += 256) {
+      float wv[8];
+      hb::load8(wr + j, wv);
+      fma_chunk(j, wv);
+    }
+#pragma unroll
+    for (int tt = 0; tt < TOK; ++tt) {
+      const float sdot = hb::warp_sum(acc[tt]);
+      if (lane == 0) {
+        lg[tt * experts + e] = sdot;
+        if (logits_out && t0 + tt < n) logits_out[(size_t)(t0 + tt) * experts + e] = sdot;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < TOK && t0 + threadIdx.x < n) {
+    const int t = t0 + threadIdx.x;
+    const float* row = lg + threadIdx.x * experts;
+    for (int r = 0; r < top_k; ++r) {
+      int best = -1;
+      float bv = 0.f;
+      for (int e = 0; e < experts; ++e) {
+        bool taken = false;
+        for (int q = 0; q < r; ++q) taken |= (ids[(size_t)t * top_k + q] == e);
+        if (taken) continue;
+        const float v = row[e];
+        if (best < 0 || v > bv) { best = e; bv = v; }
+      }
+      ids[(size_t)t * top_k + r] = best;
+      scores[(size_t)t * top_k + r] = 1.f / (1.f + expf(-bv));
+    }
+  }
+}
+
+// Top-k and sigmoid from given float32 logits [n, experts]: one thread per token (the logits of
+// many tokens come from one library matrix product; ties go to the lower id as above).
+__global__ void topk_sigmoid_kernel(const float* __restrict__ logits, int n, int experts, int top_k,
+                                    int* __restrict__ ids, float* __restrict__ scores) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const float* lg = logits + (size_t)t * experts;
+  for (int r = 0; r < top_k; ++r) {
+    int best = -1;
+    float bv = 0.f;
+    for (int e = 0; e < experts; ++e) {
+      bool taken = false;
+      for (int q = 0; q < r; ++q) taken |= (ids[(size_t)t * top_k + q] == e);
+      if (taken) continue;
+      const float v = lg[e];
+      if (best < 0 || v > bv) { best = e; bv = v; }
+    }
+    ids[(size_t)t * top_k + r] = best;
+    scores[(size_t)t * top_k + r] = 1.f / (1.f + expf(-bv));
+  }
+}
+
 // ------------------------------------------------------------------ plan
 // Stable counting sort of the n = tokens*top_k routing entries by expert, in one block:
 // offsets[e]..offsets[e+1] are the sorted slots of expert e, in entry order.
@@ -372,6 +469,30 @@ extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_d
     return HB_ERR_BAD_ARG;
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
   if (n == 0) return HB_OK;
+  if (x_dtype == HB_DTYPE_F32 && n >= 128 && hidden % 8 == 0) {
+    // many tokens: 4 rows of x per block in shared memory, the router rows read once per block
+    constexpr int TOK = 4;
+    const size_t tiled = ((size_t)TOK * hidden + (size_t)TOK * experts) * sizeof(float);
+    if (tiled <= 200 * 1024) {
+      const int blocks = (n + TOK - 1) / TOK;
+      cudaError_t e = cudaSuccess;
+      if (w_dtype == HB_DTYPE_F32) {
+        e = cudaFuncSetAttribute(router_topk_tiled_kernel<float, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled);
+        if (e != cudaSuccess) return (int)e;
+        router_topk_tiled_kernel<float, TOK><<<blocks, 512, tiled, stream>>>((const float*)x, (const float*)w, n, hidden,
+                                                                             experts, top_k, logits_out, ids, scores);
+      } else if (w_dtype == HB_DTYPE_BF16) {
+        e = cudaFuncSetAttribute(router_topk_tiled_kernel<__nv_bfloat16, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled);
+        if (e != cudaSuccess) return (int)e;
+        router_topk_tiled_kernel<__nv_bfloat16, TOK><<<blocks, 512, tiled, stream>>>(
+            (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores);
+      } else {
+        return HB_ERR_BAD_ARG;
+      }
+      HB_LAUNCH_CHECK();
+      return HB_OK;
+    }
+  }
   const size_t smem = (size_t)experts * sizeof(float);
   const int threads = experts >= 16 ? 512 : (experts >= 8 ? 256 : 128);   // a warp per expert where that fits
   if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_F32)
@@ -385,6 +506,15 @@ extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_d
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
   else
     return HB_ERR_BAD_ARG;
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_topk_sigmoid(const float* logits, int n, int experts, int top_k, int* ids, float* scores,
+                               cudaStream_t stream) {
+  if (!logits || !ids || !scores || n < 0 || experts <= 0 || top_k <= 0 || top_k > experts) return HB_ERR_BAD_ARG;
+  if (n == 0) return HB_OK;
+  topk_sigmoid_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, n, experts, top_k, ids, scores);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

@@ -45,24 +45,34 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
     dst = pool + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
   }
 
+  // Each lane takes two neighbouring pairs per step (j, j+1): its loads and stores are 4 bytes
+  // (bfloat16) or 8 bytes (float, or interleaved bfloat16) wide. half is even (head_dim % 16 == 0).
   float a[kMaxPairsPerLane], b[kMaxPairsPerLane];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxPairsPerLane; ++i) {
-    const int j = lane + 32 * i;
+  for (int i = 0; i < kMaxPairsPerLane; i += 2) {
+    const int j = 2 * lane + 32 * i;            // pairs j and j + 1
     if (j < half) {
-      const int ia = interleaved ? 2 * j : j;
-      const int ib = interleaved ? 2 * j + 1 : j + half;
-      float xa = hb::to_f32(src[ia]), xb = hb::to_f32(src[ib]);
-      if (kind != 2 && inv_freq != nullptr && j < rot_pairs) {
-        float s, c;
-        sincosf((float)pos * inv_freq[j], &s, &c);
-        const float ra = xa * c - xb * s;
-        const float rb = xb * c + xa * s;
-        xa = ra; xb = rb;
+      float xa[2], xb[2];
+      if (interleaved) {                        // elements 2j .. 2j+3: (a0, b0, a1, b1)
+        xa[0] = hb::to_f32(src[2 * j]); xb[0] = hb::to_f32(src[2 * j + 1]);
+        xa[1] = hb::to_f32(src[2 * j + 2]); xb[1] = hb::to_f32(src[2 * j + 3]);
+      } else {
+        xa[0] = hb::to_f32(src[j]); xa[1] = hb::to_f32(src[j + 1]);
+        xb[0] = hb::to_f32(src[j + half]); xb[1] = hb::to_f32(src[j + half + 1]);
       }
-      a[i] = xa; b[i] = xb;
-      ss += xa * xa + xb * xb;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (kind != 2 && inv_freq != nullptr) {
+          float sn, cs;
+          sincosf((float)pos * inv_freq[j + e], &sn, &cs);
+          const float ra = xa[e] * cs - xb[e] * sn;
+          const float rb = xb[e] * cs + xa[e] * sn;
+          xa[e] = ra; xb[e] = rb;
+        }
+        a[i + e] = xa[e]; b[i + e] = xb[e];
+        ss += xa[e] * xa[e] + xb[e] * xb[e];
+      }
     }
   }
   float mul = 1.f;
@@ -73,13 +83,16 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
   if (kind == 0 && temp_on)
     mul *= logf(floorf(((float)pos + 1.f) / floor_scale) + 1.f) * attn_scale + 1.f;
 #pragma unroll
-  for (int i = 0; i < kMaxPairsPerLane; ++i) {
-    const int j = lane + 32 * i;
+  for (int i = 0; i < kMaxPairsPerLane; i += 2) {
+    const int j = 2 * lane + 32 * i;
     if (j < half) {
-      const int ia = interleaved ? 2 * j : j;
-      const int ib = interleaved ? 2 * j + 1 : j + half;
-      dst[ia] = hb::from_f32<T>(a[i] * mul);
-      dst[ib] = hb::from_f32<T>(b[i] * mul);
+      if (interleaved) {
+        dst[2 * j] = hb::from_f32<T>(a[i] * mul); dst[2 * j + 1] = hb::from_f32<T>(b[i] * mul);
+        dst[2 * j + 2] = hb::from_f32<T>(a[i + 1] * mul); dst[2 * j + 3] = hb::from_f32<T>(b[i + 1] * mul);
+      } else {
+        dst[j] = hb::from_f32<T>(a[i] * mul); dst[j + 1] = hb::from_f32<T>(a[i + 1] * mul);
+        dst[j + half] = hb::from_f32<T>(b[i] * mul); dst[j + half + 1] = hb::from_f32<T>(b[i + 1] * mul);
+      }
     }
   }
 }
