@@ -18,113 +18,18 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "tc.cuh"
 
 namespace {
 
 constexpr int BQ = 128;          // query rows per block (UMMA M)
 constexpr int BKEYS = 64;        // key positions per tile (two blocks per SM then fit: one does MMAs while the other's softmax runs)
 constexpr int THREADS = 192;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(40);
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const float (&v)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
-        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
-        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
-        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
-        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
-        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
-        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
-        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory descriptors, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
-//   K-major (Q, K, P): the 16 k-elements of one MMA are 32 bytes inside a row; advance by 32 bytes.
-//   MN-major (V): rows are key positions (the MMA's k), the 64 contiguous elements of a row are
-//   head dims (the MMA's n); the second block of 64 dims lies `lbo_bytes` further on.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo_bytes) {
-  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
 }
 
 struct Args {
@@ -152,7 +57,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // shared memory; if it ever has not, the block reports it and leaves.
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  if ((smem_u32(smem) & 1023u) != 0) {
+  if ((tc::smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicExch(a.status, 19);
     return;
   }
@@ -161,13 +66,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint8_t* p_s = kv_s + 4 * KBYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + PBYTES);
   uint64_t* q_full = bars;            // 1
-  uint64_t* kv_full = bars + 1;       // 2
-  uint64_t* kv_empty = bars + 3;      // 2
-  uint64_t* s_full = bars + 5;        // 2
-  uint64_t* s_free = bars + 7;        // 2
-  uint64_t* p_ready = bars + 9;       // 1
-  uint64_t* pv_done = bars + 10;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_full = bars + 1;        // 2   K and V have barriers of their own: a K buffer is free
+  uint64_t* k_empty = bars + 3;       // 2   as soon as its S is computed, long before its V is used,
+  uint64_t* v_full = bars + 5;        // 2   so the next K load starts a whole softmax earlier
+  uint64_t* v_empty = bars + 7;       // 2
+  uint64_t* s_full = bars + 9;        // 2
+  uint64_t* s_free = bars + 11;       // 2
+  uint64_t* p_ready = bars + 13;      // 1
+  uint64_t* pv_done = bars + 14;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
 
   const int seq = blockIdx.z, h = blockIdx.y;
   const int qt = gridDim.x - 1 - blockIdx.x;    // later tiles read more keys: start them first
@@ -190,84 +97,90 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int nt = p_last / BKEYS - tile_begin + 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    tc::mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4);
+      tc::mbar_init(&k_full[i], 1); tc::mbar_init(&k_empty[i], 1);
+      tc::mbar_init(&v_full[i], 1); tc::mbar_init(&v_empty[i], 1);
+      tc::mbar_init(&s_full[i], 1); tc::mbar_init(&s_free[i], 4);
     }
-    mbar_init(p_ready, 4);
-    mbar_init(pv_done, 1);
+    tc::mbar_init(p_ready, 4);
+    tc::mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc::alloc(tmem_slot, TMEM_COLS);
   }
-  tc_fence_before();
+  tc::fence_before();
   __syncthreads();
-  tc_fence_after();
+  tc::fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_o = tmem + 2 * S_COLS;
 
   if (warp == 0) {
     if (lane == 0) {                            // ---- TMA producer
       const int* table = a.block_table + (size_t)seq * a.table_stride;
-      mbar_expect_tx(q_full, QBYTES);
-      for (int c = 0; c < DBLK; ++c) tma_load_2d(q_s + c * QBLOCK, &map_q, h * HD + c * 64, tok0, q_full);
+      tc::mbar_expect_tx(q_full, QBYTES);
+      for (int c = 0; c < DBLK; ++c) tc::tma_load_2d(q_s + c * QBLOCK, &map_q, h * HD + c * 64, tok0, q_full);
       const int boxes = BKEYS / a.box_rows;
       for (int j = 0; j < nt; ++j) {
         const int s = j & 1;
-        if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) - 1) & 1)) { atomicExch(a.status, 11); break; }
         uint8_t* ks = kv_s + s * 2 * KBYTES;
         uint8_t* vs = ks + KBYTES;
-        mbar_expect_tx(&kv_full[s], 2 * KBYTES);
+        int rows[BKEYS / 16];                   // first pool row of every box of this tile
         for (int b = 0; b < boxes; ++b) {
           const int key0 = (tile_begin + j) * BKEYS + b * a.box_rows;
-          int page = key0 <= p_last ? table[key0 / a.page_size] : -1;
+          const int page = key0 <= p_last ? table[key0 / a.page_size] : -1;
           // keys past the portion's last position (or without a page) are masked: any row will do
-          const int row = page >= 0 ? (page * a.nkv + kvh) * a.page_size + key0 % a.page_size : 0;
-          for (int c = 0; c < DBLK; ++c) {
-            tma_load_2d(ks + c * KVBLOCK + b * a.box_rows * 128, &map_k, c * 64, row, &kv_full[s]);
-            tma_load_2d(vs + c * KVBLOCK + b * a.box_rows * 128, &map_v, c * 64, row, &kv_full[s]);
-          }
+          rows[b] = page >= 0 ? (page * a.nkv + kvh) * a.page_size + key0 % a.page_size : 0;
         }
+        if (j >= 2 && !tc::mbar_wait(&k_empty[s], ((j >> 1) - 1) & 1)) { atomicExch(a.status, 11); break; }
+        tc::mbar_expect_tx(&k_full[s], KBYTES);
+        for (int b = 0; b < boxes; ++b)
+          for (int c = 0; c < DBLK; ++c)
+            tc::tma_load_2d(ks + c * KVBLOCK + b * a.box_rows * 128, &map_k, c * 64, rows[b], &k_full[s]);
+        if (j >= 2 && !tc::mbar_wait(&v_empty[s], ((j >> 1) - 1) & 1)) { atomicExch(a.status, 20); break; }
+        tc::mbar_expect_tx(&v_full[s], KBYTES);
+        for (int b = 0; b < boxes; ++b)
+          for (int c = 0; c < DBLK; ++c)
+            tc::tma_load_2d(vs + c * KVBLOCK + b * a.box_rows * 128, &map_v, c * 64, rows[b], &v_full[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {                            // ---- MMA issuer: S_j = Q K_j^T, then O += P_{j-1} V_{j-1}
-      constexpr uint32_t idesc_qk = idesc_f16(BQ, BKEYS, false);
-      constexpr uint32_t idesc_pv = idesc_f16(BQ, HD, true);
-      bool ok = mbar_wait(q_full, 0);
+      constexpr uint32_t idesc_qk = tc::idesc_bf16(BQ, BKEYS, false);
+      constexpr uint32_t idesc_pv = tc::idesc_bf16(BQ, HD, true);
+      bool ok = tc::mbar_wait(q_full, 0);
       if (!ok) atomicExch(a.status, 12);
-      tc_fence_after();
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      tc::fence_after();
+      const uint32_t q_addr = tc::smem_u32(q_s), p_addr = tc::smem_u32(p_s);
       for (int j = 0; j <= nt && ok; ++j) {
         if (j < nt) {
           const int s = j & 1;
-          if (!mbar_wait(&kv_full[s], (j >> 1) & 1)) { atomicExch(a.status, 13); ok = false; break; }
-          if (j >= 2 && !mbar_wait(&s_free[s], ((j >> 1) - 1) & 1)) { atomicExch(a.status, 14); ok = false; break; }
-          tc_fence_after();
-          const uint32_t k_addr = smem_u32(kv_s + s * 2 * KBYTES);
+          if (!tc::mbar_wait(&k_full[s], (j >> 1) & 1)) { atomicExch(a.status, 13); ok = false; break; }
+          if (j >= 2 && !tc::mbar_wait(&s_free[s], ((j >> 1) - 1) & 1)) { atomicExch(a.status, 14); ok = false; break; }
+          tc::fence_after();
+          const uint32_t k_addr = tc::smem_u32(kv_s + s * 2 * KBYTES);
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) {
-            tc_mma(tmem + s * S_COLS, desc_kmajor(q_addr + (k / 4) * QBLOCK + (k % 4) * 32),
-                   desc_kmajor(k_addr + (k / 4) * KVBLOCK + (k % 4) * 32), idesc_qk, k != 0);
+            tc::mma(tmem + s * S_COLS, tc::desc_kmajor(q_addr + (k / 4) * QBLOCK + (k % 4) * 32),
+                   tc::desc_kmajor(k_addr + (k / 4) * KVBLOCK + (k % 4) * 32), idesc_qk, k != 0);
           }
-          tc_commit(&s_full[s]);
+          tc::commit(&s_full[s]);
+          tc::commit(&k_empty[s]);              // the K buffer is free once these MMAs have read it
         }
         if (j >= 1) {
           const int i = j - 1, s = i & 1;
-          if (!mbar_wait(p_ready, i & 1)) { atomicExch(a.status, 15); ok = false; break; }
-          tc_fence_after();
-          const uint32_t v_addr = smem_u32(kv_s + s * 2 * KBYTES + KBYTES);
+          if (!tc::mbar_wait(&v_full[s], (i >> 1) & 1)) { atomicExch(a.status, 21); ok = false; break; }
+          if (!tc::mbar_wait(p_ready, i & 1)) { atomicExch(a.status, 15); ok = false; break; }
+          tc::fence_after();
+          const uint32_t v_addr = tc::smem_u32(kv_s + s * 2 * KBYTES + KBYTES);
 #pragma unroll
           for (int k = 0; k < BKEYS / 16; ++k) {
-            tc_mma(tmem_o, desc_kmajor(p_addr + k * 32), desc_mnmajor(v_addr + k * 2048, KVBLOCK), idesc_pv,
+            tc::mma(tmem_o, tc::desc_kmajor(p_addr + k * 32), tc::desc_mnmajor(v_addr + k * 2048, KVBLOCK), idesc_pv,
                    (i | k) != 0);
           }
-          tc_commit(&kv_empty[s]);
-          tc_commit(pv_done);
+          tc::commit(&v_empty[s]);
+          tc::commit(pv_done);
         }
       }
     }
@@ -282,31 +195,50 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     bool ok = true;
     for (int j = 0; j < nt && ok; ++j) {
       const int sb = j & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1))) {
+      if (!__all_sync(0xffffffffu, tc::mbar_wait(&s_full[sb], (j >> 1) & 1))) {
         if (lane == 0) atomicExch(a.status, 16);
         ok = false;
         break;
       }
-      tc_fence_after();
+      tc::fence_after();
       const int key_base = (tile_begin + j) * BKEYS;
+      // a tile every row of this warp sees whole needs no masks (most tiles of a long prompt)
+      const int warp_first_pos = p_first + quarter * 32;
+      const bool interior = (quarter * 32 + 31 < n_valid) && (key_base + BKEYS - 1 <= warp_first_pos) &&
+                            (key_base >= first_visible(warp_first_pos + 31));
       float sv[BKEYS];
       float mx = m;
-#pragma unroll
-      for (int c = 0; c < BKEYS; c += 32) {
-        float v[32];
-        tc_ld32(tmem + lane_addr + sb * S_COLS + c, v);
+      {
+        // the whole S row: both loads in flight, one wait
+        uint32_t raw0[32], raw1[32];
+        tc::ld32_nowait(tmem + lane_addr + sb * S_COLS, raw0);
+        tc::ld32_nowait(tmem + lane_addr + sb * S_COLS + 32, raw1);
+        tc::wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int key = key_base + c + i;
-          const float s = (row_ok && key <= pos && key >= lo) ? v[i] * a.scale_log2 : -INFINITY;
-          sv[c + i] = s;
-          mx = fmaxf(mx, s);
+          sv[i] = __uint_as_float(raw0[i]);
+          sv[32 + i] = __uint_as_float(raw1[i]);
+        }
+      }
+      if (interior) {
+        float top = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i) top = fmaxf(top, sv[i]);
+        mx = fmaxf(mx, top * a.scale_log2);
+      } else {
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i) {
+          const int key = key_base + i;
+          // masked scores become -inf BEFORE scaling, so the same exponential code serves both paths
+          const float s = (row_ok && key <= pos && key >= lo) ? sv[i] : -INFINITY;
+          sv[i] = s;
+          mx = fmaxf(mx, s * a.scale_log2);
         }
       }
       // the S buffer may be overwritten by the MMA two tiles on
-      tc_fence_before();
+      tc::fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[sb]);
+      if (lane == 0) tc::mbar_arrive(&s_free[sb]);
       // The exponentials are taken against `m`, which follows the true running max lazily: it
       // moves (and O and l are rescaled) only when some row of the warp has grown by more than
       // 2^8, so P stays below 256 and most tiles skip the pass over O. The result is the same
@@ -317,30 +249,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         corr = (m == -INFINITY) ? 0.f : fast_exp2(m - mx);
         m = mx;
       }
+      // p = 2^(raw * scale - m): one fused multiply-add and one ex2 per score; a masked score is
+      // -inf and gives 0 (m is finite here unless the whole row is still masked)
       float sum = 0.f;
+      if (m == -INFINITY) {
 #pragma unroll
-      for (int i = 0; i < BKEYS; ++i) {
-        const float p = (sv[i] == -INFINITY) ? 0.f : fast_exp2(sv[i] - m);
-        sv[i] = p;
-        sum += p;
+        for (int i = 0; i < BKEYS; ++i) sv[i] = 0.f;
+      } else {
+        const float neg_m = -m;
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i) {
+          const float p = fast_exp2(fmaf(sv[i], a.scale_log2, neg_m));
+          sv[i] = p;
+          sum += p;
+        }
       }
       l = l * corr + sum;
       if (j > 0) {
         // the previous P V product must have finished: O is stable and the P buffer is free
-        if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1))) {
+        if (!__all_sync(0xffffffffu, tc::mbar_wait(pv_done, (j - 1) & 1))) {
           if (lane == 0) atomicExch(a.status, 17);
           ok = false;
           break;
         }
-        tc_fence_after();
+        tc::fence_after();
         if (move) {
 #pragma unroll 1
           for (int c = 0; c < HD; c += 32) {
             float o[32];
-            tc_ld32(tmem_o + lane_addr + c, o);
+            tc::ld32(tmem_o + lane_addr + c, o);
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] *= corr;
-            tc_st32(tmem_o + lane_addr + c, o);
+            tc::st32(tmem_o + lane_addr + c, o);
           }
         }
       }
@@ -357,32 +297,39 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         *reinterpret_cast<uint4*>(prow + ((q ^ (r % 8)) * 16)) = pack;
       }
-      if (j == nt - 1 && r < BKEYS && key_base + r > p_last) {
+      if (j == nt - 1 && (p_last + 1) % BKEYS != 0) {
         // Value rows of positions past the portion's end hold whatever the page held before
         // (another request's numbers, possibly not finite): P is zero there, but 0 x NaN is NaN.
-        // The tile has landed (its S has been computed from it); zero this thread's row.
-        uint8_t* vrow = kv_s + sb * 2 * KBYTES + KBYTES + (r / 8) * 1024 + (r % 8) * 128;
+        // Once the V tile has landed, the threads of those rows zero them.
+        if (!__all_sync(0xffffffffu, tc::mbar_wait(&v_full[sb], (j >> 1) & 1))) {
+          if (lane == 0) atomicExch(a.status, 22);
+          ok = false;
+          break;
+        }
+        if (r < BKEYS && key_base + r > p_last) {
+          uint8_t* vrow = kv_s + sb * 2 * KBYTES + KBYTES + (r / 8) * 1024 + (r % 8) * 128;
 #pragma unroll
-        for (int blk = 0; blk < DBLK; ++blk)
+          for (int blk = 0; blk < DBLK; ++blk)
 #pragma unroll
-          for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(vrow + blk * KVBLOCK + q * 16) = make_uint4(0, 0, 0, 0);
+            for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(vrow + blk * KVBLOCK + q * 16) = make_uint4(0, 0, 0, 0);
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
-      tc_fence_before();
+      tc::fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) tc::mbar_arrive(p_ready);
     }
     if (ok) {
-      if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (nt - 1) & 1))) {
+      if (!__all_sync(0xffffffffu, tc::mbar_wait(pv_done, (nt - 1) & 1))) {
         if (lane == 0) atomicExch(a.status, 18);
       } else {
-        tc_fence_after();
+        tc::fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* dst = a.out + ((size_t)(tok0 + r) * a.nh + h) * HD;
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
           float o[32];
-          tc_ld32(tmem_o + lane_addr + c, o);
+          tc::ld32(tmem_o + lane_addr + c, o);
           if (row_ok) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
@@ -400,52 +347,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
     }
   }
-  tc_fence_before();
+  tc::fence_before();
   __syncthreads();
   if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+    tc::fence_after();
+    tc::dealloc(tmem, TMEM_COLS);
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-// [rows, cols] bfloat16 row-major, box [box_rows, 64 elements], 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return HB_ERR_UNSUPPORTED;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {64, box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? HB_OK : HB_ERR_BAD_ARG;
 }
 
 template <int HD>
 int launch(const void* q, const void* k_pages, const void* v_pages, const Args& a, int n_tokens, long long pool_rows,
            int n_seqs, int max_new, cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
-  int rc = make_map(&mq, q, (uint64_t)n_tokens, (uint64_t)a.nh * HD, BQ);
-  if (rc != HB_OK) return rc;
-  rc = make_map(&mk, k_pages, (uint64_t)pool_rows, HD, a.box_rows);
-  if (rc != HB_OK) return rc;
-  rc = make_map(&mv, v_pages, (uint64_t)pool_rows, HD, a.box_rows);
-  if (rc != HB_OK) return rc;
+  if (!tc::make_map_bf16(&mq, q, (uint64_t)n_tokens, (uint64_t)a.nh * HD, BQ) ||
+      !tc::make_map_bf16(&mk, k_pages, (uint64_t)pool_rows, HD, a.box_rows) ||
+      !tc::make_map_bf16(&mv, v_pages, (uint64_t)pool_rows, HD, a.box_rows))
+    return HB_ERR_UNSUPPORTED;
   const size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKEYS * HD * 2 + (size_t)BQ * BKEYS * 2 + 256;
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;

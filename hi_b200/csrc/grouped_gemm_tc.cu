@@ -24,6 +24,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "tc.cuh"
 
 namespace {
 
@@ -31,84 +32,6 @@ constexpr int BM = 128;          // rows of a tile (UMMA M)
 constexpr int BK = 64;           // k elements per stage: 128 bytes, one swizzle span
 constexpr int UK = 16;           // k of one tcgen05.mma
 constexpr int THREADS = 192;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
-
-// ---- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: false after SPIN_LIMIT polls (about a second), never an endless spin.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(40);
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled tile whose rows are 128 bytes:
-// start address, stride between 8-row groups = 1024 bytes, version 1, layout SWIZZLE_128B.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // bits 0-13: address / 16
-  d |= (uint64_t)1 << 16;                           // bits 16-29: leading byte offset / 16 (unused for this layout)
-  d |= (uint64_t)(1024 >> 4) << 32;                 // bits 32-45: stride byte offset / 16
-  d |= (uint64_t)1 << 46;                           // bits 46-47: descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;                           // bits 61-63: SWIZZLE_128B
-  return d;
-}
-// Instruction descriptor, kind::f16: D float32, A and B bfloat16, both K-major, N and M.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
 
 struct Params {
   const int* offsets;        // [experts + 1] first sorted row of every expert
@@ -118,10 +41,6 @@ struct Params {
   int* status;               // 0, or a code of the wait that timed out
   int experts, n_out, K, rows;
 };
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // Tile t of the launch, in the order (expert, column tile, row tile of the expert): tiles that
 // share a weight tile are neighbours, so they run at the same time and the weight tile comes from
@@ -170,18 +89,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int e = threadIdx.x; e <= p.experts; e += THREADS) s_offsets[e] = p.offsets[e];
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {                              // tensor memory for the two accumulator buffers
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc::alloc(tmem_slot, TMEM_COLS);
   }
-  tc_fence_before();
+  tc::fence_before();
   __syncthreads();
-  tc_fence_after();
+  tc::fence_after();
   const uint32_t tmem = *tmem_slot;
   const int n_tiles = (p.n_out + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -194,42 +111,42 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
-          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) { atomicExch(p.status, 1); ok = false; break; }
+          if (it >= STAGES && !tc::mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) { atomicExch(p.status, 1); ok = false; break; }
           uint8_t* st = smem + s * STAGE_BYTES;
-          mbar_expect_tx(&full[s], STAGE_BYTES);
-          tma_load_2d(st, &map_a, kb * BK, tile.row0, &full[s]);
-          tma_load_2d(st + A_BYTES, &map_w0, kb * BK, tile.expert * p.n_out + tile.n0, &full[s]);
-          if (DUAL) tma_load_2d(st + A_BYTES + B_BYTES, &map_w1, kb * BK, tile.expert * p.n_out + tile.n0, &full[s]);
+          tc::mbar_expect_tx(&full[s], STAGE_BYTES);
+          tc::tma_load_2d(st, &map_a, kb * BK, tile.row0, &full[s]);
+          tc::tma_load_2d(st + A_BYTES, &map_w0, kb * BK, tile.expert * p.n_out + tile.n0, &full[s]);
+          if (DUAL) tc::tma_load_2d(st + A_BYTES + B_BYTES, &map_w1, kb * BK, tile.expert * p.n_out + tile.n0, &full[s]);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {                            // ---- MMA issuer
-      constexpr uint32_t idesc = instr_desc(BM, BN);
+      constexpr uint32_t idesc = tc::idesc_bf16(BM, BN, false);
       uint32_t it = 0, local = 0;
       bool ok = true;
       Tile tile;
       for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x, ++local) {
         const int b = local & 1;
         const uint32_t use = local >> 1;
-        if (use > 0 && !mbar_wait(&acc_empty[b], (use - 1) & 1)) { atomicExch(p.status, 4); ok = false; break; }
-        tc_fence_after();
+        if (use > 0 && !tc::mbar_wait(&acc_empty[b], (use - 1) & 1)) { atomicExch(p.status, 4); ok = false; break; }
+        tc::fence_after();
         const uint32_t acc = tmem + b * ACC_COLS;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(&full[s], (it / STAGES) & 1)) { atomicExch(p.status, 2); ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          if (!tc::mbar_wait(&full[s], (it / STAGES) & 1)) { atomicExch(p.status, 2); ok = false; break; }
+          tc::fence_after();
+          const uint32_t a_addr = tc::smem_u32(smem + s * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k) {
-            const uint64_t ad = smem_desc(a_addr + k * UK * 2);
-            tc_mma(acc, ad, smem_desc(b_addr + k * UK * 2), idesc, (kb | k) != 0);
-            if (DUAL) tc_mma(acc + BN, ad, smem_desc(b_addr + B_BYTES + k * UK * 2), idesc, (kb | k) != 0);
+            const uint64_t ad = tc::desc_kmajor(a_addr + k * UK * 2);
+            tc::mma(acc, ad, tc::desc_kmajor(b_addr + k * UK * 2), idesc, (kb | k) != 0);
+            if (DUAL) tc::mma(acc + BN, ad, tc::desc_kmajor(b_addr + B_BYTES + k * UK * 2), idesc, (kb | k) != 0);
           }
-          tc_commit(&empty[s]);                 // the stage is free once these MMAs have read it
+          tc::commit(&empty[s]);                 // the stage is free once these MMAs have read it
         }
-        tc_commit(&acc_full[b]);                // this tile's accumulator is complete (also on the error path)
+        tc::commit(&acc_full[b]);                // this tile's accumulator is complete (also on the error path)
       }
     }
   } else {                                      // ---- epilogue: warps 2..5, lanes 32*(warp % 4) ..
@@ -240,13 +157,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     Tile tile;
     for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x, ++local) {
       const int b = local & 1;
-      const bool waited = __all_sync(0xffffffffu, mbar_wait(&acc_full[b], (local >> 1) & 1));
+      const bool waited = __all_sync(0xffffffffu, tc::mbar_wait(&acc_full[b], (local >> 1) & 1));
       if (!waited) {
         if (lane == 0) atomicExch(p.status, 3);
         ok = false;
         break;
       }
-      tc_fence_after();
+      tc::fence_after();
       const bool row_ok = r < tile.rows;
       const size_t grow = (size_t)(tile.row0 + r);
       float score = 1.f;
@@ -256,10 +173,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         float g[32];
-        tc_ld32(lane_base + c, g);
+        tc::ld32(lane_base + c, g);
         if (DUAL) {
           float u[32];
-          tc_ld32(lane_base + BN + c, u);
+          tc::ld32(lane_base + BN + c, u);
           if (row_ok) {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + grow * p.n_out + n0 + c;
 #pragma unroll
@@ -288,16 +205,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
       }
       // this warp is done reading the buffer: the MMA issuer may overwrite it two tiles on
-      tc_fence_before();
+      tc::fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[b]);
+      if (lane == 0) tc::mbar_arrive(&acc_empty[b]);
     }
   }
-  tc_fence_before();
+  tc::fence_before();
   __syncthreads();
   if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+    tc::fence_after();
+    tc::dealloc(tmem, TMEM_COLS);
   }
 }
 
@@ -311,44 +228,13 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
   for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) d[i] = s[i];
 }
 
-// ---- tensor maps (the driver's encoder, looked up through the runtime: no link against libcuda)
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-// [rows, K] bfloat16 row-major, box [box_rows, 64], 128-byte swizzle, zero fill outside.
-int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return HB_ERR_UNSUPPORTED;
-  const cuuint64_t dims[2] = {K, rows};
-  const cuuint64_t strides[1] = {K * 2};
-  const cuuint32_t box[2] = {BK, box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? HB_OK : HB_ERR_BAD_ARG;
-}
-
 template <int BN, bool DUAL, int STAGES>
 int launch(const void* a, const void* w0, const void* w1, const Params& p, int max_tiles, cudaStream_t stream) {
   CUtensorMap ma, mw0, mw1;
-  int rc = make_map(&ma, a, (uint64_t)p.rows, (uint64_t)p.K, BM);
-  if (rc != HB_OK) return rc;
-  rc = make_map(&mw0, w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BN);
-  if (rc != HB_OK) return rc;
-  rc = make_map(&mw1, DUAL ? w1 : w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BN);
-  if (rc != HB_OK) return rc;
+  if (!tc::make_map_bf16(&ma, a, (uint64_t)p.rows, (uint64_t)p.K, BM) ||
+      !tc::make_map_bf16(&mw0, w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BN) ||
+      !tc::make_map_bf16(&mw1, DUAL ? w1 : w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BN))
+    return HB_ERR_UNSUPPORTED;
   constexpr int STAGE_BYTES = BM * BK * 2 + (DUAL ? 2 : 1) * BN * BK * 2;
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + 4 * ((size_t)p.experts + 1);
   if (smem > 227 * 1024) return HB_ERR_UNSUPPORTED;
