@@ -48,8 +48,6 @@ int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pa
 
 int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
                    int top_k, float* logits_out, int* ids, float* scores, cudaStream_t stream);
-int hb_topk_sigmoid(const float* logits, int n, int experts, int top_k, int* ids, float* scores,
-                    cudaStream_t stream);
 int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
                 int* slot_of_entry, int* active, cudaStream_t stream);
 int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,

@@ -149,28 +149,6 @@ __global__ void router_topk_tiled_kernel(const float* __restrict__ x, const TW* 
   }
 }
 
-// Top-k and sigmoid from given float32 logits [n, experts]: one thread per token (the logits of
-// many tokens come from one library matrix product; ties go to the lower id as above).
-__global__ void topk_sigmoid_kernel(const float* __restrict__ logits, int n, int experts, int top_k,
-                                    int* __restrict__ ids, float* __restrict__ scores) {
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= n) return;
-  const float* lg = logits + (size_t)t * experts;
-  for (int r = 0; r < top_k; ++r) {
-    int best = -1;
-    float bv = 0.f;
-    for (int e = 0; e < experts; ++e) {
-      bool taken = false;
-      for (int q = 0; q < r; ++q) taken |= (ids[(size_t)t * top_k + q] == e);
-      if (taken) continue;
-      const float v = lg[e];
-      if (best < 0 || v > bv) { best = e; bv = v; }
-    }
-    ids[(size_t)t * top_k + r] = best;
-    scores[(size_t)t * top_k + r] = 1.f / (1.f + expf(-bv));
-  }
-}
-
 // ------------------------------------------------------------------ plan
 // Stable counting sort of the n = tokens*top_k routing entries by expert, in one block:
 // offsets[e]..offsets[e+1] are the sorted slots of expert e, in entry order.
@@ -506,15 +484,6 @@ extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_d
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
   else
     return HB_ERR_BAD_ARG;
-  HB_LAUNCH_CHECK();
-  return HB_OK;
-}
-
-extern "C" int hb_topk_sigmoid(const float* logits, int n, int experts, int top_k, int* ids, float* scores,
-                               cudaStream_t stream) {
-  if (!logits || !ids || !scores || n < 0 || experts <= 0 || top_k <= 0 || top_k > experts) return HB_ERR_BAD_ARG;
-  if (n == 0) return HB_OK;
-  topk_sigmoid_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, n, experts, top_k, ids, scores);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

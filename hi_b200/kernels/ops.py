@@ -28,7 +28,6 @@ _SIGNATURES = {
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
-    "hb_topk_sigmoid": [P, I, I, I, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
     "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, P],
     "hb_moe_down": [P, I, P, P, P, I, P, I, I, I, I, P],
@@ -398,18 +397,6 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool 
     _check(lib().hb_router_topk(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, _ptr(logits),
                                 _ptr(ids), _ptr(scores), _stream()), "router_topk")
     return ids, scores, logits
-
-
-def topk_sigmoid(logits: torch.Tensor, top_k: int):
-    """The k largest of given float32 router logits [N, E] per token (ties to the lower id) and
-    their sigmoids: the second half of :func:`router_topk` when the logits come from a matrix
-    product over many tokens."""
-    _need(logits, "logits", torch.float32)
-    n, experts = logits.shape
-    ids = torch.empty((n, top_k), dtype=torch.int32, device=logits.device)
-    scores = torch.empty((n, top_k), dtype=torch.float32, device=logits.device)
-    _check(lib().hb_topk_sigmoid(_ptr(logits), n, experts, top_k, _ptr(ids), _ptr(scores), _stream()), "topk_sigmoid")
-    return ids, scores
 
 
 class MoePlan:
