@@ -22,6 +22,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include <cstdlib>
 #include "api.h"
 #include "common.cuh"
 #include "tc.cuh"
@@ -245,7 +246,8 @@ int launch(const void* a, const void* w0, const void* w1, const Params& p, int m
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return HB_ERR_BAD_ARG;
   const long long upper = (long long)max_tiles * ((p.n_out + BN - 1) / BN);    // tiles there can be at most
-  const int grid = (int)(upper < sms ? upper : sms);                            // one persistent block per SM
+  int grid = (int)(upper < sms ? upper : sms);                            // one persistent block per SM
+  if (const char* lim = getenv("HB_TC_GRID")) { int g = atoi(lim); if (g > 0 && g < grid) grid = g; }
   grouped_gemm_tc_kernel<BN, DUAL, STAGES><<<grid, THREADS, smem, stream>>>(ma, mw0, mw1, p);
   HB_LAUNCH_CHECK();
   return HB_OK;
