@@ -1,38 +1,54 @@
 // Grouped expert products on the 5th-generation tensor cores (tcgen05), bfloat16 in, float32
 // accumulation in tensor memory:
-//     C[r, n] = sum_k A[r, k] * W[e(r), n, k]      for the expert-sorted rows r
-// A is [rows, K] with rows already in expert order (the caller gathers the activations), W is
-// [experts, n_out, K]; both K-major. Persistent blocks (one per SM) walk 128 x BN tiles:
-//   warp 0      one lane issues the TMA loads (A tile 128x64, W tile BNx64, 128-byte swizzle)
-//               into a ring of stages, signalled by mbarrier transaction counts;
-//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M 128, N BN, K 16, four
-//               per stage) and tcgen05.commit, which frees the stage / publishes the accumulator;
-//   warps 2..5  read the accumulator back with tcgen05.ld (each warp its 32 lanes = 32 rows)
-//               and write the epilogue, while the next tile already accumulates into the second
-//               buffer of tensor memory:
+//     C[r, f] = sum_k X[r, k] * W[e(r), f, k]      for the expert-sorted rows r
+// X is [rows, K] with rows already in expert order (the caller gathers the activations), W is
+// [experts, n_out, K]; both K-major. The product is taken TRANSPOSED: the 128 weight rows of a
+// tile are the MMA's M, the expert's tokens its N. N follows the number of tokens the expert
+// really has (rounded up to 16, at most 192 per tile), so an expert with 5 or 140 tokens costs
+// 16 or 144 columns of tensor-core time, and a weight tile is brought into the SM once for up
+// to 192 tokens. What bounds these products is how many weight bytes a block has in flight: a
+// stage is 32 KB of weights (DUAL) beside at most 24 KB of tokens, four stages deep.
+// Persistent blocks (one per SM) walk the tiles (expert, 128 features, up to 192 tokens):
+//   warp 0      one lane issues the TMA loads (W tile 128x64, twice when DUAL; X tile of 32, 64,
+//               128 or 192 rows x 64; 128-byte swizzle) into a ring of stages, signalled by
+//               mbarrier transaction counts;
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M 128, N tokens, K 16, four
+//               per stage and weight stack) and tcgen05.commit, which frees the stage / publishes
+//               the accumulator;
+//   warps 2..9  read the accumulator back with tcgen05.ld (each warp 32 lanes = 32 features, the
+//               columns are tokens; two warps share a lane quarter and take alternate runs of 32
+//               tokens) and write the epilogue:
 //     DUAL   two weight stacks (gate, up), two accumulators: act = silu(s*g) * (s*u), bfloat16,
-//            where s is the row's router score (crates/hi-mlx/src/models.rs:6086-6100: the score
+//            where s is the token's router score (crates/hi-mlx/src/models.rs:6086-6100: the score
 //            scales the expert input, which is the same by linearity);
 //     else   the float32 product (down projection).
-// Rows of a tile past the expert's last row belong to the next expert (or are zero fill): they
-// are computed and not stored. Every wait on an mbarrier is bounded; on a time-out the kernel
-// records where it gave up in `status` and leaves through the common exit (tensor memory is
-// freed there).
+// Tensor memory is two slots of 256 columns. A tile takes one slot, and the next tile
+// accumulates into the other while this one is written out; only a DUAL tile of more than 128
+// tokens needs both (gate in one, up in the other), and its epilogue gives them back as soon as
+// the results are in registers, before it stores them.
+// Token rows of an X tile past the expert's last token belong to the next expert (or are zero
+// fill), weight rows past n_out to the next expert: they are computed and not stored. Every
+// wait on an mbarrier is bounded; on a time-out the kernel records where it gave up in `status`
+// and leaves through the common exit (tensor memory is freed there).
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
 
-#include <cstdlib>
 #include "api.h"
 #include "common.cuh"
 #include "tc.cuh"
 
 namespace {
 
-constexpr int BM = 128;          // rows of a tile (UMMA M)
+constexpr int BF = 128;          // features (weight rows) of a tile: UMMA M
+constexpr int BT = 192;          // most tokens of a tile: UMMA N (the X tile of a stage is BT x 64)
+constexpr int SLOT_COLS = 256;   // tensor memory is two slots of 256 columns
+constexpr int TMEM_COLS = 2 * SLOT_COLS;
+constexpr int DUAL_SLOT_T = 128; // a DUAL tile of up to this many tokens has both accumulators in one slot
 constexpr int BK = 64;           // k elements per stage: 128 bytes, one swizzle span
 constexpr int UK = 16;           // k of one tcgen05.mma
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + EPI_WARPS * 32;
 
 struct Params {
   const int* offsets;        // [experts + 1] first sorted row of every expert
@@ -43,22 +59,29 @@ struct Params {
   int experts, n_out, K, rows;
 };
 
-// Tile t of the launch, in the order (expert, column tile, row tile of the expert): tiles that
+__host__ __device__ constexpr int x_box_rows(int box) { return box == 0 ? 32 : (box == 1 ? 64 : (box == 2 ? 128 : BT)); }
+
+struct Maps {                // X boxes of 32, 64, 128 and 192 rows; the weight stacks
+  CUtensorMap x[4];
+  CUtensorMap w0, w1;
+};
+
+// Tile t of the launch, in the order (expert, feature tile, token tile of the expert): tiles that
 // share a weight tile are neighbours, so they run at the same time and the weight tile comes from
-// HBM once. Returns false past the last tile. `n_tiles` = column tiles.
-struct Tile { int expert, row0, rows, n0; };
-template <int BN>
-__device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t, int n_tiles, Tile& out) {
+// HBM once. Returns false past the last tile. `f_tiles` = feature tiles.
+struct Tile { int expert, row0, tokens, f0; };
+__device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t, int f_tiles, Tile& out) {
   for (int e = 0; e < experts; ++e) {
     const int begin = offsets[e], cnt = offsets[e + 1] - begin;
-    const int m_tiles = (cnt + BM - 1) / BM;
-    const int here = m_tiles * n_tiles;
+    const int t_tiles = (cnt + BT - 1) / BT;
+    const int here = t_tiles * f_tiles;
     if (t < here) {
-      const int nt = t / m_tiles, mt = t - nt * m_tiles;
+      const int ft = t / t_tiles, tt = t - ft * t_tiles;
+      const int per = (cnt + t_tiles - 1) / t_tiles;      // the expert's tokens in equal shares
       out.expert = e;
-      out.row0 = begin + mt * BM;
-      out.rows = min(BM, cnt - mt * BM);
-      out.n0 = nt * BN;
+      out.row0 = begin + tt * per;
+      out.tokens = min(per, cnt - tt * per);
+      out.f0 = ft * BF;
       return true;
     }
     t -= here;
@@ -66,18 +89,30 @@ __device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t
   return false;
 }
 
+// The walk over a block's tiles that the MMA issuer and the epilogue warps share: which slot(s)
+// of tensor memory a tile takes, and how often each slot has been used before.
+struct SlotWalk {
+  uint32_t use[2] = {0, 0};
+  int next = 0;
+  // returns the first slot of the tile; `both` = the tile takes the two of them
+  __device__ __forceinline__ int take(bool dual, int tokens, bool& both) {
+    both = dual && tokens > DUAL_SLOT_T;
+    if (both) return 0;
+    const int b = next;
+    next ^= 1;
+    return b;
+  }
+};
+
 // Persistent: each block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... The shared-memory
-// ring runs on across tiles; tensor memory holds TWO accumulator buffers, so the epilogue of one
-// tile overlaps the loads and MMAs of the next.
-template <int BN, bool DUAL, int STAGES>
+// ring runs on across tiles.
+template <bool DUAL, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
-grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w0,
-                       const __grid_constant__ CUtensorMap map_w1, const Params p) {
-  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-  constexpr int STAGE_BYTES = A_BYTES + (DUAL ? 2 : 1) * B_BYTES;
-  constexpr int ACC_COLS = DUAL ? 2 * BN : BN;       // columns of one accumulator buffer
-  constexpr int TMEM_COLS = 2 * ACC_COLS;
-  static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "");
+grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
+  constexpr int W_BYTES = BF * BK * 2, X_BYTES = BT * BK * 2;
+  constexpr int NW = DUAL ? 2 : 1;
+  constexpr int STAGE_BYTES = NW * W_BYTES + X_BYTES;
+  static_assert(BT <= SLOT_COLS && 2 * DUAL_SLOT_T <= SLOT_COLS, "a slot holds one accumulator of any tile");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -91,17 +126,17 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   for (int e = threadIdx.x; e <= p.experts; e += THREADS) s_offsets[e] = p.offsets[e];
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {                              // tensor memory for the two accumulator buffers
+  if (warp == 1) {                              // tensor memory for the two slots
     tc::alloc(tmem_slot, TMEM_COLS);
   }
   tc::fence_before();
   __syncthreads();
   tc::fence_after();
   const uint32_t tmem = *tmem_slot;
-  const int n_tiles = (p.n_out + BN - 1) / BN;
+  const int f_tiles = (p.n_out + BF - 1) / BF;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
@@ -109,106 +144,151 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       uint32_t it = 0;                          // stages filled so far, over all tiles
       bool ok = true;
       Tile tile;
-      for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x) {
+      for (int t = blockIdx.x; ok && find_tile(s_offsets, p.experts, t, f_tiles, tile); t += gridDim.x) {
+        const int box = tile.tokens <= 32 ? 0 : (tile.tokens <= 64 ? 1 : (tile.tokens <= 128 ? 2 : 3));
+        const uint32_t bytes = NW * W_BYTES + (uint32_t)x_box_rows(box) * BK * 2;
+        const int w_row = tile.expert * p.n_out + tile.f0;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           if (it >= STAGES && !tc::mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) { atomicExch(p.status, 1); ok = false; break; }
           uint8_t* st = smem + s * STAGE_BYTES;
-          tc::mbar_expect_tx(&full[s], STAGE_BYTES);
-          tc::tma_load_2d(st, &map_a, kb * BK, tile.row0, &full[s]);
-          tc::tma_load_2d(st + A_BYTES, &map_w0, kb * BK, tile.expert * p.n_out + tile.n0, &full[s]);
-          if (DUAL) tc::tma_load_2d(st + A_BYTES + B_BYTES, &map_w1, kb * BK, tile.expert * p.n_out + tile.n0, &full[s]);
+          tc::mbar_expect_tx(&full[s], bytes);
+          tc::tma_load_2d(st, &maps.w0, kb * BK, w_row, &full[s]);
+          if (DUAL) tc::tma_load_2d(st + W_BYTES, &maps.w1, kb * BK, w_row, &full[s]);
+          tc::tma_load_2d(st + NW * W_BYTES, &maps.x[box], kb * BK, tile.row0, &full[s]);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {                            // ---- MMA issuer
-      constexpr uint32_t idesc = tc::idesc_bf16(BM, BN, false);
-      uint32_t it = 0, local = 0;
+      uint32_t it = 0;
+      SlotWalk walk;
       bool ok = true;
       Tile tile;
-      for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x, ++local) {
-        const int b = local & 1;
-        const uint32_t use = local >> 1;
-        if (use > 0 && !tc::mbar_wait(&acc_empty[b], (use - 1) & 1)) { atomicExch(p.status, 4); ok = false; break; }
+      for (int t = blockIdx.x; ok && find_tile(s_offsets, p.experts, t, f_tiles, tile); t += gridDim.x) {
+        bool both;
+        const int b = walk.take(DUAL, tile.tokens, both);
+        for (int q = b; ok && q <= (both ? 1 : b); ++q)      // the slot(s) must have been written out
+          if (walk.use[q] > 0 && !tc::mbar_wait(&acc_empty[q], (walk.use[q] - 1) & 1)) { atomicExch(p.status, 4); ok = false; }
+        if (!ok) break;
         tc::fence_after();
-        const uint32_t acc = tmem + b * ACC_COLS;
+        const uint32_t idesc = tc::idesc_bf16(BF, (tile.tokens + 15) & ~15, false);
+        const uint32_t acc = tmem + b * SLOT_COLS;
+        const uint32_t up_off = both ? SLOT_COLS : DUAL_SLOT_T;  // where the second accumulator starts
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           if (!tc::mbar_wait(&full[s], (it / STAGES) & 1)) { atomicExch(p.status, 2); ok = false; break; }
           tc::fence_after();
-          const uint32_t a_addr = tc::smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
+          const uint32_t w_addr = tc::smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t x_addr = w_addr + NW * W_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k) {
-            const uint64_t ad = tc::desc_kmajor(a_addr + k * UK * 2);
-            tc::mma(acc, ad, tc::desc_kmajor(b_addr + k * UK * 2), idesc, (kb | k) != 0);
-            if (DUAL) tc::mma(acc + BN, ad, tc::desc_kmajor(b_addr + B_BYTES + k * UK * 2), idesc, (kb | k) != 0);
+            const uint64_t xd = tc::desc_kmajor(x_addr + k * UK * 2);
+            tc::mma(acc, tc::desc_kmajor(w_addr + k * UK * 2), xd, idesc, (kb | k) != 0);
+            if (DUAL) tc::mma(acc + up_off, tc::desc_kmajor(w_addr + W_BYTES + k * UK * 2), xd, idesc, (kb | k) != 0);
           }
           tc::commit(&empty[s]);                 // the stage is free once these MMAs have read it
         }
-        tc::commit(&acc_full[b]);                // this tile's accumulator is complete (also on the error path)
+        // this tile's accumulator is complete (also on the error path)
+        tc::commit(&acc_full[b]);
+        ++walk.use[b];
+        if (both) { tc::commit(&acc_full[1]); ++walk.use[1]; }
       }
     }
-  } else {                                      // ---- epilogue: warps 2..5, lanes 32*(warp % 4) ..
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;          // row of the tile = lane of tensor memory
-    uint32_t local = 0;
+  } else {                                      // ---- epilogue: warps 2..9
+    const int quarter = warp & 3;               // the lanes of tensor memory this warp may read
+    const int half = (warp - 2) >> 2;           // which runs of 32 tokens it takes
+    SlotWalk walk;
     bool ok = true;
     Tile tile;
-    for (int t = blockIdx.x; ok && find_tile<BN>(s_offsets, p.experts, t, n_tiles, tile); t += gridDim.x, ++local) {
-      const int b = local & 1;
-      const bool waited = __all_sync(0xffffffffu, tc::mbar_wait(&acc_full[b], (local >> 1) & 1));
-      if (!waited) {
+    for (int t = blockIdx.x; ok && find_tile(s_offsets, p.experts, t, f_tiles, tile); t += gridDim.x) {
+      bool both;
+      const int b = walk.take(DUAL, tile.tokens, both);
+      const int f = tile.f0 + quarter * 32 + lane;        // this thread's feature = its lane of tensor memory
+      const bool f_ok = f < p.n_out;
+      // lane j fetches the scores of tokens c + j for this warp's runs c (at most BT / 64 of
+      // them) while the tile still accumulates; the loops below take them by shuffle
+      constexpr int RUNS = (BT + 63) / 64;
+      float my_score[RUNS];
+#pragma unroll
+      for (int q = 0; q < RUNS; ++q) {
+        const int tk = half * 32 + q * 64 + lane;
+        my_score[q] = (DUAL && tk < tile.tokens) ? p.scores[p.sorted_entry[tile.row0 + tk]] : 1.f;
+      }
+      bool waited = tc::mbar_wait(&acc_full[b], walk.use[b] & 1);
+      if (both) waited = tc::mbar_wait(&acc_full[1], walk.use[1] & 1) && waited;
+      if (!__all_sync(0xffffffffu, waited)) {
         if (lane == 0) atomicExch(p.status, 3);
         ok = false;
         break;
       }
       tc::fence_after();
-      const bool row_ok = r < tile.rows;
-      const size_t grow = (size_t)(tile.row0 + r);
-      float score = 1.f;
-      if (DUAL && row_ok) score = p.scores[p.sorted_entry[tile.row0 + r]];
-      const uint32_t lane_base = tmem + b * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      const int n0 = tile.n0;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        float g[32];
-        tc::ld32(lane_base + c, g);
-        if (DUAL) {
-          float u[32];
-          tc::ld32(lane_base + BN + c, u);
-          if (row_ok) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + grow * p.n_out + n0 + c;
+      const uint32_t lane_base = tmem + b * SLOT_COLS + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t up_off = both ? SLOT_COLS : DUAL_SLOT_T;
+      const int live = tile.tokens;
+      if (DUAL) {
+        // results of this warp's runs, two bfloat16 per register
+        uint32_t packed[RUNS][16];
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              if (n0 + c + i < p.n_out) {       // n_out is a multiple of 8: the 8 columns are in or out together
-                uint4 pack;
-                uint32_t* w = reinterpret_cast<uint32_t*>(&pack);
+        for (int q = 0; q < RUNS; ++q) {
+          const int c = half * 32 + q * 64;
+          if (c < live) {
+            uint32_t g[32], u[32];
+            tc::ld32_nowait(lane_base + c, g);
+            tc::ld32_nowait(lane_base + up_off + c, u);
+            tc::wait_ld();
 #pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                  const float g0 = score * g[i + j], g1 = score * g[i + j + 1];
-                  const float a0 = g0 / (1.f + expf(-g0)) * (score * u[i + j]);
-                  const float a1 = g1 / (1.f + expf(-g1)) * (score * u[i + j + 1]);
-                  __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1);
-                  w[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                *reinterpret_cast<uint4*>(dst + i) = pack;
+            for (int j = 0; j < 32; j += 2) {
+              float a[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const float s = __shfl_sync(0xffffffffu, my_score[q], j + h);
+                const float gs = s * __uint_as_float(g[j + h]);
+                // silu by the fast exponential and division: their error is far below the
+                // bfloat16 rounding of the result
+                a[h] = __fdividef(gs, 1.f + __expf(-gs)) * (s * __uint_as_float(u[j + h]));
               }
+              __nv_bfloat162 pr = __floats2bfloat162_rn(a[0], a[1]);
+              packed[q][j >> 1] = *reinterpret_cast<uint32_t*>(&pr);
             }
           }
-        } else if (row_ok) {
-          float* dst = reinterpret_cast<float*>(p.out) + grow * p.n_out + n0 + c;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            if (n0 + c + i < p.n_out)           // n_out is a multiple of 8
-              *reinterpret_cast<float4*>(dst + i) = make_float4(g[i], g[i + 1], g[i + 2], g[i + 3]);
         }
+        // this warp is done reading the slot(s): the MMA issuer may overwrite them
+        tc::fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          tc::mbar_arrive(&acc_empty[b]);
+          if (both) tc::mbar_arrive(&acc_empty[1]);
+        }
+#pragma unroll
+        for (int q = 0; q < RUNS; ++q) {
+          const int c = half * 32 + q * 64;
+          if (c < live && f_ok) {
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (size_t)(tile.row0 + c) * p.n_out + f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)               // 32 lanes: 64 bytes in a row
+              if (c + j < tile.tokens) dst[(size_t)j * p.n_out] = (uint16_t)(packed[q][j >> 1] >> ((j & 1) * 16));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < RUNS; ++q) {
+          const int c = half * 32 + q * 64;
+          if (c < live) {
+            float g[32];
+            tc::ld32(lane_base + c, g);
+            float* dst = reinterpret_cast<float*>(p.out) + (size_t)(tile.row0 + c) * p.n_out + f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)               // 32 lanes: 128 bytes in a row
+              if (f_ok && c + j < tile.tokens) dst[(size_t)j * p.n_out] = g[j];
+          }
+        }
+        tc::fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&acc_empty[b]);
       }
-      // this warp is done reading the buffer: the MMA issuer may overwrite it two tiles on
-      tc::fence_before();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&acc_empty[b]);
+      ++walk.use[b];
+      if (both) ++walk.use[1];
     }
   }
   tc::fence_before();
@@ -229,26 +309,26 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
   for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) d[i] = s[i];
 }
 
-template <int BN, bool DUAL, int STAGES>
-int launch(const void* a, const void* w0, const void* w1, const Params& p, int max_tiles, cudaStream_t stream) {
-  CUtensorMap ma, mw0, mw1;
-  if (!tc::make_map_bf16(&ma, a, (uint64_t)p.rows, (uint64_t)p.K, BM) ||
-      !tc::make_map_bf16(&mw0, w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BN) ||
-      !tc::make_map_bf16(&mw1, DUAL ? w1 : w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BN))
+template <bool DUAL, int STAGES>
+int launch(const void* x, const void* w0, const void* w1, const Params& p, int max_tiles, cudaStream_t stream) {
+  Maps maps;
+  for (int b = 0; b < 4; ++b)
+    if (!tc::make_map_bf16(&maps.x[b], x, (uint64_t)p.rows, (uint64_t)p.K, (uint32_t)x_box_rows(b))) return HB_ERR_UNSUPPORTED;
+  if (!tc::make_map_bf16(&maps.w0, w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BF) ||
+      !tc::make_map_bf16(&maps.w1, DUAL ? w1 : w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BF))
     return HB_ERR_UNSUPPORTED;
-  constexpr int STAGE_BYTES = BM * BK * 2 + (DUAL ? 2 : 1) * BN * BK * 2;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + 4 * ((size_t)p.experts + 1);
+  constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * BF * BK * 2 + BT * BK * 2;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 128 + 4 * ((size_t)p.experts + 1);
   if (smem > 227 * 1024) return HB_ERR_UNSUPPORTED;
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<BN, DUAL, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<DUAL, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return HB_ERR_BAD_ARG;
-  const long long upper = (long long)max_tiles * ((p.n_out + BN - 1) / BN);    // tiles there can be at most
-  int grid = (int)(upper < sms ? upper : sms);                            // one persistent block per SM
-  if (const char* lim = getenv("HB_TC_GRID")) { int g = atoi(lim); if (g > 0 && g < grid) grid = g; }
-  grouped_gemm_tc_kernel<BN, DUAL, STAGES><<<grid, THREADS, smem, stream>>>(ma, mw0, mw1, p);
+  const long long upper = (long long)max_tiles * ((p.n_out + BF - 1) / BF);    // tiles there can be at most
+  const int grid = (int)(upper < sms ? upper : sms);                            // one persistent block per SM
+  grouped_gemm_tc_kernel<DUAL, STAGES><<<grid, THREADS, smem, stream>>>(maps, p);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -273,10 +353,10 @@ extern "C" int hb_moe_gate_up_tc(const void* xs, const int* sorted_entry, const 
     return HB_ERR_BAD_ARG;
   if (hidden % 8 != 0 || inter % 8 != 0 || hidden <= 0 || inter <= 0) return HB_ERR_UNSUPPORTED;
   if (rows == 0) return HB_OK;
-  const int max_tiles = (rows + BM - 1) / BM + (experts < rows ? experts : rows);
+  const int max_tiles = (rows + BT - 1) / BT + (experts < rows ? experts : rows);
   if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
   Params p{offsets, sorted_entry, scores, act, status, experts, inter, hidden, rows};
-  return launch<128, true, 4>(xs, w_gate, w_up, p, max_tiles, stream);
+  return launch<true, 4>(xs, w_gate, w_up, p, max_tiles, stream);
 }
 
 // down projection on tensor cores: act [rows, inter] -> y float32 [rows, hidden].
@@ -285,8 +365,8 @@ extern "C" int hb_moe_down_tc(const void* act, const void* w_down, const int* of
   if (!act || !w_down || !offsets || !y || !status || rows < 0 || experts <= 0) return HB_ERR_BAD_ARG;
   if (hidden % 8 != 0 || inter % 8 != 0 || hidden <= 0 || inter <= 0) return HB_ERR_UNSUPPORTED;
   if (rows == 0) return HB_OK;
-  const int max_tiles = (rows + BM - 1) / BM + (experts < rows ? experts : rows);
+  const int max_tiles = (rows + BT - 1) / BT + (experts < rows ? experts : rows);
   if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
   Params p{offsets, nullptr, nullptr, y, status, experts, hidden, inter, rows};
-  return launch<256, false, 4>(act, w_down, nullptr, p, max_tiles, stream);
+  return launch<false, 5>(act, w_down, nullptr, p, max_tiles, stream);
 }
