@@ -341,10 +341,13 @@ def test_router_plan_and_experts(shape, dt, tol):
 
 
 @pytest.mark.parametrize("shape", [(256, 4, 1, 128, 300), (5120, 16, 1, 512, 2048), (192, 8, 2, 96, 700), (136, 3, 2, 72, 50),
-                                   (1024, 5, 1, 1032, 1000), (64, 2, 1, 64, 129)])
+                                   (1024, 5, 1, 1032, 1000), (64, 2, 1, 64, 129), (256, 4, 1, 2112, 100),
+                                   (128, 2, 2, 2048, 40)])
 def test_expert_products_on_tcgen05(shape):
-    """The tcgen05 grouped products (TMA + tensor memory) against float32 references: row counts
-    per expert above and below a tile, widths that are no multiple of the tile, K tails."""
+    """The tcgen05 grouped products (TMA + tensor memory) against float32 references: token counts
+    per expert above and below a tile and a slot of tensor memory, widths that are no multiple of
+    the tile, K tails, and (the last two shapes) few tokens with a long K, where the down
+    projection is cut in two along K and the halves are added."""
     o = ops()
     H, E, k, I, n = shape
     dt = torch.bfloat16
