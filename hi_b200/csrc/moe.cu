@@ -14,9 +14,42 @@
 namespace {
 
 // ------------------------------------------------------------------ router
-// One block per token; warps take experts in turn; lanes stride over the hidden dim.
-// x may be float32 while the weights are bfloat16: the router reads the float32 output of the
-// norm, so its logits carry no activation rounding of their own.
+// logit[t, e] = sum_k x[t, k] * w[e, k] in float32. x may be float32 while the weights are
+// bfloat16: the router reads the float32 output of the norm, so its logits carry no activation
+// rounding of their own.
+//
+// Both kernels below take the sum in the SAME order, so a token's routing does not depend on
+// which of them ran (how many tokens the step had): K is cut into runs of 256 elements; the runs
+// form ROUTER_KPARTS consecutive parts; inside a part lane l adds elements 8l .. 8l+7 of every run
+// in ascending order into one accumulator; each part is reduced over the lanes by the xor tree
+// (offsets 16, 8, 4, 2, 1); the parts are added in ascending order.
+constexpr int ROUTER_KPARTS = 4;
+
+__device__ __forceinline__ void router_part_range(int hidden, int part, int& run_begin, int& run_end) {
+  const int runs = (hidden + 255) / 256, per = (runs + ROUTER_KPARTS - 1) / ROUTER_KPARTS;
+  run_begin = part * per;
+  run_end = min(runs, run_begin + per);
+}
+
+// The k largest of a row of logits (ties to the lower id) and their sigmoids.
+__device__ __forceinline__ void router_select(const float* row, int experts, int top_k, int* ids, float* scores) {
+  for (int r = 0; r < top_k; ++r) {
+    int best = -1;
+    float bv = 0.f;
+    for (int e = 0; e < experts; ++e) {
+      bool taken = false;
+      for (int q = 0; q < r; ++q) taken |= (ids[q] == e);
+      if (taken) continue;
+      const float v = row[e];
+      if (best < 0 || v > bv) { best = e; bv = v; }  // strict '>' keeps the lowest id on ties
+    }
+    ids[r] = best;
+    scores[r] = 1.f / (1.f + expf(-bv));
+  }
+}
+
+// Few tokens: one block per token; warps take experts in turn; the parts of K are independent
+// accumulators of the same lane, so their loads are in flight together.
 template <typename TX, typename TW>
 __global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int hidden, int experts,
                                    int top_k, float* __restrict__ logits_out, int* __restrict__ ids,
@@ -25,130 +58,137 @@ __global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restric
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const TX* xr = x + (size_t)t * hidden;
+  int rb[ROUTER_KPARTS], re[ROUTER_KPARTS];
+#pragma unroll
+  for (int q = 0; q < ROUTER_KPARTS; ++q) router_part_range(hidden, q, rb[q], re[q]);
+  const int per = re[0] - rb[0];
   for (int e = warp; e < experts; e += nwarps) {
     const TW* wr = w + (size_t)e * hidden;
-    float s = 0.f;
-    if ((hidden & 7) == 0) {   // rows are 16-byte aligned: 8 elements per load
-      int j = lane * 8;
-      for (; j + 768 < hidden; j += 1024) {      // four independent pairs of loads in flight
-        float xv[4][8], wv[4][8];
+    float s[ROUTER_KPARTS];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          hb::load8(xr + j + 256 * q, xv[q]);
-          hb::load8(wr + j + 256 * q, wv[q]);
+    for (int q = 0; q < ROUTER_KPARTS; ++q) s[q] = 0.f;
+    if ((hidden & 7) == 0) {   // rows are 16-byte aligned: 8 elements per load
+      for (int c = 0; c < per; ++c) {
+        float xv[ROUTER_KPARTS][8], wv[ROUTER_KPARTS][8];
+        bool on[ROUTER_KPARTS];
+#pragma unroll
+        for (int q = 0; q < ROUTER_KPARTS; ++q) {
+          const int j = (rb[q] + c) * 256 + lane * 8;
+          on[q] = rb[q] + c < re[q] && j < hidden;
+          if (on[q]) {
+            hb::load8(xr + j, xv[q]);
+            hb::load8(wr + j, wv[q]);
+          }
         }
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
+        for (int q = 0; q < ROUTER_KPARTS; ++q)
+          if (on[q])
 #pragma unroll
-          for (int i = 0; i < 8; ++i) s += xv[q][i] * wv[q][i];
+            for (int i = 0; i < 8; ++i) s[q] += xv[q][i] * wv[q][i];
       }
-      for (; j < hidden; j += 256) {
-        float xv[8], wv[8];
-        hb::load8(xr + j, xv);
-        hb::load8(wr + j, wv);
+    } else {                   // any width: the same order, element by element
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s += xv[i] * wv[i];
-      }
-    } else {
-      for (int j = lane; j < hidden; j += 32) s += hb::to_f32(xr[j]) * hb::to_f32(wr[j]);
+      for (int q = 0; q < ROUTER_KPARTS; ++q)
+        for (int run = rb[q]; run < re[q]; ++run)
+          for (int i = 0; i < 8; ++i) {
+            const int j = run * 256 + lane * 8 + i;
+            if (j < hidden) s[q] += hb::to_f32(xr[j]) * hb::to_f32(wr[j]);
+          }
     }
-    s = hb::warp_sum(s);
+    float total = hb::warp_sum(s[0]);
+#pragma unroll
+    for (int q = 1; q < ROUTER_KPARTS; ++q) total += hb::warp_sum(s[q]);
     if (lane == 0) {
-      lg[e] = s;
-      if (logits_out) logits_out[(size_t)t * experts + e] = s;
+      lg[e] = total;
+      if (logits_out) logits_out[(size_t)t * experts + e] = total;
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int r = 0; r < top_k; ++r) {
-      int best = -1;
-      float bv = 0.f;
-      for (int e = 0; e < experts; ++e) {
-        bool taken = false;
-        for (int q = 0; q < r; ++q) taken |= (ids[(size_t)t * top_k + q] == e);
-        if (taken) continue;
-        const float v = lg[e];
-        if (best < 0 || v > bv) { best = e; bv = v; }  // strict '>' keeps the lowest id on ties
+  if (threadIdx.x == 0) router_select(lg, experts, top_k, ids + (size_t)t * top_k, scores + (size_t)t * top_k);
+}
+
+// Many tokens: a block takes ROUTER_TOK tokens x ROUTER_EXP experts with one warp per part of K;
+// a lane holds its 8 elements of the four token rows in registers and walks the expert rows past
+// them, four at a time, so every load is used 4 (weights) or 16 (activations) times from
+// registers and nothing waits on shared memory. Needs hidden % 8 == 0. The partial sums meet in
+// shared memory and are added in part order. With one block column (experts <= ROUTER_EXP) the
+// block also selects; otherwise router_select_kernel does.
+constexpr int ROUTER_TOK = 4, ROUTER_EXP = 16;
+
+template <typename TW>
+__global__ void __launch_bounds__(ROUTER_KPARTS * 32)
+router_logits_tiled_kernel(const float* __restrict__ x, const TW* __restrict__ w, int n, int hidden, int experts,
+                           int top_k, float* __restrict__ logits, int* __restrict__ ids,
+                           float* __restrict__ scores) {
+  __shared__ float partial[ROUTER_KPARTS][ROUTER_TOK][ROUTER_EXP];
+  __shared__ float lg[ROUTER_TOK][ROUTER_EXP];
+  const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
+  const int t0 = blockIdx.x * ROUTER_TOK, e0 = blockIdx.y * ROUTER_EXP;
+  int run_begin, run_end;
+  router_part_range(hidden, part, run_begin, run_end);
+  float acc[ROUTER_TOK][ROUTER_EXP];
+#pragma unroll
+  for (int tt = 0; tt < ROUTER_TOK; ++tt)
+#pragma unroll
+    for (int e = 0; e < ROUTER_EXP; ++e) acc[tt][e] = 0.f;
+  for (int run = run_begin; run < run_end; ++run) {
+    const int j = run * 256 + lane * 8;
+    if (j >= hidden) continue;
+    float xv[ROUTER_TOK][8];
+#pragma unroll
+    for (int tt = 0; tt < ROUTER_TOK; ++tt) {
+      if (t0 + tt < n) {
+        hb::load8(x + (size_t)(t0 + tt) * hidden + j, xv[tt]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xv[tt][i] = 0.f;
       }
-      ids[(size_t)t * top_k + r] = best;
-      scores[(size_t)t * top_k + r] = 1.f / (1.f + expf(-bv));
     }
+#pragma unroll
+    for (int es = 0; es < ROUTER_EXP; es += 4) {
+      float wv[4][8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int e = min(e0 + es + q, experts - 1);         // rows past the last expert: computed, not used
+        hb::load8(w + (size_t)e * hidden + j, wv[q]);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int tt = 0; tt < ROUTER_TOK; ++tt)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[tt][es + q] += xv[tt][i] * wv[q][i];
+    }
+  }
+#pragma unroll
+  for (int tt = 0; tt < ROUTER_TOK; ++tt)
+#pragma unroll
+    for (int e = 0; e < ROUTER_EXP; ++e) {
+      const float v = hb::warp_sum(acc[tt][e]);
+      if (lane == 0) partial[part][tt][e] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < ROUTER_TOK * ROUTER_EXP) {
+    const int tt = threadIdx.x / ROUTER_EXP, e = threadIdx.x % ROUTER_EXP;
+    float total = partial[0][tt][e];
+#pragma unroll
+    for (int q = 1; q < ROUTER_KPARTS; ++q) total += partial[q][tt][e];
+    lg[tt][e] = total;
+    if (logits && t0 + tt < n && e0 + e < experts) logits[(size_t)(t0 + tt) * experts + e0 + e] = total;
+  }
+  if (gridDim.y > 1) return;
+  __syncthreads();
+  if (threadIdx.x < ROUTER_TOK && t0 + threadIdx.x < n) {
+    const size_t t = t0 + threadIdx.x;
+    router_select(lg[threadIdx.x], experts, top_k, ids + t * top_k, scores + t * top_k);
   }
 }
 
-// Many tokens: a block stages TOK float32 rows of x in shared memory and walks the router rows
-// once for all of them (the one-token kernel re-reads the whole router per token). Per-token
-// arithmetic and its order (lane-strided partial sums, then the warp tree) do not depend on TOK.
-template <typename TW, int TOK>
-__global__ void router_topk_tiled_kernel(const float* __restrict__ x, const TW* __restrict__ w, int n, int hidden,
-                                         int experts, int top_k, float* __restrict__ logits_out,
-                                         int* __restrict__ ids, float* __restrict__ scores) {
-  extern __shared__ float tile_sm[];     // [TOK][hidden] rows, then [TOK][experts] logits
-  float* xs = tile_sm;
-  float* lg = tile_sm + (size_t)TOK * hidden;
-  const int t0 = blockIdx.x * TOK;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int i = threadIdx.x * 4; i < TOK * hidden; i += blockDim.x * 4) {
-    const int tt = i / hidden, j = i - tt * hidden;          // hidden % 8 == 0: a float4 stays in its row
-    const float4 v = t0 + tt < n ? *reinterpret_cast<const float4*>(x + (size_t)(t0 + tt) * hidden + j)
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
-    *reinterpret_cast<float4*>(xs + i) = v;
-  }
-  __syncthreads();
-  for (int e = warp; e < experts; e += nwarps) {
-    const TW* wr = w + (size_t)e * hidden;
-    float acc[TOK];
-#pragma unroll
-    for (int tt = 0; tt < TOK; ++tt) acc[tt] = 0.f;
-    auto fma_chunk = [&](int j, const float (&wv)[8]) {
-#pragma unroll
-      for (int tt = 0; tt < TOK; ++tt) {
-        const float4 a = *reinterpret_cast<const float4*>(xs + tt * hidden + j);
-        const float4 b = *reinterpret_cast<const float4*>(xs + tt * hidden + j + 4);
-        acc[tt] += a.x * wv[0]; acc[tt] += a.y * wv[1]; acc[tt] += a.z * wv[2]; acc[tt] += a.w * wv[3];
-        acc[tt] += b.x * wv[4]; acc[tt] += b.y * wv[5]; acc[tt] += b.z * wv[6]; acc[tt] += b.w * wv[7];
-      }
-    };
-    int j = lane * 8;
-    for (; j + 768 < hidden; j += 1024) {        // four router loads in flight per lane
-      float wv[4][8];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) hb::load8(wr + j + 256 * q, wv[q]);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) fma_chunk(j + 256 * q, wv[q]);
-    }
-    for (; j < hidden; j += 256) {
-      float wv[8];
-      hb::load8(wr + j, wv);
-      fma_chunk(j, wv);
-    }
-#pragma unroll
-    for (int tt = 0; tt < TOK; ++tt) {
-      const float sdot = hb::warp_sum(acc[tt]);
-      if (lane == 0) {
-        lg[tt * experts + e] = sdot;
-        if (logits_out && t0 + tt < n) logits_out[(size_t)(t0 + tt) * experts + e] = sdot;
-      }
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x < TOK && t0 + threadIdx.x < n) {
-    const int t = t0 + threadIdx.x;
-    const float* row = lg + threadIdx.x * experts;
-    for (int r = 0; r < top_k; ++r) {
-      int best = -1;
-      float bv = 0.f;
-      for (int e = 0; e < experts; ++e) {
-        bool taken = false;
-        for (int q = 0; q < r; ++q) taken |= (ids[(size_t)t * top_k + q] == e);
-        if (taken) continue;
-        const float v = row[e];
-        if (best < 0 || v > bv) { best = e; bv = v; }
-      }
-      ids[(size_t)t * top_k + r] = best;
-      scores[(size_t)t * top_k + r] = 1.f / (1.f + expf(-bv));
-    }
-  }
+// Selection from stored logits, one thread per token (more experts than one block column holds).
+__global__ void router_select_kernel(const float* __restrict__ logits, int n, int experts, int top_k,
+                                     int* __restrict__ ids, float* __restrict__ scores) {
+  const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < (size_t)n) router_select(logits + t * experts, experts, top_k, ids + t * top_k, scores + t * top_k);
 }
 
 // ------------------------------------------------------------------ plan
@@ -442,29 +482,25 @@ extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_d
     return HB_ERR_BAD_ARG;
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
   if (n == 0) return HB_OK;
-  if (x_dtype == HB_DTYPE_F32 && n >= 128 && hidden % 8 == 0) {
-    // many tokens: 4 rows of x per block in shared memory, the router rows read once per block
-    constexpr int TOK = 4;
-    const size_t tiled = ((size_t)TOK * hidden + (size_t)TOK * experts) * sizeof(float);
-    if (tiled <= 200 * 1024) {
-      const int blocks = (n + TOK - 1) / TOK;
-      cudaError_t e = cudaSuccess;
-      if (w_dtype == HB_DTYPE_F32) {
-        e = cudaFuncSetAttribute(router_topk_tiled_kernel<float, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled);
-        if (e != cudaSuccess) return (int)e;
-        router_topk_tiled_kernel<float, TOK><<<blocks, 512, tiled, stream>>>((const float*)x, (const float*)w, n, hidden,
-                                                                             experts, top_k, logits_out, ids, scores);
-      } else if (w_dtype == HB_DTYPE_BF16) {
-        e = cudaFuncSetAttribute(router_topk_tiled_kernel<__nv_bfloat16, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled);
-        if (e != cudaSuccess) return (int)e;
-        router_topk_tiled_kernel<__nv_bfloat16, TOK><<<blocks, 512, tiled, stream>>>(
-            (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores);
-      } else {
-        return HB_ERR_BAD_ARG;
-      }
+  if (x_dtype == HB_DTYPE_F32 && n >= 192 && hidden % 8 == 0 && (w_dtype == HB_DTYPE_F32 || w_dtype == HB_DTYPE_BF16)) {
+    // many tokens (measured: faster than one block per token from about 200): register tiles of
+    // 4 tokens x 16 experts; with more than 16 experts the
+    // selection needs the stored logits of all block columns
+    dim3 grid((n + ROUTER_TOK - 1) / ROUTER_TOK, (experts + ROUTER_EXP - 1) / ROUTER_EXP);
+    if (grid.y > 1 && !logits_out) return HB_ERR_BAD_ARG;
+    if (grid.y > 65535) return HB_ERR_UNSUPPORTED;
+    if (w_dtype == HB_DTYPE_F32)
+      router_logits_tiled_kernel<float><<<grid, ROUTER_KPARTS * 32, 0, stream>>>(
+          (const float*)x, (const float*)w, n, hidden, experts, top_k, logits_out, ids, scores);
+    else
+      router_logits_tiled_kernel<__nv_bfloat16><<<grid, ROUTER_KPARTS * 32, 0, stream>>>(
+          (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores);
+    HB_LAUNCH_CHECK();
+    if (grid.y > 1) {
+      router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, ids, scores);
       HB_LAUNCH_CHECK();
-      return HB_OK;
     }
+    return HB_OK;
   }
   const size_t smem = (size_t)experts * sizeof(float);
   const int threads = experts >= 16 ? 512 : (experts >= 8 ? 256 : 128);   // a warp per expert where that fits

@@ -1,6 +1,7 @@
 // After the fused q/k/v projection: position encoding (rotary) or attention temperature,
 // optional weightless L2 norm of q and k, and the append of k and v to the paged cache.
-// One warp per (token, head) over the nh q heads, nkv k heads and nkv v heads.
+// One warp per (token, head) over the nh q heads, nkv k heads and nkv v heads; a block is one
+// token and up to 16 of its heads, and computes the token's sines and cosines once for them.
 // All arithmetic in float32; angles are position * inv_freq in float32 with sincosf.
 //
 // Formulas: rotary pairs (j, j + hd/2) or (2j, 2j+1): crates/hi-cuda/src/kernels.cu:3757-3785,
@@ -12,6 +13,7 @@
 namespace {
 
 constexpr int kMaxPairsPerLane = 4;  // head_dim <= 256
+constexpr int kHeadsPerBlock = 16;
 
 template <typename T>
 __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ inv_freq,
@@ -21,15 +23,19 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
                                 int table_stride, T* __restrict__ q_out, T* __restrict__ k_pages,
                                 T* __restrict__ v_pages, int page_size, int write_kv, int n_tokens, int nh,
                                 int nkv, int hd) {
+  __shared__ float cs_s[32 * kMaxPairsPerLane], sn_s[32 * kMaxPairsPerLane];
   const int lane = threadIdx.x & 31;
   const int heads_total = nh + 2 * nkv;
-  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (wid >= (long long)n_tokens * heads_total) return;
-  const int t = (int)(wid / heads_total);
-  const int head = (int)(wid - (long long)t * heads_total);
+  const int t = blockIdx.x;
+  const int head = blockIdx.y * kHeadsPerBlock + (threadIdx.x >> 5);
+  const int pos = positions[t];
+  if (inv_freq != nullptr && blockIdx.y * kHeadsPerBlock < nh + nkv) {   // a block of v heads alone rotates nothing
+    for (int j = threadIdx.x; j < (hd >> 1); j += blockDim.x) sincosf((float)pos * inv_freq[j], &sn_s[j], &cs_s[j]);
+  }
+  __syncthreads();
+  if (head >= heads_total) return;
   const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
   if (kind != 0 && !write_kv) return;
-  const int pos = positions[t];
   const T* src = qkv + ((size_t)t * heads_total + head) * hd;
   const int half = hd >> 1;
 
@@ -64,8 +70,7 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         if (kind != 2 && inv_freq != nullptr) {
-          float sn, cs;
-          sincosf((float)pos * inv_freq[j + e], &sn, &cs);
+          const float sn = sn_s[j + e], cs = cs_s[j + e];
           const float ra = xa[e] * cs - xb[e] * sn;
           const float rb = xb[e] * cs + xa[e] * sn;
           xa[e] = ra; xb[e] = rb;
@@ -111,17 +116,17 @@ extern "C" int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, in
   if (inv_freq && rot_pairs != hd / 2) return HB_ERR_UNSUPPORTED;  // all of head_dim rotates
   if (temp_on && !(floor_scale > 0.f)) return HB_ERR_BAD_ARG;
   if (n_tokens == 0) return HB_OK;
-  const long long warps = (long long)n_tokens * (nh + 2 * nkv);
-  const int warps_per_block = 4;
-  const long long blocks = (warps + warps_per_block - 1) / warps_per_block;
-  if (blocks > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
+  const int heads_total = nh + 2 * nkv;
+  const dim3 grid(n_tokens, (heads_total + kHeadsPerBlock - 1) / kHeadsPerBlock);
+  const int threads = 32 * (heads_total < kHeadsPerBlock ? heads_total : kHeadsPerBlock);
+  if (grid.y > 65535) return HB_ERR_UNSUPPORTED;
   if (dtype == HB_DTYPE_F32)
-    qkv_post_kernel<float><<<(int)blocks, warps_per_block * 32, 0, stream>>>(
+    qkv_post_kernel<float><<<grid, threads, 0, stream>>>(
         (const float*)qkv, inv_freq, rot_pairs, interleaved, qk_norm, qk_eps, temp_on, floor_scale, attn_scale,
         positions, seq_of_token, block_table, table_stride, (float*)q_out, (float*)k_pages, (float*)v_pages,
         page_size, write_kv, n_tokens, nh, nkv, hd);
   else if (dtype == HB_DTYPE_BF16)
-    qkv_post_kernel<__nv_bfloat16><<<(int)blocks, warps_per_block * 32, 0, stream>>>(
+    qkv_post_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (const __nv_bfloat16*)qkv, inv_freq, rot_pairs, interleaved, qk_norm, qk_eps, temp_on, floor_scale,
         attn_scale, positions, seq_of_token, block_table, table_stride, (__nv_bfloat16*)q_out,
         (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, write_kv, n_tokens, nh, nkv, hd);

@@ -293,7 +293,7 @@ def counts_of(ids, experts):
 
 @pytest.mark.parametrize("dt,tol", DT)
 @pytest.mark.parametrize("shape", [(64, 4, 1, 128, 50), (192, 8, 2, 96, 33), (120, 5, 3, 72, 300), (120, 5, 5, 72, 1),
-                                   (256, 16, 1, 512, 8), (200, 128, 1, 64, 64), (104, 3, 2, 40, 700), (100, 4, 2, 36, 20)])
+                                   (256, 16, 1, 512, 8), (200, 128, 1, 64, 200), (104, 3, 2, 40, 700), (100, 4, 2, 36, 20)])
 def test_router_plan_and_experts(shape, dt, tol):
     o = ops()
     H, E, k, I, n = shape
@@ -380,6 +380,24 @@ def test_expert_products_on_tcgen05(shape):
     # and against the general kernels on the same inputs
     close(o.moe_gate_up(x.to(DEV), plan, k, wg.to(DEV), wu.to(DEV), scores, False), act_ref, 2e-2, "general gate/up")
     assert not o.moe_tc_supported(x.float().to(DEV), wg.float().to(DEV))
+
+
+@pytest.mark.parametrize("shape", [(1288, 16, 200), (5120, 16, 257), (328, 40, 230), (2048, 5, 192)])
+def test_router_logits_do_not_depend_on_the_number_of_tokens(shape):
+    """The many-token router kernel and the one-token kernel add in the same order: the logits of
+    a token are the same bits whether it is routed in a long step or in a short one."""
+    o = ops()
+    H, E, n = shape
+    g = torch.Generator().manual_seed(H + E)
+    x = torch.randn(n, H, generator=g).to(DEV)
+    for wdt in (torch.bfloat16, torch.float32):
+        w = torch.randn(E, H, generator=g).to(wdt).to(DEV)
+        ids_all, _, logits_all = o.router_topk(x, w, 2, True)                 # n >= 192: the tiled kernel
+        for lo in range(0, n, 37):
+            ids, _, logits = o.router_topk(x[lo:lo + 37].contiguous(), w, 2, True)   # few rows: one block per token
+            assert torch.equal(logits, logits_all[lo:lo + 37]), f"{shape} {wdt}: logits differ between the kernels"
+            assert torch.equal(ids, ids_all[lo:lo + 37])
+        close(logits_all, x.float() @ w.float().T, 1e-5, "router logits")
 
 
 def test_router_ties_go_to_the_lower_id():
