@@ -76,8 +76,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* pv_done = bars + 14;      // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
 
-  const int seq = blockIdx.z, h = blockIdx.y;
-  const int qt = gridDim.x - 1 - blockIdx.x;    // later tiles read more keys: start them first
+  // Blocks start in the order x, y, z: the heads are x and the query tiles y, latest first, so
+  // the tiles that read the most keys start first for every head and the short ones fill the end.
+  const int seq = blockIdx.z, h = blockIdx.x;
+  const int qt = gridDim.y - 1 - blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq_begin = a.cu_seqlens[seq], seq_end = a.cu_seqlens[seq + 1];
   const int tok0 = seq_begin + qt * BQ;
@@ -366,7 +368,9 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const Args& 
   const size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKEYS * HD * 2 + (size_t)BQ * BKEYS * 2 + 256;
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((max_new + BQ - 1) / BQ, a.nh, n_seqs);
+  const int q_tiles = (max_new + BQ - 1) / BQ;
+  if (q_tiles > 65535 || n_seqs > 65535) return HB_ERR_UNSUPPORTED;
+  dim3 grid(a.nh, q_tiles, n_seqs);
   attn_prefill_tc_kernel<HD><<<grid, THREADS, smem, stream>>>(mq, mk, mv, a);
   HB_LAUNCH_CHECK();
   return HB_OK;
