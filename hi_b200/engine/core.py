@@ -9,10 +9,12 @@ crates/hi-cuda/src/gpu.rs:8842-8929, 10541-10715, 9026-9132.)
 """
 from __future__ import annotations
 
+import itertools
 import os
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.device import DeviceCache, plan_groups
@@ -183,19 +185,12 @@ class Engine:
                 if not self.manager.is_open(e.request_id):
                     self.open(e.request_id)
                     opened.append(e.request_id)
-                before = [list(t) for t in self.manager.requests[e.request_id].tables]
-                reserved.append((e.request_id, before))
+                reserved.append((e.request_id, self.manager.table_lengths(e.request_id)))
                 self.manager.reserve(e.request_id, len(e.tokens))
         except Exception:
             for rid, before in reserved:
-                if rid in opened:
-                    continue
-                rc = self.manager.requests[rid]
-                for g, table in enumerate(rc.tables):
-                    for b in range(len(before[g]), len(table)):
-                        if table[b] >= 0:
-                            self.manager.pools[g].give(table[b], rid)
-                    del table[len(before[g]):]
+                if rid not in opened:
+                    self.manager.unreserve(rid, before)
             for rid in opened:
                 self.manager.close(rid)
             raise
@@ -241,13 +236,11 @@ class Engine:
         With ``static`` the buffers of a captured decode graph are filled instead."""
         mgr = self.manager
         n_seqs = len(entries)
-        n_tokens = sum(len(e.tokens) for e in entries)
-        starts = [mgr.length(e.request_id) for e in entries]
         n_new = [len(e.tokens) for e in entries]
-        slots = [mgr.slot(e.request_id) for e in entries]
-        tables = [[mgr.table(g, e.request_id) for e in entries] for g in range(len(mgr.groups))]
+        n_tokens = sum(n_new)
+        handles = mgr.handles_of([e.request_id for e in entries])
         if widths is None:
-            widths = [max(len(t) for t in tg) for tg in tables]
+            widths = mgr.step_widths(handles)
         n_want = sum(len(e.want) for e in entries)
 
         def pad4(n):
@@ -263,35 +256,29 @@ class Engine:
             host = static.host
         else:
             host = _pinned_int32(max(total, 4))
-        buf = host.numpy()
         o_tok, o_pos, o_seq, o_cu, o_slot, o_want = offsets[:6]
-        cursor, want_cursor = 0, 0
-        buf[o_cu] = 0
-        for s, e in enumerate(entries):
-            n = n_new[s]
-            buf[o_tok + cursor: o_tok + cursor + n] = list(e.tokens)
-            buf[o_pos + cursor: o_pos + cursor + n] = range(starts[s], starts[s] + n)
-            buf[o_seq + cursor: o_seq + cursor + n] = s
-            for w in e.want:
-                buf[o_want + want_cursor] = cursor + int(w)
-                want_cursor += 1
-            cursor += n
-            buf[o_cu + s + 1] = cursor
-            buf[o_slot + s] = slots[s]
-        # a captured decode step keeps its table rows between steps: a row is rewritten only when
-        # another request sits in it or the request's tables changed (a new page, a freed chunk)
-        fresh = [True] * n_seqs
-        if static is not None:
-            sigs = [(e.request_id, mgr.table_version(e.request_id)) for e in entries]
-            fresh = [static.row_sig[s] != sigs[s] for s in range(n_seqs)]
-            static.row_sig = sigs
-        for g, tg in enumerate(tables):
-            o, w = offsets[6 + g], widths[g]
-            view = buf[o: o + n_seqs * w].reshape(n_seqs, w)
-            for s, t in enumerate(tg):
-                if fresh[s]:
-                    view[s, : len(t)] = t
-                    view[s, len(t):] = -1
+        # the native runtime fills the buffer: tokens, positions, sequence ids, cumulative counts,
+        # slots, wanted rows and the block tables. A captured decode step keeps its table rows
+        # between steps: a row is rewritten only when another request sits in it or the request's
+        # tables changed (a new page, a freed chunk)
+        if n_tokens == n_seqs:
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n_seqs)
+        else:
+            tokens = np.fromiter(itertools.chain.from_iterable(e.tokens for e in entries), dtype=np.int32, count=n_tokens)
+        want_counts = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=n_seqs)
+        want = np.fromiter(itertools.chain.from_iterable(e.want for e in entries), dtype=np.int32, count=n_want)
+        n_new_a = np.asarray(n_new, dtype=np.int32)
+        widths_a = np.asarray(widths if widths else [0], dtype=np.int32)
+        offsets_a = np.asarray(offsets, dtype=np.int64)
+        starts_a, slots_a = np.empty(n_seqs, dtype=np.int32), np.empty(n_seqs, dtype=np.int32)
+        code = mgr._lib.hbh_pack_step(
+            mgr._ptr, n_seqs, handles.ctypes.data, n_new_a.ctypes.data, tokens.ctypes.data, want_counts.ctypes.data,
+            want.ctypes.data, widths_a.ctypes.data, offsets_a.ctypes.data, host.data_ptr(), starts_a.ctypes.data,
+            slots_a.ctypes.data, static.row_request.ctypes.data if static is not None else None,
+            static.row_version.ctypes.data if static is not None else None)
+        if code != 0:
+            raise RuntimeError(f"packing the step's inputs failed (code {code})")
+        starts, slots = starts_a.tolist(), slots_a.tolist()
         self.last_step_h2d_bytes = host.numel() * 4     # the one host-to-device copy of this step
         if static is not None:
             static.dev.copy_(host, non_blocking=True)
@@ -303,7 +290,7 @@ class Engine:
             return dev[off: off + n]
 
         block_tables = {g: seg(offsets[6 + g], n_seqs * widths[g]).view(n_seqs, widths[g])
-                        for g in range(len(tables))}
+                        for g in range(len(widths))}
         ctx = StepContext(
             n_tokens=n_tokens, n_seqs=n_seqs, tokens=seg(o_tok, n_tokens), positions=seg(o_pos, n_tokens),
             seq_of_token=seg(o_seq, n_tokens), cu_seqlens=seg(o_cu, n_seqs + 1), slots=seg(o_slot, n_seqs),
@@ -386,7 +373,8 @@ class _DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.captured = False
         self.eager_runs = 0
-        self.row_sig = [None] * n_seqs      # (request, table version) last written into each table row
+        self.row_request = np.full(n_seqs, -1, dtype=np.int64)    # request and table version last written
+        self.row_version = np.full(n_seqs, -1, dtype=np.int64)    # into each table row
         self.kernels = 0
         self.uses_tensor_core_experts = False
 

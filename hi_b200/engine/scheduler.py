@@ -1,5 +1,8 @@
 """The scheduler above the step function: admit, cut prompts into portions under a token
-budget, decode, finish and free. Host-only; it decides, the engine runs.
+budget, decode, finish and free. Host-only; it decides, the engine runs. The decisions are
+taken by the native host runtime (``hi_b200/csrc/host/scheduler.cpp``), which works on counts;
+this module is its Python face and keeps what only the caller knows: token values, sampling
+parameters, generator state, end-of-sequence ids.
 
 Compared with the reference's continuous loop (crates/hi-cuda/src/lib.rs:4418-4471,
 5062-5298): that one leases all pages of a request at admission and runs prefill chunks and
@@ -17,14 +20,17 @@ When pages run out, in this order:
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
 from ..cache.pages import CacheManager
+from ..host import build as host
 from ..sampling.sampler import DEFAULT_SEED, Lcg, SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+_STATUS = {0: WAITING, 1: RUNNING, 2: FINISHED}
+_REASON = {0: None, 1: "length", 2: "stop", 3: "aborted", 4: "insufficient_gpu_memory"}
 
 
 @dataclass
@@ -46,21 +52,38 @@ class SchedulerConfig:
             raise ValueError("max_prefill_portion must be positive")
 
 
-@dataclass(eq=False)          # requests are compared by identity
 class Request:
-    request_id: Hashable
-    prompt: List[int]
-    params: SamplingParams
-    output: List[int] = field(default_factory=list)
-    status: str = WAITING
-    finish_reason: Optional[str] = None
-    computed: int = 0                    # tokens whose keys are in the cache
-    preemptions: int = 0
-    rng: Lcg = None                      # type: ignore[assignment]
+    """One generation request. ``status``, ``computed`` (tokens whose keys are in the cache) and
+    ``preemptions`` are the scheduler's; they are read from it while it knows the request."""
 
-    def __post_init__(self):
-        if self.rng is None:
-            self.rng = Lcg(DEFAULT_SEED if self.params.seed is None else self.params.seed)
+    def __init__(self, request_id: Hashable, prompt: List[int], params: SamplingParams,
+                 output: Optional[List[int]] = None, rng: Optional[Lcg] = None):
+        self.request_id, self.prompt, self.params = request_id, prompt, params
+        self.output: List[int] = [] if output is None else output
+        self.finish_reason: Optional[str] = None
+        self.rng = rng if rng is not None else Lcg(DEFAULT_SEED if params.seed is None else params.seed)
+        self._scheduler: Optional["Scheduler"] = None
+        self._handle = -1
+        self._last = (WAITING, 0, 0)       # status, computed, preemptions once the scheduler has let go
+
+    def _stat(self, what: int) -> Optional[int]:
+        s = self._scheduler
+        return None if s is None else int(s._lib.hbh_sched_request_stat(s._ptr, self._handle, what))
+
+    @property
+    def status(self) -> str:
+        v = self._stat(0)
+        return self._last[0] if v is None else _STATUS[v]
+
+    @property
+    def computed(self) -> int:
+        v = self._stat(1)
+        return self._last[1] if v is None else v
+
+    @property
+    def preemptions(self) -> int:
+        v = self._stat(2)
+        return self._last[2] if v is None else v
 
     @property
     def tokens(self) -> List[int]:
@@ -83,6 +106,9 @@ class Request:
             return self.output[begin - n:end - n]
         return self.prompt[begin:] + self.output[:end - n]
 
+    def __repr__(self) -> str:
+        return f"Request({self.request_id!r}, prompt={len(self.prompt)}, output={len(self.output)}, {self.status})"
+
 
 @dataclass
 class PlannedEntry:
@@ -101,6 +127,24 @@ class StepPlan:
         return sum(len(e.tokens) for e in self.entries)
 
 
+class _Counters:
+    """``scheduler.counters``: read from the native scheduler."""
+
+    _NAMES = ("admitted", "preemptions", "steps", "shrunk_portions", "stalled_portions")
+
+    def __init__(self, scheduler: "Scheduler"):
+        self._s = scheduler
+
+    def __getitem__(self, name: str) -> int:
+        return int(self._s._lib.hbh_sched_counter(self._s._ptr, self._NAMES.index(name)))
+
+    def keys(self):
+        return list(self._NAMES)
+
+    def __iter__(self):
+        return iter(self._NAMES)
+
+
 class Scheduler:
     def __init__(self, manager: CacheManager, config: SchedulerConfig, eos_token_ids: Sequence[int] = (),
                  max_model_len: Optional[int] = None, release: Optional[Callable[[Hashable], None]] = None):
@@ -108,11 +152,36 @@ class Scheduler:
         self.manager, self.config = manager, config
         self.eos = set(int(t) for t in eos_token_ids)
         self.max_model_len = max_model_len
-        self.release = release or (lambda rid: manager.close(rid) if manager.is_open(rid) else None)
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []          # in admission order
+        self._lib = host.library()
+        self._ptr = self._lib.hbh_sched_create(manager._ptr, config.max_batch_size, config.max_active_requests or 0,
+                                               config.max_batched_tokens, config.max_prefill_portion or 0,
+                                               int(max_model_len or 0))
+        if not self._ptr:
+            raise ValueError("the native scheduler refused this configuration")
+        self.release = release
+        if release is not None:
+            handles = manager._handles
+
+            def call_release(_user, handle):
+                release(handles.of_handle[handle])
+
+            self._release_c = host.RELEASE_FN(call_release)      # kept alive with the scheduler
+            self._lib.hbh_sched_set_release(self._ptr, self._release_c, None)
+        self._live: Dict[int, Request] = {}          # handle -> request the native scheduler knows
         self.finished: List[Request] = []
-        self.counters = {"admitted": 0, "preemptions": 0, "steps": 0, "shrunk_portions": 0, "stalled_portions": 0}
+        self.counters = _Counters(self)
+        cap = max(config.max_batch_size, manager.max_requests, 1) + 1
+        self._cap = cap
+        self._entries = (ctypes.c_int64 * (4 * cap))()
+        self._preempted = (ctypes.c_int64 * cap)()
+        self._dropped = (ctypes.c_int64 * cap)()
+        self._finished = (ctypes.c_int64 * (2 * cap))()
+        self._counts = (ctypes.c_int * 3)()
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            self._lib.hbh_sched_destroy(self._ptr)
+            self._ptr = None
 
     # ------------------------------------------------------------------ admission
     @property
@@ -120,184 +189,103 @@ class Scheduler:
         limit = self.config.max_active_requests or self.config.max_batch_size
         return min(limit, self.manager.max_requests)
 
+    def _queue(self, which: int) -> List[Request]:
+        n = self._lib.hbh_sched_queue(self._ptr, which, None, 0)
+        buf = (ctypes.c_int64 * max(n, 1))()
+        self._lib.hbh_sched_queue(self._ptr, which, buf, n)
+        return [self._live[buf[i]] for i in range(n)]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._queue(0)
+
+    @property
+    def running(self) -> List[Request]:          # in admission order
+        return self._queue(1)
+
     def add(self, request: Request) -> None:
         request.params.validate()
         if not request.prompt:
             raise ValueError("invalid_request_parameter: the prompt is empty")
-        total = len(request.prompt) + request.params.max_tokens
-        if self.max_model_len is not None and total > self.max_model_len:
-            raise ValueError(f"context_length_exceeded: prompt ({len(request.prompt)}) + max_tokens "
-                             f"({request.params.max_tokens}) exceeds the model's {self.max_model_len} positions")
-        ps = self.manager.page_size
-        for g, (spec, pool) in enumerate(zip(self.manager.groups, self.manager.pools)):
-            if spec.window is None:
-                need = -(-total // ps)
-            else:
-                # a windowed group holds at most its window plus the page being written
-                need = min(-(-total // ps), -(-spec.window[1] // ps) + 1)
-            if need > pool.total:
-                raise ValueError(f"insufficient_gpu_memory: the request needs {need} page(s) of group {g}, "
-                                 f"the pool has {pool.total}")
-        request.status = WAITING
-        self.waiting.append(request)
+        handles = self.manager._handles
+        h = handles.pin(request.request_id)
+        code = self._lib.hbh_sched_add(self._ptr, h, len(request.prompt), int(request.params.max_tokens))
+        if code != host.OK:
+            handles.unpin(h)
+            handles.drop_if_unused(h, self.manager.is_open(request.request_id))
+            if code in (host.ERR_CONTEXT_LENGTH, host.ERR_NEVER_FITS):
+                raise ValueError(self._lib.hbh_sched_error(self._ptr).decode())
+            if code == host.ERR_ALREADY_OPEN:
+                raise ValueError(f"invalid_request_parameter: request {request.request_id!r} is already scheduled")
+            raise ValueError(f"invalid_request_parameter: the scheduler refused the request (code {code})")
+        request._scheduler, request._handle = self, h
+        self._live[h] = request
+
+    def _let_go(self, r: Request, reason: Optional[str]) -> None:
+        """The request is finished: keep its last state on the Python object, drop the native record."""
+        r._last = (FINISHED, r.computed, r.preemptions)
+        if reason is not None:
+            r.finish_reason = reason
+        h = r._handle
+        r._scheduler = None
+        self._lib.hbh_sched_forget(self._ptr, h)
+        self._live.pop(h, None)
+        handles = self.manager._handles
+        handles.unpin(h)
+        handles.drop_if_unused(h, self.manager.is_open(r.request_id))
+        self.finished.append(r)
 
     def abort(self, request_id: Hashable) -> Optional[Request]:
-        for r in list(self.running):
-            if r.request_id == request_id:
-                self.running.remove(r)
-                self._finish(r, "aborted")
-                return r
-        for r in list(self.waiting):
-            if r.request_id == request_id:
-                self.waiting.remove(r)
-                self._finish(r, "aborted")
-                return r
-        return None
+        h = self.manager._handles.get(request_id)
+        r = self._live.get(h) if h is not None else None
+        if r is None or not self._lib.hbh_sched_abort(self._ptr, h):
+            return None
+        self._let_go(r, "aborted")
+        return r
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.hbh_sched_has_work(self._ptr))
 
     # ------------------------------------------------------------------ planning
-    def _fits(self, request: Request, n: int, promised: List[int], opened: bool) -> bool:
-        need = self.manager.pages_needed(request.request_id if opened else None, n, request.computed)
-        return all(promised[g] + need[g] <= self.manager.pools[g].free for g in range(len(need)))
-
-    def _largest_fit(self, request: Request, n: int, promised: List[int], opened: bool) -> int:
-        if self._fits(request, n, promised, opened):
-            return n
-        lo, hi = 0, n            # lo fits (0 tokens need nothing), hi does not
-        while hi - lo > 1:
-            mid = (lo + hi) // 2
-            if self._fits(request, mid, promised, opened):
-                lo = mid
-            else:
-                hi = mid
-        return lo
-
-    def _promise(self, request: Request, n: int, promised: List[int], opened: bool) -> None:
-        need = self.manager.pages_needed(request.request_id if opened else None, n, request.computed)
-        for g, v in enumerate(need):
-            promised[g] += v
-
-    def _preempt(self, victim: Request, plan: StepPlan) -> None:
-        self.running.remove(victim)
-        self.release(victim.request_id)
-        victim.status = WAITING
-        victim.computed = 0
-        victim.preemptions += 1
-        self.counters["preemptions"] += 1
-        self.waiting.appendleft(victim)
-        plan.preempted.append(victim)
-        plan.entries = [e for e in plan.entries if e.request is not victim]
-
     def plan(self) -> StepPlan:
         """Decide the next step. Preemptions are carried out (through ``release``) here."""
-        cfg = self.config
+        c = self._counts
+        code = self._lib.hbh_sched_plan(self._ptr, self._entries, self._cap, ctypes.byref(c, 0), self._preempted, self._cap,
+                                        ctypes.byref(c, 4), self._dropped, self._cap, ctypes.byref(c, 8))
+        if code != host.OK:
+            raise RuntimeError(f"the native scheduler failed to plan (code {code})")
         plan = StepPlan()
-        budget = cfg.max_batched_tokens
-        promised = [0] * len(self.manager.groups)
-
-        # 1. every running request that has one token pending decodes, oldest first
-        decoding = [r for r in self.running if r.pending == 1 and r.computed >= len(r.prompt)]
-        planned = set()                        # ids of requests with an entry in this plan
-        i = 0
-        while i < len(decoding) and budget > 0 and len(plan.entries) < cfg.max_batch_size:
-            r = decoding[i]
-            if r.status != RUNNING:             # preempted meanwhile
-                i += 1
-                continue
-            if self._fits(r, 1, promised, True):
-                self._promise(r, 1, promised, True)
-                plan.entries.append(PlannedEntry(r, [r.last_token], True))
-                planned.add(id(r))
-                budget -= 1
-                i += 1
-                continue
-            victim = self.running[-1]
-            if victim is r and len(self.running) == 1:
-                self.running.remove(r)
-                self._finish(r, "insufficient_gpu_memory")
-                i += 1
-                continue
-            # the victim's promised pages, if it was planned, come back with it
-            if id(victim) in planned:
-                planned.discard(id(victim))
-                promised = [0] * len(self.manager.groups)
-                self._preempt(victim, plan)
-                budget = cfg.max_batched_tokens
-                for e in plan.entries:
-                    self._promise(e.request, len(e.tokens), promised, True)
-                    budget -= len(e.tokens)
-            else:
-                self._preempt(victim, plan)
-            # try r again (unless it was the victim)
-
-        # 2. running requests still in their prompt get portions, oldest first
-        for r in self.running:
-            if budget <= 0 or len(plan.entries) >= cfg.max_batch_size:
-                break
-            if id(r) in planned or r.pending <= 0:
-                continue
-            self._plan_portion(r, plan, promised, budget, opened=True)
-            budget = cfg.max_batched_tokens - plan.n_tokens
-
-        # 3. admit waiting requests into what is left
-        if not plan.preempted:
-            slots_left = self.manager.free_slots
-            while (self.waiting and budget > 0 and len(plan.entries) < cfg.max_batch_size
-                   and len(self.running) < self.max_active and slots_left > 0):
-                r = self.waiting[0]
-                before = len(plan.entries)
-                self._plan_portion(r, plan, promised, budget, opened=False)
-                if len(plan.entries) == before:
-                    break                       # no page for even one token: wait
-                self.waiting.popleft()
-                r.status = RUNNING
-                self.running.append(r)
-                self.counters["admitted"] += 1
-                slots_left -= 1
-                budget = cfg.max_batched_tokens - plan.n_tokens
-        self.counters["steps"] += 1
+        for i in range(c[0]):
+            h, begin, count, samples = self._entries[4 * i: 4 * i + 4]
+            r = self._live[h]
+            plan.entries.append(PlannedEntry(r, r.span(begin, begin + count), bool(samples)))
+        plan.preempted = [self._live[self._preempted[i]] for i in range(c[1])]
+        for i in range(c[2]):            # a lone decode that cannot get a page
+            self._let_go(self._live[self._dropped[i]], "insufficient_gpu_memory")
         return plan
-
-    def _plan_portion(self, r: Request, plan: StepPlan, promised: List[int], budget: int, opened: bool) -> None:
-        want = min(r.pending, budget)
-        if self.config.max_prefill_portion is not None:
-            want = min(want, self.config.max_prefill_portion)
-        n = self._largest_fit(r, want, promised, opened)
-        if n <= 0:
-            self.counters["stalled_portions"] += 1
-            return
-        if n < want:
-            self.counters["shrunk_portions"] += 1
-        self._promise(r, n, promised, opened)
-        toks = r.span(r.computed, r.computed + n)
-        plan.entries.append(PlannedEntry(r, toks, samples=(r.computed + n == len(r.prompt) + len(r.output))))
 
     # ------------------------------------------------------------------ after the step
     def commit(self, plan: StepPlan, sampled: Dict[Hashable, int]) -> List[Request]:
         """The step ran; ``sampled`` holds one token for every entry with ``samples``.
         Returns the requests that finished (their cache is released here)."""
-        done: List[Request] = []
+        stops = []
         for e in plan.entries:
-            r = e.request
-            r.computed += len(e.tokens)
             if not e.samples:
                 continue
+            r = e.request
             tok = int(sampled[r.request_id])
-            is_eos = (tok in self.eos and not r.params.ignore_eos) or tok in r.params.stop_token_ids
-            if is_eos:
-                reason = "stop"                 # EOS is not emitted (crates/hi-mlx/src/models.rs:598-600)
-            else:
+            stop = (tok in self.eos and not r.params.ignore_eos) or tok in r.params.stop_token_ids
+            if not stop:                    # EOS is not emitted (crates/hi-mlx/src/models.rs:598-600)
                 r.output.append(tok)
-                reason = "length" if len(r.output) >= r.params.max_tokens else None
-            if reason:
-                self.running.remove(r)
-                self._finish(r, reason)
-                done.append(r)
+            stops.append(1 if stop else 0)
+        n = ctypes.c_int(0)
+        code = self._lib.hbh_sched_commit(self._ptr, (ctypes.c_int * max(len(stops), 1))(*stops), len(stops),
+                                          self._finished, self._cap, ctypes.byref(n))
+        if code != host.OK:
+            raise RuntimeError(f"the native scheduler failed to commit (code {code}): is this its last plan?")
+        done: List[Request] = []
+        for i in range(n.value):
+            r = self._live[self._finished[2 * i]]
+            self._let_go(r, _REASON[self._finished[2 * i + 1]])
+            done.append(r)
         return done
-
-    def _finish(self, r: Request, reason: str) -> None:
-        r.status, r.finish_reason = FINISHED, reason
-        self.release(r.request_id)
-        self.finished.append(r)
