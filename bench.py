@@ -264,10 +264,8 @@ def main(argv=None) -> int:
         reqs.append(req)
     # the prompts' keys are taken as cached noise except for their last token
     for req in reqs:
-        llm.scheduler.waiting.remove(req)
         engine.assume_cached(req.request_id, len(req.prompt) - 1)
-        req.computed, req.status = len(req.prompt) - 1, "running"
-        llm.scheduler.running.append(req)
+        llm.scheduler.assume_running(req, len(req.prompt) - 1)
     for _ in range(args.warmup):
         llm.step()
     torch.cuda.synchronize()

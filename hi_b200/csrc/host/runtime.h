@@ -97,6 +97,8 @@ void hbh_sched_set_release(void* sched, hbh_release_fn fn, void* user);
 int hbh_sched_add(void* sched, int64_t request, int prompt_len, int max_tokens);
 // returns 1 if the request was known (it is finished as "aborted" and released), 0 if not
 int hbh_sched_abort(void* sched, int64_t request);
+// benchmarks only: a waiting request whose first `computed` tokens are in the cache already runs from there
+int hbh_sched_assume_running(void* sched, int64_t request, int64_t computed);
 int hbh_sched_has_work(void* sched);
 // Decide the next step. entries: (request, first token index, token count, samples) x n_entries;
 // preempted: requests sent back to the head of the waiting queue (released already);

@@ -45,6 +45,7 @@ class Scheduler {
 
   int add(int64_t id, int64_t prompt_len, int64_t max_tokens);
   bool abort(int64_t id);
+  int assume_running(int64_t id, int64_t computed);
   bool has_work() const { return !waiting_.empty() || !running_.empty(); }
   void plan();
   int commit(const int* stop, int n_stop);
@@ -154,6 +155,19 @@ bool Scheduler::abort(int64_t id) {
   waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), r), waiting_.end());
   finish(r, ABORTED);
   return true;
+}
+
+// Benchmarks only: a waiting request whose first `computed` tokens the caller has put into the
+// cache by other means starts running from there.
+int Scheduler::assume_running(int64_t id, int64_t computed) {
+  Request* r = find(id);
+  if (!r || r->status != WAITING || computed < 0 || computed >= r->prompt_len + r->output_len) return HBH_ERR_ARG;
+  waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), r), waiting_.end());
+  r->computed = computed;
+  r->status = RUNNING;
+  running_.push_back(r);
+  ++admitted;
+  return HBH_OK;
 }
 
 void Scheduler::preempt(Request* victim) {
@@ -309,6 +323,9 @@ int hbh_sched_add(void* sched, int64_t request, int prompt_len, int max_tokens) 
   return static_cast<Scheduler*>(sched)->add(request, prompt_len, max_tokens);
 }
 int hbh_sched_abort(void* sched, int64_t request) { return static_cast<Scheduler*>(sched)->abort(request) ? 1 : 0; }
+int hbh_sched_assume_running(void* sched, int64_t request, int64_t computed) {
+  return static_cast<Scheduler*>(sched)->assume_running(request, computed);
+}
 int hbh_sched_has_work(void* sched) { return static_cast<Scheduler*>(sched)->has_work() ? 1 : 0; }
 
 int hbh_sched_plan(void* sched, int64_t* entries, int cap_entries, int* n_entries, int64_t* preempted, int cap_preempted,

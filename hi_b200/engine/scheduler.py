@@ -243,6 +243,12 @@ class Scheduler:
         self._let_go(r, "aborted")
         return r
 
+    def assume_running(self, request: Request, computed: int) -> None:
+        """Benchmarks only: a waiting request whose first ``computed`` tokens the caller has put
+        into the cache by other means (``Engine.assume_cached``) starts running from there."""
+        if self._lib.hbh_sched_assume_running(self._ptr, request._handle, int(computed)) != host.OK:
+            raise ValueError(f"request {request.request_id!r} is not waiting, or {computed} is not inside its tokens")
+
     def has_work(self) -> bool:
         return bool(self._lib.hbh_sched_has_work(self._ptr))
 
