@@ -110,3 +110,58 @@ def test_random_orders_keep_every_invariant(seed):
     m.check_invariants()
     assert all(p.free == p.total for p in m.pools) and m.free_slots == 4
     assert reused, "no page was ever used again: the test did not stress the pools"
+
+
+def test_step_inputs_are_packed_from_the_tables():
+    """The native packing of a step's integer inputs: tokens, positions from the requests'
+    lengths, sequence ids, cumulative counts, slots, wanted rows, block tables padded with -1;
+    and rows of a buffer that lives on are rewritten only when their request or its tables changed."""
+    import numpy as np
+
+    m = CacheManager([GLOBAL, CHUNK], [16, 16], page_size=4, max_requests=3)
+    m.open("a"); m.reserve("a", 9); m.commit("a", 9)          # a: 9 tokens in the cache
+    m.open("b")
+    m.reserve("a", 1); m.reserve("b", 6)                      # this step: a decodes, b brings 6 prompt tokens
+    handles = m.handles_of(["a", "b"])
+    widths = m.step_widths(handles)
+    assert widths == [3, 3]
+    n_new = np.array([1, 6], dtype=np.int32)
+    tokens = np.array([70, 11, 12, 13, 14, 15, 16], dtype=np.int32)
+    want_counts = np.array([1, 2], dtype=np.int32)
+    want = np.array([0, 2, 5], dtype=np.int32)
+    sizes = [7, 7, 7, 3, 2, 3, 2 * 3, 2 * 3]
+    offsets = np.cumsum([0] + [(s + 3) // 4 * 4 for s in sizes[:-1]]).astype(np.int64)
+    buf = np.full(int(offsets[-1]) + 8, -7, dtype=np.int32)
+    starts, slots = np.empty(2, dtype=np.int32), np.empty(2, dtype=np.int32)
+    row_request, row_version = np.full(2, -1, dtype=np.int64), np.full(2, -1, dtype=np.int64)
+
+    def pack():
+        code = m._lib.hbh_pack_step(m._ptr, 2, handles.ctypes.data, n_new.ctypes.data, tokens.ctypes.data,
+                                    want_counts.ctypes.data, want.ctypes.data, np.array(widths, dtype=np.int32).ctypes.data,
+                                    offsets.ctypes.data, buf.ctypes.data, starts.ctypes.data, slots.ctypes.data,
+                                    row_request.ctypes.data, row_version.ctypes.data)
+        assert code == 0
+
+    pack()
+    o = offsets
+    assert buf[o[0]: o[0] + 7].tolist() == tokens.tolist()
+    assert buf[o[1]: o[1] + 7].tolist() == [9, 0, 1, 2, 3, 4, 5]
+    assert buf[o[2]: o[2] + 7].tolist() == [0, 1, 1, 1, 1, 1, 1]
+    assert buf[o[3]: o[3] + 3].tolist() == [0, 1, 7]
+    assert buf[o[4]: o[4] + 2].tolist() == [m.slot("a"), m.slot("b")] == slots.tolist()
+    assert buf[o[5]: o[5] + 3].tolist() == [0, 1 + 2, 1 + 5] and starts.tolist() == [9, 0]
+    for g in range(2):
+        rows = buf[o[6 + g]: o[6 + g] + 6].reshape(2, 3)
+        assert rows[0].tolist() == m.table(g, "a") and rows[1].tolist() == m.table(g, "b") + [-1]
+    # nothing changed: the rows are left alone (a scribble survives); a row that held another
+    # request, or an older state of the tables, is rewritten
+    buf[o[6]] = 99
+    pack()
+    assert buf[o[6]] == 99
+    row_request[0] = 12345
+    pack()
+    assert buf[o[6]] == m.table(0, "a")[0]
+    buf[o[6]] = 99
+    row_version[0] -= 1
+    pack()
+    assert buf[o[6]] == m.table(0, "a")[0] and row_version[0] == m.table_version("a")
