@@ -1,7 +1,10 @@
 """The engine in process, with small pages so that every edge is crossed often: the four ways
 of cutting, long decoding, the first tokens, crafted weights that make one far key or one page
-matter, a schedule that runs a layer twice, generation through the entry point, and a toy mixer
-with state of its own registered from here."""
+matter, a schedule that runs a layer twice, generation through the entry point, and toy parts
+registered from here: a mixer with state of its own, a position encoding that is no rotation and
+a feed-forward with routing."""
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -244,3 +247,129 @@ def test_toy_mixer_with_state_registers_builds_and_steps(model_dirs):
         assert sliding["peak"] <= 2 * (9 // 4 + 3), "the sliding window kept pages it had passed"
     finally:
         registry.unregister("mixer", "toy_running_mean")
+
+
+# --------------------------------------------------------------------------- a toy position encoding and a toy routed feed-forward
+def test_toy_position_and_toy_routed_feed_forward_against_a_plain_model():
+    """A position encoding that is no rotation (a decay gamma^(query - key) put on q and k) and a
+    feed-forward that routes each token to one of three tiny experts, both defined here, are
+    registered, built into a model beside the framework's own parts, and stepped whole, in
+    portions and token by token; the logits are compared with a plain model written out below
+    from the plain functions and the toy formulas."""
+    from hi_b200.engine.core import Engine, StepEntry
+    from hi_b200.parts import registry
+    from hi_b200.parts.basic import Part
+    from hi_b200.parts.model import Model
+    from hi_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, TensorSpec
+
+    GAMMA = 0.97
+
+    @registry.register("position", "toy_decay")
+    class ToyDecay(Part):
+        graph_safe = True
+
+        def rotary_table(self):
+            return None
+
+        def apply(self, q, k, positions):
+            decay = torch.exp(positions.to(torch.float32)[:, None, None] * math.log(GAMMA))   # device work only:
+            return q.float() * decay, k.float() / decay                                          # the step may be captured
+
+    @registry.register("feed_forward", "toy_three_experts")
+    class ToyThreeExperts(Part):
+        graph_safe = True
+
+        def __init__(self, params, prefix, env):
+            super().__init__(params, prefix, env)
+            self.h = int(params["hidden_size"])
+
+        def tensor_specs(self):
+            return [TensorSpec(f"{self.prefix}.gate.weight", (3, self.h)),
+                    TensorSpec(f"{self.prefix}.experts.weight", (3, self.h, self.h))]
+
+        def load(self, fetch):
+            self.gate, self.experts = fetch(f"{self.prefix}.gate.weight"), fetch(f"{self.prefix}.experts.weight")
+
+        def forward(self, normed, ctx):
+            x = normed.float()
+            choice = (x @ self.gate.float().T).argmax(dim=1)
+            w = self.experts.float()[choice]                          # [n, h, h]
+            return torch.tanh(torch.einsum("nh,noh->no", x, w)).to(normed.dtype)
+
+    try:
+        H, V, NH, NKV, HD, EPS = 48, 61, 4, 2, 16, 1e-5
+        norm = lambda n: PartSpec("rmsnorm", {"name": n, "size": H, "eps": EPS})
+        attn = lambda pos, window: PartSpec("attention", {"name": "attn", "hidden_size": H, "num_heads": NH, "num_kv_heads": NKV,
+                                                          "head_dim": HD, "window": window, "position": pos})
+        rotary = PartSpec("rope", {"head_dim": HD, "theta": 10000.0, "scaling": None})
+        layers = (
+            LayerSpec(prefix="toy.layers.0", mixer=attn(PartSpec("toy_decay", {}), None), norm_mixer=norm("n1"),
+                      norm_feed_forward=norm("n2"),
+                      feed_forward=PartSpec("toy_three_experts", {"name": "ff", "hidden_size": H})),
+            LayerSpec(prefix="toy.layers.1", mixer=attn(rotary, ("chunk", 12)), norm_mixer=norm("n1"), norm_feed_forward=norm("n2"),
+                      feed_forward=PartSpec("dense_swiglu", {"name": "ff", "hidden_size": H, "intermediate_size": 56})),
+        )
+        spec = ModelSpec(hidden_size=H, vocab_size=V, layers=layers, schedule=ModelSpec.sequential(2),
+                         embedding=PartSpec("token_embedding", {"name": "toy.embed", "vocab_size": V, "hidden_size": H}),
+                         final_norm=norm("toy.norm"),
+                         head=PartSpec("linear_head", {"name": "toy.head", "vocab_size": V, "hidden_size": H}))
+        model = Model(spec, torch.float32, "cuda:0")
+        g = torch.Generator().manual_seed(11)
+        w = {}
+        for ts in model.tensor_specs():
+            w[ts.name] = torch.ones(ts.shape) if ts.init == "ones" else torch.randn(ts.shape, generator=g) * 0.25
+        model.load(lambda name: w[name].to("cuda:0"))
+        eng = Engine(model, kv_page_size=4, kv_cache_tokens=96, max_active_requests=2)
+        assert sorted(str(gr.window) for gr in eng.manager.groups) == ["('chunk', 12)", "None"]
+
+        def plain_model(tokens):
+            T = len(tokens)
+            pos = torch.arange(T)
+            x = w["toy.embed.weight"][tokens].float()
+            inv = plain.rope_inverse_frequencies(HD, 10000.0, None)
+            for i in range(2):
+                p = f"toy.layers.{i}"
+                z = plain.rms_norm(x, w[f"{p}.n1.weight"], EPS)
+                q = (z @ w[f"{p}.attn.q_proj.weight"].T).reshape(T, NH, HD)
+                k = (z @ w[f"{p}.attn.k_proj.weight"].T).reshape(T, NKV, HD)
+                v = (z @ w[f"{p}.attn.v_proj.weight"].T).reshape(T, NKV, HD)
+                if i == 0:      # the toy decay: score(t, s) = gamma^(t - s) q_t . k_s / sqrt(hd)
+                    q, k = q * GAMMA ** pos[:, None, None], k * GAMMA ** (-pos[:, None, None].float())
+                    a = plain.attention_core(q, k, v, None)
+                else:
+                    q, k = plain.apply_rope(q, pos, inv, False), plain.apply_rope(k, pos, inv, False)
+                    a = plain.attention_core(q, k, v, 12)
+                x = x + a @ w[f"{p}.attn.o_proj.weight"].T
+                z = plain.rms_norm(x, w[f"{p}.n2.weight"], EPS)
+                if i == 0:      # the toy experts: the largest gate logit picks one of three tanh layers
+                    choice = (z @ w[f"{p}.ff.gate.weight"].T).argmax(dim=1)
+                    x = x + torch.tanh(torch.einsum("nh,noh->no", z, w[f"{p}.ff.experts.weight"][choice]))
+                else:
+                    x = x + plain.swiglu(z, w[f"{p}.ff.gate_proj.weight"], w[f"{p}.ff.up_proj.weight"], w[f"{p}.ff.down_proj.weight"])
+            return plain.rms_norm(x, w["toy.norm.weight"], EPS) @ w["toy.head.weight"].T
+
+        toks = {"a": [(5 * i + 2) % V for i in range(41)], "b": [(11 * i + 7) % V for i in range(29)]}
+        want = {r: plain_model(t) for r, t in toks.items()}
+        for r, t in toks.items():                                   # whole
+            got = eng.step([StepEntry(r, t, list(range(len(t))))]).cpu()
+            eng.finish(r)
+            assert h.rel_err(got, want[r]) <= 2e-5, f"toy parts, whole: request {r}"
+        outs, at = {r: [] for r in toks}, {r: 0 for r in toks}      # both at once: portions, then token by token
+        sizes, i = [6, 2, 9, 1, 4], 0
+        while any(at[r] < len(toks[r]) for r in toks):
+            entries = []
+            for r, t in toks.items():
+                if at[r] < len(t):
+                    n = 1 if at[r] >= 24 else min(sizes[i % len(sizes)], len(t) - at[r]); i += 1
+                    entries.append(StepEntry(r, t[at[r]:at[r] + n], list(range(n))))
+                    at[r] += n
+            lg, row = eng.step(entries).cpu(), 0
+            for e in entries:
+                outs[e.request_id].append(lg[row:row + len(e.tokens)]); row += len(e.tokens)
+            eng.manager.check_invariants()
+        for r in toks:
+            assert h.rel_err(torch.cat(outs[r]), want[r]) <= 2e-5, f"toy parts, portions and decoding: request {r}"
+            eng.finish(r)
+    finally:
+        registry.unregister("position", "toy_decay")
+        registry.unregister("feed_forward", "toy_three_experts")
