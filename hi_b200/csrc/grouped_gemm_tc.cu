@@ -7,7 +7,9 @@
 // really has (rounded up to 16, at most 192 per tile), so an expert with 5 or 140 tokens costs
 // 16 or 144 columns of tensor-core time, and a weight tile is brought into the SM once for up
 // to 192 tokens. What bounds these products is how many weight bytes a block has in flight: a
-// stage is 32 KB of weights (DUAL) beside at most 24 KB of tokens, four stages deep.
+// stage is 32 KB of weights (DUAL) beside at most 24 KB of tokens, four stages deep; in
+// decode-sized steps a tile holds at most 64 tokens (8 KB) and the ring is five / eight stages
+// deep (measured at 64 tokens over 16 experts: 427 -> 415 us and 235 -> 222 us).
 // Persistent blocks (one per SM) walk the tiles (expert, 128 features, up to 192 tokens):
 //   warp 0      one lane issues the TMA loads (W tile 128x64, twice when DUAL; X tile of 32, 64,
 //               128 or 192 rows x 64; 128-byte swizzle) into a ring of stages, signalled by
@@ -41,7 +43,9 @@
 namespace {
 
 constexpr int BF = 128;          // features (weight rows) of a tile: UMMA M
-constexpr int BT = 192;          // most tokens of a tile: UMMA N (the X tile of a stage is BT x 64)
+constexpr int BT_LONG = 192;     // most tokens of a tile (UMMA N; the X tile of a stage is BT x 64) in steps of many
+constexpr int SHORT_STEP_ROWS = 256;   // steps of up to this many routed rows use BT_SHORT
+constexpr int BT_SHORT = 64;     // tokens, and in decode-sized steps: less room for tokens, more stages of weights
 constexpr int SLOT_COLS = 256;   // tensor memory is two slots of 256 columns
 constexpr int TMEM_COLS = 2 * SLOT_COLS;
 constexpr int DUAL_SLOT_T = 128; // a DUAL tile of up to this many tokens has both accumulators in one slot
@@ -61,7 +65,10 @@ struct Params {
                              // (not DUAL; `out` starts as zeros; two addends give the same sum in either order)
 };
 
-__host__ __device__ constexpr int x_box_rows(int box) { return box == 0 ? 32 : (box == 1 ? 64 : (box == 2 ? 128 : BT)); }
+__host__ __device__ constexpr int x_box_rows(int box, int bt) {
+  const int rows = box == 0 ? 32 : (box == 1 ? 64 : (box == 2 ? 128 : bt));
+  return rows < bt ? rows : bt;
+}
 
 struct Maps {                // X boxes of 32, 64, 128 and 192 rows; the weight stacks
   CUtensorMap x[4];
@@ -72,6 +79,7 @@ struct Maps {                // X boxes of 32, 64, 128 and 192 rows; the weight 
 // share a weight tile are neighbours, so they run at the same time and the weight tile comes from
 // HBM once. Returns false past the last tile. `f_tiles` = feature tiles.
 struct Tile { int expert, row0, tokens, f0, k_part; };
+template <int BT>
 __device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t, int f_tiles, int k_splits, Tile& out) {
   for (int e = 0; e < experts; ++e) {
     const int begin = offsets[e], cnt = offsets[e + 1] - begin;
@@ -110,7 +118,7 @@ struct SlotWalk {
 
 // Persistent: each block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... The shared-memory
 // ring runs on across tiles.
-template <bool DUAL, int STAGES>
+template <bool DUAL, int STAGES, int BT>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
   constexpr int W_BYTES = BF * BK * 2, X_BYTES = BT * BK * 2;
@@ -149,9 +157,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
       uint32_t it = 0;                          // stages filled so far, over all tiles
       bool ok = true;
       Tile tile;
-      for (int t = blockIdx.x; ok && find_tile(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
+      for (int t = blockIdx.x; ok && find_tile<BT>(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
         const int box = tile.tokens <= 32 ? 0 : (tile.tokens <= 64 ? 1 : (tile.tokens <= 128 ? 2 : 3));
-        const uint32_t bytes = NW * W_BYTES + (uint32_t)x_box_rows(box) * BK * 2;
+        const uint32_t bytes = NW * W_BYTES + (uint32_t)x_box_rows(box, BT) * BK * 2;
         const int w_row = tile.expert * p.n_out + tile.f0;
         const int kb0 = tile.k_part * kb_per_part, kb1 = min(num_kb, kb0 + kb_per_part);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -171,7 +179,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
       SlotWalk walk;
       bool ok = true;
       Tile tile;
-      for (int t = blockIdx.x; ok && find_tile(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
+      for (int t = blockIdx.x; ok && find_tile<BT>(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
         bool both;
         const int b = walk.take(DUAL, tile.tokens, both);
         for (int q = b; ok && q <= (both ? 1 : b); ++q)      // the slot(s) must have been written out
@@ -208,7 +216,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
     SlotWalk walk;
     bool ok = true;
     Tile tile;
-    for (int t = blockIdx.x; ok && find_tile(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
+    for (int t = blockIdx.x; ok && find_tile<BT>(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
       bool both;
       const int b = walk.take(DUAL, tile.tokens, both);
       const int f = tile.f0 + quarter * 32 + lane;        // this thread's feature = its lane of tensor memory
@@ -320,18 +328,19 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
   for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) d[i] = s[i];
 }
 
-template <bool DUAL, int STAGES>
+template <bool DUAL, int STAGES, int BT>
 int launch(const void* x, const void* w0, const void* w1, const Params& p, int max_tiles, cudaStream_t stream) {
   Maps maps;
   for (int b = 0; b < 4; ++b)
-    if (!tc::make_map_bf16(&maps.x[b], x, (uint64_t)p.rows, (uint64_t)p.K, (uint32_t)x_box_rows(b))) return HB_ERR_UNSUPPORTED;
+    if (!tc::make_map_bf16(&maps.x[b], x, (uint64_t)p.rows, (uint64_t)p.K, (uint32_t)x_box_rows(b, BT))) return HB_ERR_UNSUPPORTED;
   if (!tc::make_map_bf16(&maps.w0, w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BF) ||
       !tc::make_map_bf16(&maps.w1, DUAL ? w1 : w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BF))
     return HB_ERR_UNSUPPORTED;
   constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * BF * BK * 2 + BT * BK * 2;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 128 + 4 * ((size_t)p.experts + 1);
+  static_assert((2 * STAGES + 4) * 8 + 8 <= 256, "the barriers and the tensor-memory slot fit their 256 bytes");
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + 4 * ((size_t)p.experts + 1);
   if (smem > 227 * 1024) return HB_ERR_UNSUPPORTED;
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<DUAL, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<DUAL, STAGES, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
   int dev = 0, sms = 0;
@@ -339,7 +348,7 @@ int launch(const void* x, const void* w0, const void* w1, const Params& p, int m
     return HB_ERR_BAD_ARG;
   const long long upper = (long long)max_tiles * ((p.n_out + BF - 1) / BF) * p.k_splits;    // tiles there can be at most
   const int grid = (int)(upper < sms ? upper : sms);                            // one persistent block per SM
-  grouped_gemm_tc_kernel<DUAL, STAGES><<<grid, THREADS, smem, stream>>>(maps, p);
+  grouped_gemm_tc_kernel<DUAL, STAGES, BT><<<grid, THREADS, smem, stream>>>(maps, p);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -364,10 +373,13 @@ extern "C" int hb_moe_gate_up_tc(const void* xs, const int* sorted_entry, const 
     return HB_ERR_BAD_ARG;
   if (hidden % 8 != 0 || inter % 8 != 0 || hidden <= 0 || inter <= 0) return HB_ERR_UNSUPPORTED;
   if (rows == 0) return HB_OK;
-  const int max_tiles = (rows + BT - 1) / BT + (experts < rows ? experts : rows);
+  const bool few = rows <= SHORT_STEP_ROWS;
+  const int bt = few ? BT_SHORT : BT_LONG;
+  const int max_tiles = (rows + bt - 1) / bt + (experts < rows ? experts : rows);
   if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
   Params p{offsets, sorted_entry, scores, act, status, experts, inter, hidden, rows, 1};
-  return launch<true, 4>(xs, w_gate, w_up, p, max_tiles, stream);
+  return few ? launch<true, 5, BT_SHORT>(xs, w_gate, w_up, p, max_tiles, stream)
+             : launch<true, 4, BT_LONG>(xs, w_gate, w_up, p, max_tiles, stream);
 }
 
 // down projection on tensor cores: act [rows, inter] -> y float32 [rows, hidden].
@@ -376,7 +388,9 @@ extern "C" int hb_moe_down_tc(const void* act, const void* w_down, const int* of
   if (!act || !w_down || !offsets || !y || !status || rows < 0 || experts <= 0) return HB_ERR_BAD_ARG;
   if (hidden % 8 != 0 || inter % 8 != 0 || hidden <= 0 || inter <= 0) return HB_ERR_UNSUPPORTED;
   if (rows == 0) return HB_OK;
-  const int max_tiles = (rows + BT - 1) / BT + (experts < rows ? experts : rows);
+  const bool few = rows <= SHORT_STEP_ROWS;
+  const int bt = few ? BT_SHORT : BT_LONG;
+  const int max_tiles = (rows + bt - 1) / bt + (experts < rows ? experts : rows);
   if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
   // With few tokens per expert (decode batches) there are f_tiles x experts equal tiles; when
   // that is only a few rounds over the SMs, the last, partly filled round costs much. Halving
@@ -392,5 +406,6 @@ extern "C" int hb_moe_down_tc(const void* act, const void* w_down, const int* of
     if (e != cudaSuccess) return (int)e;
   }
   Params p{offsets, nullptr, nullptr, y, status, experts, hidden, inter, rows, k_splits};
-  return launch<false, 5>(act, w_down, nullptr, p, max_tiles, stream);
+  return few ? launch<false, 8, BT_SHORT>(act, w_down, nullptr, p, max_tiles, stream)
+             : launch<false, 5, BT_LONG>(act, w_down, nullptr, p, max_tiles, stream);
 }
