@@ -72,8 +72,8 @@ class SigmoidRoutedExperts(Part):
 
     graph_safe = True
 
-    FEW_ROWS = 16    # up to this many routed rows the weight-streaming kernel is used (measured: above
-                     # it the tcgen05 kernel streams the expert weights faster, even with nearly empty tiles)
+    FEW_ROWS = 12    # up to this many routed rows the weight-streaming kernel is used (measured: from 16
+                     # rows the tcgen05 kernel streams the expert weights faster, even with nearly empty tiles)
     wants_f32_input = True   # the router reads the norm's float32 output
     OVERLAP_SHARED = True    # run the shared expert on a second stream beside the routed path
 
