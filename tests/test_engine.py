@@ -158,6 +158,29 @@ def test_seeded_sampling_does_not_depend_on_batching(model_dirs):
     assert together == alone
 
 
+def test_generation_with_so_few_pages_that_requests_are_preempted(model_dirs):
+    """Four requests in a cache that cannot hold them all to the end: decoding runs out of pages,
+    the scheduler preempts the youngest request (its pages go back, it is computed again from its
+    prompt and the tokens it had generated), and every request still ends with exactly the tokens
+    it generates alone: greedy, and sampled with a seed (the generator's state survives)."""
+    import hi_b200
+
+    cfg, mdir = model_dirs["A"]
+    prompts = [h.random_tokens(cfg, n, seed=90 + n) for n in (30, 26, 21, 17)]
+    for sp in ([hi_b200.SamplingParams(max_tokens=40, ignore_eos=True)] * 4,
+               [hi_b200.SamplingParams(max_tokens=40, temperature=0.8, seed=3 + i, ignore_eos=True) for i in range(4)]):
+        roomy = hi_b200.LLM(mdir, dtype="float32", kv_page_size=8, max_batch_size=4, kv_cache_tokens=1024)
+        alone = [roomy.generate([p], [s])[0].token_ids for p, s in zip(prompts, sp)]
+        tight = hi_b200.LLM(mdir, dtype="float32", kv_page_size=8, max_batch_size=4, kv_cache_tokens=176,
+                            windowed_cache_tokens=176)
+        outs = tight.generate(prompts, sp)
+        assert sum(o.preemptions for o in outs) >= 1, "the pool was large enough: nothing was preempted"
+        assert [o.token_ids for o in outs] == alone
+        assert all(o.finish_reason == "length" and o.completion_tokens == 40 for o in outs)
+        tight.engine.manager.check_invariants()
+        assert not tight.engine.manager.requests and all(p.free == p.total for p in tight.engine.manager.pools)
+
+
 # --------------------------------------------------------------------------- a toy mixer with state
 def test_toy_mixer_with_state_registers_builds_and_steps(model_dirs):
     """A mixer defined here, with per-request state of fixed size (a running mean of a projection),
