@@ -100,17 +100,22 @@ int hbh_sched_abort(void* sched, int64_t request);
 // benchmarks only: a waiting request whose first `computed` tokens are in the cache already runs from there
 int hbh_sched_assume_running(void* sched, int64_t request, int64_t computed);
 int hbh_sched_has_work(void* sched);
-// Decide the next step. entries: (request, first token index, token count, samples) x n_entries;
-// preempted: requests sent back to the head of the waiting queue (released already);
-// dropped: requests finished as insufficient_gpu_memory (a lone decode that cannot get a page).
-int hbh_sched_plan(void* sched, int64_t* entries, int cap_entries, int* n_entries, int64_t* preempted, int cap_preempted,
-                   int* n_preempted, int64_t* dropped, int cap_dropped, int* n_dropped);
-// The planned step ran. stop[i] for the i-th SAMPLING entry of the plan: nonzero = the sampled
-// token ends the request and is not emitted; zero = it is appended. finished: (request, reason)
+// Decide the next step. entries: (request, first token index, token count, samples, last token in
+// flight) x n_entries: "in flight" = the entry's last token is the one the step before samples, so
+// the host does not know its value yet. preempted: requests sent back to the head of the waiting
+// queue (released already); dropped: requests finished as insufficient_gpu_memory (a lone decode
+// that cannot get a page). The plan counts as carried out at once (tokens computed, samples in
+// flight); a second plan may be made before the first is committed, not a third.
+int hbh_sched_plan(void* sched, int64_t* plan_id, int64_t* entries, int cap_entries, int* n_entries, int64_t* preempted,
+                   int cap_preempted, int* n_preempted, int64_t* dropped, int cap_dropped, int* n_dropped);
+// The oldest outstanding plan's samples are known. stop[i] for the i-th SAMPLING entry of that
+// plan: nonzero = the sampled token ends the request and is not emitted; zero = it is appended
+// (flags of entries whose request has ended meanwhile are ignored). finished: (request, reason)
 // pairs, reason 1 = length, 2 = stop.
-int hbh_sched_commit(void* sched, const int* stop, int n_stop, int64_t* finished, int cap, int* n_finished);
+int hbh_sched_commit(void* sched, int64_t plan_id, const int* stop, int n_stop, int64_t* finished, int cap,
+                     int* n_finished);
 // what: 0 status (0 waiting, 1 running, 2 finished), 1 computed, 2 preemptions, 3 output length,
-//       4 finish reason (0 none, 1 length, 2 stop, 3 aborted, 4 insufficient_gpu_memory)
+//       4 finish reason (0 none, 1 length, 2 stop, 3 aborted, 4 insufficient_gpu_memory), 5 samples in flight
 int64_t hbh_sched_request_stat(void* sched, int64_t request, int what);
 int hbh_sched_queue(void* sched, int which, int64_t* out, int cap);    // 0 waiting, 1 running; returns the count
 // what: 0 admitted, 1 preemptions, 2 steps, 3 shrunk portions, 4 stalled portions

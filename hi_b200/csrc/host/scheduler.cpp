@@ -10,6 +10,12 @@
 //      with prompt + generated tokens as its prompt;
 //   4. a request that could never fit is refused when it is added (insufficient_gpu_memory,
 //      crates/hi-cuda/src/lib.rs:845-858).
+//
+// One step may be planned while the step before it still runs: a plan advances `computed` and
+// counts a token "in flight" for every entry that samples, so the next plan can already hold that
+// request's next decode token (its value then comes from the device, not from the host). Plans
+// are committed in the order they were made, at most two are outstanding. A request that ends
+// while a later plan already holds an entry of it leaves that entry void: it runs, nobody reads it.
 #include <algorithm>
 #include <deque>
 #include <string>
@@ -26,14 +32,23 @@ enum Reason { NONE = 0, LENGTH = 1, STOP = 2, ABORTED = 3, NO_MEMORY = 4 };
 struct Request {
   int64_t id = 0;
   int64_t prompt_len = 0, output_len = 0, computed = 0, max_tokens = 0, preemptions = 0;
+  int64_t in_flight = 0;       // tokens sampled by planned steps that are not committed yet
   int status = WAITING, reason = NONE;
-  int64_t pending() const { return prompt_len + output_len - computed; }
+  int64_t pending() const { return prompt_len + output_len + in_flight - computed; }
+  bool may_sample_more() const { return output_len + in_flight < max_tokens; }
 };
 
 struct Entry {
   Request* request;
   int64_t begin, count;
   bool samples;
+  bool last_in_flight;         // its last token is sampled by the step before: the host does not know it yet
+  bool is_void = false;        // the request ended (or was dropped) after this entry was planned
+};
+
+struct Plan {
+  int64_t id = 0;
+  std::vector<Entry> entries;
 };
 
 class Scheduler {
@@ -47,8 +62,8 @@ class Scheduler {
   bool abort(int64_t id);
   int assume_running(int64_t id, int64_t computed);
   bool has_work() const { return !waiting_.empty() || !running_.empty(); }
-  void plan();
-  int commit(const int* stop, int n_stop);
+  int plan();
+  int commit(int64_t plan_id, const int* stop, int n_stop);
   Request* find(int64_t id) {
     auto it = requests_.find(id);
     return it == requests_.end() ? nullptr : &it->second;
@@ -63,7 +78,9 @@ class Scheduler {
   void* release_user = nullptr;
   std::deque<Request*> waiting_;
   std::vector<Request*> running_;          // in admission order
-  std::vector<Entry> entries_;             // the last plan
+  std::vector<Entry> entries_;             // the plan being made / made last
+  std::deque<Plan> outstanding_;           // planned, not committed yet (oldest first; at most two)
+  int64_t last_plan_id = 0, current_plan_id = 0;   // ids start at 1; an empty plan has id 0 and is not kept
   std::vector<int64_t> preempted_, dropped_, finished_;   // of the last plan / the last commit (finished: id, reason)
   int64_t admitted = 0, preemptions = 0, steps = 0, shrunk = 0, stalled = 0;
 
@@ -76,7 +93,17 @@ class Scheduler {
   void finish(Request* r, int reason) {
     r->status = FINISHED;
     r->reason = reason;
+    running_.erase(std::remove(running_.begin(), running_.end(), r), running_.end());
+    waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), r), waiting_.end());
+    for (Plan& p : outstanding_)           // what later plans hold of it runs for nobody
+      for (Entry& e : p.entries)
+        if (e.request == r) e.is_void = true;
     release(r->id);
+  }
+  Entry make_entry(Request* r, int64_t count) const {
+    const int64_t known = r->prompt_len + r->output_len;                 // tokens whose values the host has
+    const bool samples = r->computed + count == known + r->in_flight;
+    return Entry{r, r->computed, count, samples, r->computed + count > known};
   }
   void needed(const Request* r, int64_t n, std::vector<int>& out) const {
     // an open request is measured from its tables; one not yet in the cache from `computed`
@@ -151,8 +178,6 @@ int Scheduler::add(int64_t id, int64_t prompt_len, int64_t max_tokens) {
 bool Scheduler::abort(int64_t id) {
   Request* r = find(id);
   if (!r || r->status == FINISHED) return false;
-  running_.erase(std::remove(running_.begin(), running_.end(), r), running_.end());
-  waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), r), waiting_.end());
   finish(r, ABORTED);
   return true;
 }
@@ -193,10 +218,14 @@ void Scheduler::plan_portion(Request* r, std::vector<int>& promised, int64_t bud
   }
   if (n < want) ++shrunk;
   promise(r, n, promised);
-  entries_.push_back(Entry{r, r->computed, n, r->computed + n == r->prompt_len + r->output_len});
+  entries_.push_back(make_entry(r, n));
 }
 
-void Scheduler::plan() {
+int Scheduler::plan() {
+  if (outstanding_.size() >= 2) {
+    error = "two plans are outstanding already: commit the older one first";
+    return HBH_ERR_ARG;
+  }
   entries_.clear();
   preempted_.clear();
   dropped_.clear();
@@ -206,7 +235,7 @@ void Scheduler::plan() {
   // 1. every running request that has one token pending decodes, oldest first
   std::vector<Request*> decoding;
   for (Request* r : running_)
-    if (r->pending() == 1 && r->computed >= r->prompt_len) decoding.push_back(r);
+    if (r->pending() == 1 && r->computed >= r->prompt_len && r->may_sample_more()) decoding.push_back(r);
   std::vector<Request*> planned;           // requests with a decode entry in this plan
   size_t i = 0;
   while (i < decoding.size() && budget > 0 && (int)entries_.size() < max_batch_) {
@@ -217,7 +246,7 @@ void Scheduler::plan() {
     }
     if (fits(r, 1, promised)) {
       promise(r, 1, promised);
-      entries_.push_back(Entry{r, r->computed, 1, true});
+      entries_.push_back(make_entry(r, 1));
       planned.push_back(r);
       --budget;
       ++i;
@@ -225,7 +254,6 @@ void Scheduler::plan() {
     }
     Request* victim = running_.back();
     if (victim == r && running_.size() == 1) {
-      running_.pop_back();
       finish(r, NO_MEMORY);
       dropped_.push_back(r->id);
       ++i;
@@ -249,7 +277,8 @@ void Scheduler::plan() {
   // 2. running requests still in their prompt get portions, oldest first
   for (Request* r : std::vector<Request*>(running_)) {
     if (budget <= 0 || (int)entries_.size() >= max_batch_) break;
-    if (std::find(planned.begin(), planned.end(), r) != planned.end() || r->pending() <= 0) continue;
+    if (std::find(planned.begin(), planned.end(), r) != planned.end() || r->pending() <= 0 || !r->may_sample_more())
+      continue;                                  // planned, or only waiting for its last sample to be committed
     plan_portion(r, promised, budget);
     budget = budget_ - planned_tokens();
   }
@@ -271,32 +300,52 @@ void Scheduler::plan() {
       budget = budget_ - planned_tokens();
     }
   }
+  // the plan is taken as carried out: its tokens count as computed, its samples as in flight
+  for (const Entry& e : entries_) {
+    e.request->computed += e.count;
+    if (e.samples) ++e.request->in_flight;
+  }
   ++steps;
+  if (entries_.empty()) {                  // nothing to run, nothing to commit
+    current_plan_id = 0;
+    return HBH_OK;
+  }
+  Plan p;
+  p.id = current_plan_id = ++last_plan_id;
+  p.entries = entries_;
+  outstanding_.push_back(std::move(p));
+  return HBH_OK;
 }
 
-int Scheduler::commit(const int* stop, int n_stop) {
+int Scheduler::commit(int64_t plan_id, const int* stop, int n_stop) {
+  if (outstanding_.empty() || outstanding_.front().id != plan_id) {
+    error = "plans are committed in the order they were made";
+    return HBH_ERR_ARG;
+  }
   finished_.clear();
+  Plan plan = std::move(outstanding_.front());
+  outstanding_.pop_front();
   int s = 0;
-  for (const Entry& e : entries_) {
-    Request* r = e.request;
-    r->computed += e.count;
+  for (const Entry& e : plan.entries) {
     if (!e.samples) continue;
     if (s >= n_stop) return HBH_ERR_ARG;
+    const bool stops = stop[s++] != 0;
+    if (e.is_void) continue;               // the request ended before this entry's sample was read
+    Request* r = e.request;
+    --r->in_flight;
     int reason = NONE;
-    if (stop[s++]) {
+    if (stops) {
       reason = STOP;                       // the ending token is not emitted (crates/hi-mlx/src/models.rs:598-600)
     } else {
       ++r->output_len;
       if (r->output_len >= r->max_tokens) reason = LENGTH;
     }
     if (reason != NONE) {
-      running_.erase(std::remove(running_.begin(), running_.end(), r), running_.end());
       finish(r, reason);
       finished_.push_back(r->id);
       finished_.push_back(reason);
     }
   }
-  entries_.clear();
   return HBH_OK;
 }
 
@@ -328,29 +377,33 @@ int hbh_sched_assume_running(void* sched, int64_t request, int64_t computed) {
 }
 int hbh_sched_has_work(void* sched) { return static_cast<Scheduler*>(sched)->has_work() ? 1 : 0; }
 
-int hbh_sched_plan(void* sched, int64_t* entries, int cap_entries, int* n_entries, int64_t* preempted, int cap_preempted,
-                   int* n_preempted, int64_t* dropped, int cap_dropped, int* n_dropped) {
+int hbh_sched_plan(void* sched, int64_t* plan_id, int64_t* entries, int cap_entries, int* n_entries, int64_t* preempted,
+                   int cap_preempted, int* n_preempted, int64_t* dropped, int cap_dropped, int* n_dropped) {
   Scheduler* s = static_cast<Scheduler*>(sched);
-  s->plan();
+  const int rc = s->plan();
+  if (rc != HBH_OK) return rc;
+  *plan_id = s->current_plan_id;
   *n_entries = (int)s->entries_.size();
   *n_preempted = (int)s->preempted_.size();
   *n_dropped = (int)s->dropped_.size();
   if (*n_entries > cap_entries || *n_preempted > cap_preempted || *n_dropped > cap_dropped) return HBH_ERR_CAPACITY;
   for (int i = 0; i < *n_entries; ++i) {
     const hbh::Entry& e = s->entries_[i];
-    entries[4 * i] = e.request->id;
-    entries[4 * i + 1] = e.begin;
-    entries[4 * i + 2] = e.count;
-    entries[4 * i + 3] = e.samples ? 1 : 0;
+    entries[5 * i] = e.request->id;
+    entries[5 * i + 1] = e.begin;
+    entries[5 * i + 2] = e.count;
+    entries[5 * i + 3] = e.samples ? 1 : 0;
+    entries[5 * i + 4] = e.last_in_flight ? 1 : 0;
   }
   std::copy(s->preempted_.begin(), s->preempted_.end(), preempted);
   std::copy(s->dropped_.begin(), s->dropped_.end(), dropped);
   return HBH_OK;
 }
 
-int hbh_sched_commit(void* sched, const int* stop, int n_stop, int64_t* finished, int cap, int* n_finished) {
+int hbh_sched_commit(void* sched, int64_t plan_id, const int* stop, int n_stop, int64_t* finished, int cap,
+                     int* n_finished) {
   Scheduler* s = static_cast<Scheduler*>(sched);
-  const int r = s->commit(stop, n_stop);
+  const int r = s->commit(plan_id, stop, n_stop);
   if (r != HBH_OK) return r;
   *n_finished = (int)s->finished_.size() / 2;
   if (*n_finished > cap) return HBH_ERR_CAPACITY;
@@ -367,6 +420,7 @@ int64_t hbh_sched_request_stat(void* sched, int64_t request, int what) {
     case 2: return r->preemptions;
     case 3: return r->output_len;
     case 4: return r->reason;
+    case 5: return r->in_flight;
   }
   return HBH_ERR_ARG;
 }

@@ -29,6 +29,7 @@ from ..host import build as host
 from ..sampling.sampler import DEFAULT_SEED, Lcg, SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+IN_FLIGHT = -1     # in a planned entry's tokens: the token that the step before samples (its value is on the device)
 _STATUS = {0: WAITING, 1: RUNNING, 2: FINISHED}
 _REASON = {0: None, 1: "length", 2: "stop", 3: "aborted", 4: "insufficient_gpu_memory"}
 
@@ -113,7 +114,7 @@ class Request:
 @dataclass
 class PlannedEntry:
     request: Request
-    tokens: List[int]
+    tokens: List[int]      # the last one is IN_FLIGHT when the step before samples it
     samples: bool          # the portion ends at the request's last token: its logits are wanted
 
 
@@ -121,6 +122,7 @@ class PlannedEntry:
 class StepPlan:
     entries: List[PlannedEntry] = field(default_factory=list)
     preempted: List[Request] = field(default_factory=list)
+    plan_id: int = 0
 
     @property
     def n_tokens(self) -> int:
@@ -172,7 +174,7 @@ class Scheduler:
         self.counters = _Counters(self)
         cap = max(config.max_batch_size, manager.max_requests, 1) + 1
         self._cap = cap
-        self._entries = (ctypes.c_int64 * (4 * cap))()
+        self._entries = (ctypes.c_int64 * (5 * cap))()
         self._preempted = (ctypes.c_int64 * cap)()
         self._dropped = (ctypes.c_int64 * cap)()
         self._finished = (ctypes.c_int64 * (2 * cap))()
@@ -254,17 +256,23 @@ class Scheduler:
 
     # ------------------------------------------------------------------ planning
     def plan(self) -> StepPlan:
-        """Decide the next step. Preemptions are carried out (through ``release``) here."""
+        """Decide the next step. Preemptions are carried out (through ``release``) here. The plan
+        counts as carried out at once; a second plan may be made before the first is committed
+        (its entries then hold ``IN_FLIGHT`` where the first one's sample goes), not a third."""
         c = self._counts
-        code = self._lib.hbh_sched_plan(self._ptr, self._entries, self._cap, ctypes.byref(c, 0), self._preempted, self._cap,
-                                        ctypes.byref(c, 4), self._dropped, self._cap, ctypes.byref(c, 8))
+        plan_id = ctypes.c_int64(0)
+        code = self._lib.hbh_sched_plan(self._ptr, ctypes.byref(plan_id), self._entries, self._cap, ctypes.byref(c, 0),
+                                        self._preempted, self._cap, ctypes.byref(c, 4), self._dropped, self._cap,
+                                        ctypes.byref(c, 8))
         if code != host.OK:
-            raise RuntimeError(f"the native scheduler failed to plan (code {code})")
-        plan = StepPlan()
+            raise RuntimeError(f"the native scheduler failed to plan (code {code}): "
+                               f"{self._lib.hbh_sched_error(self._ptr).decode()}")
+        plan = StepPlan(plan_id=plan_id.value)
         for i in range(c[0]):
-            h, begin, count, samples = self._entries[4 * i: 4 * i + 4]
+            h, begin, count, samples, in_flight = self._entries[5 * i: 5 * i + 5]
             r = self._live[h]
-            plan.entries.append(PlannedEntry(r, r.span(begin, begin + count), bool(samples)))
+            toks = r.span(begin, begin + count - 1) + [IN_FLIGHT] if in_flight else r.span(begin, begin + count)
+            plan.entries.append(PlannedEntry(r, toks, bool(samples)))
         plan.preempted = [self._live[self._preempted[i]] for i in range(c[1])]
         for i in range(c[2]):            # a lone decode that cannot get a page
             self._let_go(self._live[self._dropped[i]], "insufficient_gpu_memory")
@@ -274,21 +282,29 @@ class Scheduler:
     def commit(self, plan: StepPlan, sampled: Dict[Hashable, int]) -> List[Request]:
         """The step ran; ``sampled`` holds one token for every entry with ``samples``.
         Returns the requests that finished (their cache is released here)."""
-        stops = []
+        if not plan.entries:                # an empty plan was never outstanding
+            return []
+        stops, appended = [], []
         for e in plan.entries:
             if not e.samples:
                 continue
             r = e.request
+            if r._scheduler is None:        # it ended after this entry was planned: nobody reads the sample
+                stops.append(0)
+                continue
             tok = int(sampled[r.request_id])
             stop = (tok in self.eos and not r.params.ignore_eos) or tok in r.params.stop_token_ids
             if not stop:                    # EOS is not emitted (crates/hi-mlx/src/models.rs:598-600)
-                r.output.append(tok)
+                appended.append((r, tok))
             stops.append(1 if stop else 0)
         n = ctypes.c_int(0)
-        code = self._lib.hbh_sched_commit(self._ptr, (ctypes.c_int * max(len(stops), 1))(*stops), len(stops),
+        code = self._lib.hbh_sched_commit(self._ptr, plan.plan_id, (ctypes.c_int * max(len(stops), 1))(*stops), len(stops),
                                           self._finished, self._cap, ctypes.byref(n))
         if code != host.OK:
-            raise RuntimeError(f"the native scheduler failed to commit (code {code}): is this its last plan?")
+            raise RuntimeError(f"the native scheduler failed to commit (code {code}): "
+                               f"{self._lib.hbh_sched_error(self._ptr).decode()}")
+        for r, tok in appended:
+            r.output.append(tok)
         done: List[Request] = []
         for i in range(n.value):
             r = self._live[self._finished[2 * i]]

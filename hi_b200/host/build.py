@@ -93,7 +93,7 @@ _SIGNATURES = {
     "hbh_sched_create": (P, [P, I, I, I, I, L]), "hbh_sched_destroy": (None, [P]),
     "hbh_sched_error": (ctypes.c_char_p, [P]), "hbh_sched_set_release": (None, [P, P, P]),
     "hbh_sched_add": (I, [P, L, I, I]), "hbh_sched_abort": (I, [P, L]), "hbh_sched_has_work": (I, [P]), "hbh_sched_assume_running": (I, [P, L, L]),
-    "hbh_sched_plan": (I, [P, P, I, P, P, I, P, P, I, P]), "hbh_sched_commit": (I, [P, P, I, P, I, P]),
+    "hbh_sched_plan": (I, [P, P, P, I, P, P, I, P, P, I, P]), "hbh_sched_commit": (I, [P, L, P, I, P, I, P]),
     "hbh_sched_request_stat": (L, [P, L, I]), "hbh_sched_queue": (I, [P, I, P, I]), "hbh_sched_counter": (L, [P, I]),
     "hbh_sched_forget": (None, [P, L]),
 }

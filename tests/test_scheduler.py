@@ -152,3 +152,85 @@ def test_random_workloads_finish_and_leak_nothing(seed):
         assert steps < 5000, "the scheduler does not make progress"
     assert all(r.status == FINISHED and len(r.output) == r.params.max_tokens for r in reqs)
     assert all(p.free == p.total for p in mgr.pools) and mgr.free_slots == 4
+
+
+def run_ahead(mgr, sched, token_of):
+    """The loop of a caller that plans step t+1 while step t still runs: the plan is 'launched'
+    (pages reserved and committed) at once, the step before it is committed only afterwards."""
+    in_flight, done, steps = None, [], 0
+    while sched.has_work() or in_flight is not None:
+        plan = sched.plan() if sched.has_work() else None
+        if plan is not None:
+            for e in plan.entries:
+                rid = e.request.request_id
+                if not mgr.is_open(rid):
+                    mgr.open(rid)
+                mgr.reserve(rid, len(e.tokens))
+            for e in plan.entries:
+                mgr.commit(e.request.request_id, len(e.tokens))
+        if in_flight is not None:
+            sampled = {e.request.request_id: token_of(e.request) for e in in_flight.entries if e.samples}
+            done += sched.commit(in_flight, sampled)
+        mgr.check_invariants()
+        in_flight = plan if plan is not None and plan.entries else None
+        steps += 1
+        assert steps < 5000, "the scheduler does not make progress"
+    return done
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_planning_one_step_ahead_gives_the_same_outputs(seed):
+    """Planning step t+1 before step t is committed: the entries of t+1 hold IN_FLIGHT where t's
+    sample goes, a request that stops at t leaves a void entry in t+1, preemption still works, and
+    every request ends with the tokens and the reason it has when each step is committed at once."""
+    from hi_b200.engine.scheduler import IN_FLIGHT
+
+    def token_of(r):             # the next token is a function of the request and how far it is
+        return 9 if (r.request_id * 7 + len(r.output)) % 11 == 5 else 20 + (r.request_id + len(r.output)) % 30
+
+    def workload():
+        rng = random.Random(seed)
+        return [req(i, rng.randint(1, 30), max_tokens=rng.randint(1, 14)) for i in range(10)]
+
+    results = []
+    for ahead in (False, True):
+        rng = random.Random(100 + seed)
+        mgr, s = make(pages=(rng.randint(10, 20),) * 2, page=4, slots=4, eos=(9,), max_batched_tokens=rng.choice([8, 24]),
+                      max_batch_size=3, max_active_requests=4)
+        for r in workload():
+            s.add(r)
+        if ahead:
+            done = run_ahead(mgr, s, token_of)
+        else:
+            done = []
+            while s.has_work():
+                done += run_step(mgr, s, token_of)[1]
+        assert len(done) == 10 and all(p.free == p.total for p in mgr.pools) and mgr.free_slots == 4 and not mgr.requests
+        results.append({r.request_id: (r.output, r.finish_reason) for r in done})
+        assert all(9 not in out for out, _ in results[-1].values()), "the end-of-sequence token was emitted"
+    assert results[0] == results[1]
+    assert {reason for _, reason in results[0].values()} == {"stop", "length"}
+
+
+def test_a_plan_made_ahead_marks_the_token_in_flight_and_a_third_plan_is_refused():
+    from hi_b200.engine.scheduler import IN_FLIGHT
+
+    mgr, s = make()
+    s.add(req("a", 5, max_tokens=3))
+    p1 = s.plan()
+    assert [(e.tokens, e.samples) for e in p1.entries] == [([1, 2, 3, 4, 5], True)]
+    p2 = s.plan()                                     # before p1 is committed: a's next token is not known yet
+    assert [(e.tokens, e.samples) for e in p2.entries] == [([IN_FLIGHT], True)]
+    with pytest.raises(RuntimeError, match="outstanding"):
+        s.plan()
+    assert s.commit(p1, {"a": 40}) == [] and p2.entries[0].request.output == [40]
+    p3 = s.plan()                                     # the third and last token: still ahead of p2's commit
+    assert [(e.tokens, e.samples) for e in p3.entries] == [([IN_FLIGHT], True)]
+    assert s.commit(p2, {"a": 41}) == []
+    p4 = s.plan()                                     # nothing left to plan: a waits for its last sample
+    assert p4.entries == [] and s.commit(p4, {}) == []
+    with pytest.raises(RuntimeError, match="order"):
+        s.commit(p2, {"a": 41})                       # p2 is committed already
+    done = s.commit(p3, {"a": 42})
+    assert [r.request_id for r in done] == ["a"] and done[0].output == [40, 41, 42] and done[0].finish_reason == "length"
+    assert not s.has_work()
