@@ -8,6 +8,7 @@
 extern "C" {
 #endif
 
+int hb_feed_tokens(int* tokens, const int* dst, const int* src, const int* sampled, int n, cudaStream_t stream);
 int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int n, int hidden,
                     int vocab, cudaStream_t stream);
 int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed, const int* slot_of_entry,

@@ -174,6 +174,23 @@ extern "C" int hb_embed_gather(const void* table, int table_dtype, const int* to
   return HB_OK;
 }
 
+// tokens[dst[i]] = sampled[src[i]]: the step before this one left its sampled tokens on the
+// device; a step that is launched before the host has read them takes them from there.
+__global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ dst, const int* __restrict__ src,
+                                   const int* __restrict__ sampled, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) tokens[dst[i]] = sampled[src[i]];
+}
+
+extern "C" int hb_feed_tokens(int* tokens, const int* dst, const int* src, const int* sampled, int n,
+                              cudaStream_t stream) {
+  if (!tokens || !dst || !src || !sampled || n < 0) return HB_ERR_BAD_ARG;
+  if (n == 0) return HB_OK;
+  feed_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, dst, src, sampled, n);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
 extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed,
                               const int* slot_of_entry, int top_k, const void* w, int w_dtype, void* y, int y_dtype,
                               float* y_f32, const int* row_map, int rows, int hidden, float eps,

@@ -23,7 +23,10 @@ from ..config.registry import load_architecture, lookup
 from ..parts.context import StepContext
 from ..parts.linear import configure_matmul_precision
 from ..parts.model import Model
+from ..kernels import ops
 from ..weights.loader import load_from_dir, load_random
+
+IN_FLIGHT = -1     # a token that the step before samples: its value is on the device, not on the host
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            "f32": torch.float32}
@@ -157,15 +160,20 @@ class Engine:
             done += n
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], tap=None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], tap=None, feedback=None) -> Optional[torch.Tensor]:
         """Run one batch. Returns float32 logits [wanted, vocab] on the device, in the order
         of the entries and of each entry's ``want`` (None if nothing is wanted). ``tap(name,
         tensor)``, if given, is called by parts that report intermediate tensors (router ids),
-        in the step's flat token order (crates/hi-cuda/src/lib.rs:87-201 has such a dump hook)."""
+        in the step's flat token order (crates/hi-cuda/src/lib.rs:87-201 has such a dump hook).
+
+        ``feedback = (sampled, rows)``: an entry whose last token is ``IN_FLIGHT`` (-1) takes it on
+        the device from ``sampled[rows[request_id]]``, an int32 tensor that the step before this
+        one filled (its sampled tokens): the step can be launched before the host has read them."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        self._resolve_status()
+        self._resolve_status(wait=False)
         if not entries:
             return None
+        fed = feedback[1] if feedback is not None else {}
         seen = set()
         for e in entries:
             if e.request_id in seen:
@@ -173,7 +181,8 @@ class Engine:
             seen.add(e.request_id)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.request_id!r} brings no tokens")
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+            known = e.tokens[:-1] if (e.tokens[-1] == IN_FLIGHT and e.request_id in fed) else e.tokens
+            bad = [t for t in known if not 0 <= int(t) < self.vocab_size]
             if bad:
                 raise ValueError(f"request {e.request_id!r}: token ids {bad[:4]} outside 0..{self.vocab_size - 1}")
             if any(not 0 <= int(w) < len(e.tokens) for w in e.want):
@@ -197,7 +206,7 @@ class Engine:
 
         graph = self._decode_graph_for(entries) if tap is None else None
         if graph is not None:
-            self._build_context(entries, widths=graph.widths, static=graph)
+            self._build_context(entries, widths=graph.widths, static=graph, feedback=feedback)
             graph.graph.replay()
             _count_launches(graph.kernels)
             if graph.uses_tensor_core_experts:
@@ -211,7 +220,7 @@ class Engine:
             logits = graph.logits.clone()
             ctx, logit_rows = graph.ctx, graph.logit_rows
         else:
-            ctx, logit_rows = self._build_context(entries)
+            ctx, logit_rows = self._build_context(entries, feedback=feedback)
             ctx.tap = tap
             logits = self.model.forward(ctx, self.cache.views, logit_rows)
             _check_kernel_status()
@@ -231,7 +240,8 @@ class Engine:
         return logits
 
     def _build_context(self, entries: Sequence[StepEntry], widths: Optional[List[int]] = None,
-                       static: Optional["_DecodeGraph"] = None) -> Tuple[StepContext, Optional[torch.Tensor]]:
+                       static: Optional["_DecodeGraph"] = None, feedback=None
+                       ) -> Tuple[StepContext, Optional[torch.Tensor]]:
         """All of a step's integer inputs in one pinned buffer, one host-to-device copy.
         With ``static`` the buffers of a captured decode graph are filled instead."""
         mgr = self.manager
@@ -242,11 +252,21 @@ class Engine:
         if widths is None:
             widths = mgr.step_widths(handles)
         n_want = sum(len(e.want) for e in entries)
+        # tokens that the step before this one sampled and the host has not read: (place, row) pairs
+        fed_dst, fed_src, cursor = [], [], 0
+        for e in entries:
+            cursor += len(e.tokens)
+            if feedback is not None and e.tokens[-1] == IN_FLIGHT:
+                fed_dst.append(cursor - 1)
+                fed_src.append(feedback[1][e.request_id])
+        n_fed = len(fed_dst)
+        fed_room = n_seqs if static is not None else n_fed
 
         def pad4(n):
             return (n + 3) // 4 * 4
 
-        sizes = [n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_want] + [n_seqs * w for w in widths]
+        sizes = [n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_want] + [n_seqs * w for w in widths] + \
+            [fed_room, fed_room]
         offsets, total = [], 0
         for s in sizes:
             offsets.append(total)
@@ -279,12 +299,23 @@ class Engine:
         if code != 0:
             raise RuntimeError(f"packing the step's inputs failed (code {code})")
         starts, slots = starts_a.tolist(), slots_a.tolist()
+        o_fed_dst, o_fed_src = offsets[-2], offsets[-1]
+        if n_fed:
+            view = host.numpy()
+            view[o_fed_dst: o_fed_dst + n_fed] = fed_dst
+            view[o_fed_src: o_fed_src + n_fed] = fed_src
         self.last_step_h2d_bytes = host.numel() * 4     # the one host-to-device copy of this step
         if static is not None:
             static.dev.copy_(host, non_blocking=True)
             static.copied.record()
+            if n_fed:
+                ops.feed_tokens(static.ctx.tokens, static.dev[o_fed_dst: o_fed_dst + n_fed],
+                                static.dev[o_fed_src: o_fed_src + n_fed], feedback[0])
             return static.ctx, static.logit_rows
         dev = host.to(self.device, non_blocking=True)
+        if n_fed:
+            ops.feed_tokens(dev[o_tok: o_tok + n_tokens], dev[o_fed_dst: o_fed_dst + n_fed],
+                            dev[o_fed_src: o_fed_src + n_fed], feedback[0])
 
         def seg(off, n):
             return dev[off: off + n]
@@ -331,10 +362,11 @@ class Engine:
             graph.capture(entries)
         return graph
 
-    def _resolve_status(self) -> None:
-        if self._status_pending:
+    def _resolve_status(self, wait: bool = True) -> None:
+        """Read the status word that followed a captured step's kernels; without ``wait`` only if
+        its copy has run already (the next look, or ``snapshot``, catches up)."""
+        if self._status_pending and self._status.resolve(wait):
             self._status_pending = False
-            self._status.resolve()
 
     # ------------------------------------------------------------------ bookkeeping
     def snapshot(self) -> dict:
@@ -352,7 +384,8 @@ class _DecodeGraph:
         self.engine, self.n_seqs, self.bucket = engine, n_seqs, bucket
         self.widths = [-(-bucket // engine.page_size) for _ in engine.manager.groups]
         pad4 = lambda n: (n + 3) // 4 * 4
-        sizes = [n_seqs, n_seqs, n_seqs, n_seqs + 1, n_seqs, n_seqs] + [n_seqs * w for w in self.widths]
+        sizes = [n_seqs, n_seqs, n_seqs, n_seqs + 1, n_seqs, n_seqs] + [n_seqs * w for w in self.widths] + \
+            [n_seqs, n_seqs]                     # the last two: places and rows of tokens fed on the device
         offsets, total = [], 0
         for sz in sizes:
             offsets.append(total)

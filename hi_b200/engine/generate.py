@@ -13,9 +13,9 @@ from typing import Callable, Dict, Hashable, List, Optional, Sequence, Union
 
 import torch
 
-from ..sampling.sampler import SamplingParams, sample
+from ..sampling.sampler import SamplingParams, sample, sample_on_device
 from .core import Engine, StepEntry
-from .scheduler import Request, Scheduler, SchedulerConfig
+from .scheduler import IN_FLIGHT, Request, Scheduler, SchedulerConfig, StepPlan
 
 
 @dataclass
@@ -29,8 +29,29 @@ class GenerationOutput:
     preemptions: int = 0
 
 
+class _Launched:
+    """A step that runs on the GPU while the host goes on: its plan, the requests it samples
+    for, and the sampled tokens on the device, on their way to pinned host memory."""
+
+    __slots__ = ("plan", "sampling", "tokens_dev", "tokens_host", "copied", "row_of")
+
+    def __init__(self, plan, sampling, tokens_dev, host_buffer, copied):
+        self.plan, self.sampling, self.tokens_dev = plan, sampling, tokens_dev
+        self.row_of = {r.request_id: i for i, r in enumerate(sampling)}
+        self.tokens_host = host_buffer[: tokens_dev.numel()]
+        self.tokens_host.copy_(tokens_dev, non_blocking=True)
+        self.copied = copied
+        self.copied.record()
+
+
 class LLM:
     """A model ready to generate: engine + scheduler + sampler.
+
+    With ``lookahead`` (the default) a step is planned and launched while the step before it still
+    runs: its decode tokens are taken on the device from what that step sampled, and the host reads
+    the sampled tokens one step late (finished requests and ``on_token`` calls come one ``step()``
+    later; a request that ends leaves one unread row in the step that was already launched). Rows
+    that sample with top-k / top-p are ranked on the host and make their step wait.
 
     ``model`` is a model folder, or a config dict together with ``random_seed`` (weights are
     then generated on the device). Options are the reference's serve flags
@@ -43,7 +64,7 @@ class LLM:
                  random_seed: Optional[int] = None, random_std: float = 0.02, kv_page_size: int = 64,
                  kv_cache_tokens: Optional[int] = None, windowed_cache_tokens: Optional[int] = None,
                  max_batch_size: int = 8, max_active_requests: Optional[int] = None,
-                 max_batched_tokens: int = 8192, max_prefill_portion: Optional[int] = None):
+                 max_batched_tokens: int = 8192, max_prefill_portion: Optional[int] = None, lookahead: bool = True):
         self.config = SchedulerConfig(max_batch_size=max_batch_size, max_active_requests=max_active_requests,
                                       max_batched_tokens=max_batched_tokens, max_prefill_portion=max_prefill_portion)
         self.config.validate()
@@ -63,6 +84,14 @@ class LLM:
         self.scheduler = Scheduler(self.engine.manager, self.config, eos_token_ids=spec.eos_token_ids,
                                    max_model_len=spec.max_position_embeddings, release=self.engine.finish)
         self._ids = itertools.count()
+        self.lookahead = lookahead
+        self._launched: Optional[_Launched] = None       # the step whose samples the host has not read yet
+        # two pinned buffers and events, used in turn: a launched step's tokens arrive in one while
+        # the host still reads the other
+        self._token_buffers = [torch.empty(max(max_batch_size, 1), dtype=torch.int32, pin_memory=True) for _ in range(2)] \
+            if torch.cuda.is_available() else []
+        self._token_events = [torch.cuda.Event() for _ in self._token_buffers]
+        self._turn = 0
 
     # ------------------------------------------------------------------ low level
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -79,27 +108,52 @@ class LLM:
     def abort(self, request_id: Hashable) -> None:
         self.scheduler.abort(request_id)
 
-    def step(self, on_token: Optional[Callable[[Hashable, int], None]] = None) -> List[Request]:
-        """One scheduler iteration: plan, run the batch, sample, finish. Returns finished requests."""
-        plan = self.scheduler.plan()
-        if not plan.entries:
-            if plan.preempted or not self.scheduler.has_work():
-                return []
-            raise RuntimeError("scheduler stalled: no request can take a step with the pages that are free")
-        entries = [StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
-                   for e in plan.entries]
-        logits = self.engine.step(entries)
-        sampling = [e.request for e in plan.entries if e.samples]
-        sampled: Dict[Hashable, int] = {}
-        if sampling:
-            toks = sample(logits, [r.params for r in sampling], [r.rng for r in sampling])
-            sampled = {r.request_id: t for r, t in zip(sampling, toks)}
+    def _entries(self, plan: StepPlan) -> List[StepEntry]:
+        return [StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.samples else []) for e in plan.entries]
+
+    def _commit(self, plan: StepPlan, sampling: List[Request], tokens: Sequence[int],
+                on_token: Optional[Callable[[Hashable, int], None]]) -> List[Request]:
+        sampled = {r.request_id: int(t) for r, t in zip(sampling, tokens)}
         before = {r.request_id: len(r.output) for r in sampling}
         done = self.scheduler.commit(plan, sampled)
         if on_token is not None:
             for r in sampling:
                 if len(r.output) > before[r.request_id]:
                     on_token(r.request_id, r.output[-1])
+        return done
+
+    def _read(self, launched: _Launched, on_token) -> List[Request]:
+        """The host catches up with a launched step: waits for its sampled tokens and commits them."""
+        launched.copied.synchronize()
+        return self._commit(launched.plan, launched.sampling, launched.tokens_host.tolist(), on_token)
+
+    def step(self, on_token: Optional[Callable[[Hashable, int], None]] = None) -> List[Request]:
+        """One scheduler iteration: plan, run the batch, sample, finish. Returns finished requests
+        (with ``lookahead``: those of the step before the one launched now)."""
+        previous = self._launched
+        self._launched = None
+        plan = self.scheduler.plan() if self.scheduler.has_work() else StepPlan()
+        if not plan.entries:
+            done = self._read(previous, on_token) if previous is not None else []
+            if previous is None and not plan.preempted and self.scheduler.has_work():
+                raise RuntimeError("scheduler stalled: no request can take a step with the pages that are free")
+            return done
+        feedback = (previous.tokens_dev, previous.row_of) if previous is not None else None
+        logits = self.engine.step(self._entries(plan), feedback=feedback)
+        sampling = [e.request for e in plan.entries if e.samples]
+        done: List[Request] = []
+        launched = None
+        if sampling and self.lookahead:
+            tokens_dev = sample_on_device(logits, [r.params for r in sampling], [r.rng for r in sampling])
+            if tokens_dev is not None:
+                self._turn ^= 1
+                launched = _Launched(plan, sampling, tokens_dev, self._token_buffers[self._turn], self._token_events[self._turn])
+        if previous is not None:                       # the step before: its tokens have had a whole step to arrive
+            done += self._read(previous, on_token)
+        if launched is None:                           # read this step's samples now (host-side sampling, or no lookahead)
+            tokens = sample(logits, [r.params for r in sampling], [r.rng for r in sampling]) if sampling else []
+            done += self._commit(plan, sampling, tokens, on_token)
+        self._launched = launched
         return done
 
     # ------------------------------------------------------------------ the call a user makes

@@ -17,6 +17,7 @@ from . import build as _build
 P, I, F = c_void_p, c_int, c_float
 
 _SIGNATURES = {
+    "hb_feed_tokens": [P, P, P, P, I, P],
     "hb_embed_gather": [P, I, P, P, I, I, I, P],
     "hb_add_rmsnorm": [P, P, I, P, P, I, P, I, P, I, P, P, I, I, F, P],
     "hb_swiglu": [P, P, I, I, I, P],
@@ -95,6 +96,16 @@ def _stream() -> int:
 
 
 # --------------------------------------------------------------------------- elementwise
+def feed_tokens(tokens: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, sampled: torch.Tensor) -> None:
+    """tokens[dst[i]] = sampled[src[i]], all int32 on the device: a step takes tokens that the step
+    before it sampled without the host having read them."""
+    for t, nm in ((tokens, "tokens"), (dst, "dst"), (src, "src"), (sampled, "sampled")):
+        _need(t, nm, torch.int32)
+    if dst.numel() != src.numel():
+        raise KernelError("dst and src need the same number of entries")
+    _check(lib().hb_feed_tokens(_ptr(tokens), _ptr(dst), _ptr(src), _ptr(sampled), dst.numel(), _stream()), "feed_tokens")
+
+
 def embed_gather(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
     """Rows of ``table`` [V, H] for int32 ``tokens`` [N] -> float32 residual stream [N, H]."""
     _need(table, "table"); _need(tokens, "tokens", torch.int32)
@@ -499,10 +510,16 @@ class PendingStatus:
         self.host.copy_(_tc_status(self.device), non_blocking=True)
         self.event.record()
 
-    def resolve(self) -> None:
+    def resolve(self, wait: bool = True) -> bool:
+        """Read the copied word; raises if a kernel reported a failed wait. With ``wait=False`` it
+        returns False, without blocking, while the copy has not run yet (the word on the device
+        stays set until it is read, so a later look still sees it)."""
+        if not wait and not self.event.query():
+            return False
         self.event.synchronize()
         if int(self.host[0]) != 0:
             check_tc_status()          # raises with the reason, and clears the word
+        return True
 
 
 def moe_tc_supported(x: torch.Tensor, w_gate: torch.Tensor) -> bool:

@@ -86,6 +86,24 @@ def ranked_sample(row: np.ndarray, temperature: float, top_p: float, top_k: Opti
     return int(np.argmax(row))
 
 
+def sample_on_device(logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[Lcg]
+                     ) -> Optional[torch.Tensor]:
+    """One token for each row of float32 ``logits`` [R, V], left on the device as int32 [R] (no
+    wait for the GPU), or None if a row samples with top-k / top-p: those are ranked on the host
+    (use :func:`sample`; no generator has been advanced then)."""
+    rows, vocab = logits.shape
+    if rows != len(params) or rows != len(rngs):
+        raise ValueError("one SamplingParams and one generator per row are needed")
+    if any(p.ranked(vocab) for p in params):
+        return None
+    if all(p.greedy for p in params):
+        return ops.sample_rows(logits, None, None)
+    uniforms = [0.0 if p.greedy else rng.next_f32() for p, rng in zip(params, rngs)]
+    temps = [0.0 if p.greedy else float(p.temperature) for p in params]
+    host = torch.tensor([temps, uniforms], dtype=torch.float32).to(logits.device, non_blocking=True)
+    return ops.sample_rows(logits, host[0].contiguous(), host[1].contiguous())
+
+
 def sample(logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[Lcg]) -> List[int]:
     """One token for each row of float32 ``logits`` [R, V] on the device."""
     rows, vocab = logits.shape

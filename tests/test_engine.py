@@ -158,6 +158,37 @@ def test_seeded_sampling_does_not_depend_on_batching(model_dirs):
     assert together == alone
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_launching_a_step_ahead_changes_no_token(dtype, model_dirs):
+    """With lookahead a decode step is launched before the host has read the tokens of the step
+    before it (they are fed on the device), requests that stop leave an unread row in the step
+    already launched, and rows ranked on the host make their step wait: the generated tokens, the
+    reasons and the streamed tokens are those of the step-by-step loop. The stop token is chosen
+    from what the model really generates, so that requests end in the middle."""
+    import hi_b200
+
+    cfg, mdir = model_dirs["B"]
+    prompts = [h.random_tokens(cfg, n, seed=70 + n) for n in (9, 30, 3, 44, 17)]
+
+    def params(stop):
+        return [hi_b200.SamplingParams(max_tokens=24, temperature=0.0 if i % 2 else 0.9, seed=11 + i, ignore_eos=True,
+                                       stop_token_ids=stop, top_k=5 if i == 4 else None) for i in range(5)]
+
+    free = hi_b200.LLM(mdir, dtype=dtype, kv_page_size=16, max_batch_size=3, kv_cache_tokens=1024, lookahead=False)
+    seen = [o.token_ids for o in free.generate(prompts, params(()))]
+    stop = tuple({out[len(out) // 2] for out in seen[:3]})          # tokens that do occur half-way
+    runs = []
+    for ahead in (False, True):
+        llm = hi_b200.LLM(mdir, dtype=dtype, kv_page_size=16, max_batch_size=3, kv_cache_tokens=1024, lookahead=ahead)
+        streamed = {}
+        outs = llm.generate(prompts, params(stop), on_token=lambda rid, tok: streamed.setdefault(rid, []).append(tok))
+        assert all(streamed.get(o.request_id, []) == o.token_ids for o in outs)
+        assert not llm.engine.manager.requests and all(p.free == p.total for p in llm.engine.manager.pools)
+        runs.append([(o.token_ids, o.finish_reason) for o in outs])
+    assert runs[0] == runs[1]
+    assert any(reason == "stop" and len(toks) < 24 for toks, reason in runs[0]), "no request stopped in the middle"
+
+
 def test_generation_with_so_few_pages_that_requests_are_preempted(model_dirs):
     """Four requests in a cache that cannot hold them all to the end: decoding runs out of pages,
     the scheduler preempts the youngest request (its pages go back, it is computed again from its
