@@ -187,6 +187,14 @@ def test_launching_a_step_ahead_changes_no_token(dtype, model_dirs):
         runs.append([(o.token_ids, o.finish_reason) for o in outs])
     assert runs[0] == runs[1]
     assert any(reason == "stop" and len(toks) < 24 for toks, reason in runs[0]), "no request stopped in the middle"
+    # and ahead in a pool so small that requests are preempted while a step of theirs is in flight
+    tight = hi_b200.LLM(mdir, dtype=dtype, kv_page_size=16, max_batch_size=3, kv_cache_tokens=96, windowed_cache_tokens=96,
+                        lookahead=True)
+    outs = tight.generate(prompts, params(stop))
+    assert [(o.token_ids, o.finish_reason) for o in outs] == runs[0]
+    assert sum(o.preemptions for o in outs) >= 1, "the pool was large enough: nothing was preempted"
+    tight.engine.manager.check_invariants()
+    assert not tight.engine.manager.requests and all(p.free == p.total for p in tight.engine.manager.pools)
 
 
 def test_generation_with_so_few_pages_that_requests_are_preempted(model_dirs):
