@@ -37,6 +37,11 @@ int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages,
                         int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int split_size,
                         int max_splits, float* part_acc, float* part_ml, cudaStream_t stream);
 
+int hb_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, int n_pages, const int* block_table,
+                            int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
+                            int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int split_size,
+                            int max_splits, float* part_acc, float* part_ml, int* status, cudaStream_t stream);
+
 int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                          int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_seqs,
                          int max_new, int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,

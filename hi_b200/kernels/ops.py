@@ -26,6 +26,7 @@ _SIGNATURES = {
     "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "hb_attention_merge": [P, P, P, I, I, I, I, P],
     "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
+    "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
@@ -38,6 +39,7 @@ _SIGNATURES = {
     "hb_sample_rows": [P, I, I, P, P, P, P],
 }
 
+_UNSUPPORTED = 1002
 _ERRORS = {1001: "bad argument (size, pointer or dtype)", 1002: "shape not supported by this kernel"}
 
 
@@ -316,10 +318,19 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     if splits > 1:
         part_acc = torch.empty((n, nh, splits, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n, nh, splits, 2), dtype=torch.float32, device=q.device)
-    _check(lib().hb_attention_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
-                                     _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size,
-                                     int(chunk), int(window), float(scale), split_size, splits, _ptr(part_acc),
-                                     _ptr(part_ml), _stream()), "attention_decode")
+    # tile loads by TMA where the range and the pages allow it (the kernel says if not)
+    code = lib().hb_attention_decode_tma(_ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
+                                         block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv,
+                                         hd, page_size, int(chunk), int(window), float(scale), split_size, splits,
+                                         _ptr(part_acc), _ptr(part_ml), _ptr(_tc_status(q.device)), _stream())
+    if code == _UNSUPPORTED:
+        code = lib().hb_attention_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                                         _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size,
+                                         int(chunk), int(window), float(scale), split_size, splits, _ptr(part_acc),
+                                         _ptr(part_ml), _stream())
+    else:
+        TC_USED[0] = True
+    _check(code, "attention_decode")
     if splits > 1:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
                                         _stream()), "attention_merge")
@@ -483,7 +494,8 @@ def _tc_status(device: torch.device) -> torch.Tensor:
 
 
 def check_tc_status(device=None) -> None:
-    """Raise if a tcgen05 kernel timed out on one of its barriers since the last check
+    """Raise if a kernel with bounded mbarrier waits (the tcgen05 products and attention, the TMA
+    decode attention) timed out on one of its barriers since the last check
     (synchronises; skipped while a stream is being captured)."""
     TC_USED[0] = False
     if torch.cuda.is_current_stream_capturing():
@@ -495,9 +507,10 @@ def check_tc_status(device=None) -> None:
             where = {1: "grouped product: the TMA producer waiting for a free stage",
                      2: "grouped product: the MMA issuer waiting for a loaded stage",
                      3: "grouped product: the epilogue waiting for the accumulator",
-                     4: "grouped product: the MMA issuer waiting for a free accumulator"}.get(
+                     4: "grouped product: the MMA issuer waiting for a free accumulator",
+                     31: "decode attention: the warps waiting for a tile's TMA loads"}.get(
                 code, f"prefill attention, wait {code}" if code >= 11 else f"code {code}")
-            raise KernelError(f"a tcgen05 kernel gave up a bounded wait ({where}); its output is invalid")
+            raise KernelError(f"a kernel gave up a bounded wait ({where}); its output is invalid")
 
 
 class PendingStatus:

@@ -158,10 +158,12 @@ def test_qkv_post_and_paged_attention(case, dt, tol):
 
 
 @pytest.mark.parametrize("shape", [(40, 8, 128, 64, 0, 0), (8, 8, 64, 16, 0, 0), (32, 2, 128, 32, 512, 0), (10, 2, 64, 8, 0, 300),
-                                   (3, 1, 128, 64, 100, 0)])
+                                   (3, 1, 128, 64, 100, 0), (16, 4, 128, 128, 0, 0), (12, 4, 64, 64, 192, 0)])
 def test_decode_attention_on_tensor_cores(shape):
-    """The decode kernel (bfloat16, split over 256-key runs) against whole-sequence attention, for
-    requests of very different lengths in one batch, and against the general kernel."""
+    """The decode kernels (bfloat16, split over runs of keys) against whole-sequence attention, for
+    requests of very different lengths in one batch, and against the general kernel. Pages of 16,
+    32, 64 and 128 with no window or a chunk that is a multiple of 64 run the kernel with TMA tile
+    loads; pages of 8, a chunk of 100 and the sliding window run the cp.async kernel."""
     o = ops()
     nh, nkv, hd, page, chunk, window = shape
     lens = [1, 1, 1, 1, 1, 1]
