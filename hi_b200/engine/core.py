@@ -49,15 +49,11 @@ def _require_cuda(device) -> None:
 
 def _check_kernel_status(force: bool = False) -> None:
     """A tensor-core kernel that gave up a bounded wait makes the step fail loudly."""
-    from ..kernels import ops
-
     if ops.TC_USED[0] or force:
         ops.check_tc_status()
 
 
 def _count_launches(n: int) -> None:
-    from ..kernels import ops
-
     ops.LAUNCHES[0] += n
 
 
@@ -213,7 +209,6 @@ class Engine:
                 # no sync here: the status word follows the kernels to pinned memory and is read
                 # at the start of the next step (or when the engine is asked for its state)
                 if self._status is None:
-                    from ..kernels import ops
                     self._status = ops.PendingStatus(self.device)
                 self._status.enqueue()
                 self._status_pending = True
@@ -421,8 +416,6 @@ class _DecodeGraph:
             eng.model.forward(self.ctx, eng.cache.views, self.logit_rows)
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
-        from ..kernels import ops
-
         before = ops.LAUNCHES[0]
         ops.TC_USED[0] = False
         self.graph = torch.cuda.CUDAGraph()
