@@ -56,6 +56,9 @@ int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n
                    int top_k, float* logits_out, int* ids, float* scores, cudaStream_t stream);
 int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
                 int* slot_of_entry, int* active, cudaStream_t stream);
+int hb_router_plan(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts, int top_k,
+                   float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry, int* slot_of_entry,
+                   int* active, int* counter, cudaStream_t stream);
 int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,
                    const void* w_up, const int* offsets, const int* active, int experts, const float* scores,
                    void* act, int n_entries, int inter, int hidden, int few_rows, cudaStream_t stream);

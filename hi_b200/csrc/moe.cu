@@ -13,6 +13,56 @@
 
 namespace {
 
+// ------------------------------------------------------------------ the plan, by one block
+// Stable counting sort of the n = tokens*top_k routing entries by expert:
+// offsets[e]..offsets[e+1] are the sorted slots of expert e, in entry order.
+// active[0] = number of experts with at least one row, active[1..] = their ids in order.
+// `ids` is read past L1 (in the fused router + plan kernel other blocks wrote it).
+// `sm` holds 2 * experts ints.
+__device__ __forceinline__ void plan_block(const int* ids, int n, int experts, int* __restrict__ offsets,
+                                           int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry,
+                                           int* __restrict__ active, int* sm) {
+  int* cnt = sm;
+  int* base = sm + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = __ldcg(ids + i);
+    if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, n_active = 0;
+    for (int e = 0; e < experts; ++e) {
+      offsets[e] = run;
+      base[e] = run;
+      run += cnt[e];
+      if (cnt[e] > 0) active[1 + n_active++] = e;
+    }
+    offsets[experts] = run;
+    active[0] = n_active;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    for (int start = 0; start < n; start += 32) {
+      const int i = start + lane;
+      int e = i < n ? __ldcg(ids + i) : -1;
+      if (e >= experts) e = -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      if (e >= 0) {
+        const int slot = base[e] + rank;
+        sorted_entry[slot] = i;
+        slot_of_entry[i] = slot;
+      }
+      __syncwarp();
+      if (e >= 0 && rank == 0) base[e] += __popc(peers);
+      __syncwarp();
+    }
+  }
+}
+
 // ------------------------------------------------------------------ router
 // logit[t, e] = sum_k x[t, k] * w[e, k] in float32. x may be float32 while the weights are
 // bfloat16: the router reads the float32 output of the norm, so its logits carry no activation
@@ -52,9 +102,10 @@ __device__ __forceinline__ void router_select(const float* row, int experts, int
 // accumulators of the same lane, so their loads are in flight together.
 template <typename TX, typename TW>
 __global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int hidden, int experts,
-                                   int top_k, float* __restrict__ logits_out, int* __restrict__ ids,
-                                   float* __restrict__ scores) {
-  extern __shared__ float lg[];  // [experts]
+                                   int top_k, float* __restrict__ logits_out, int* ids, float* __restrict__ scores,
+                                   int* __restrict__ offsets, int* __restrict__ sorted_entry,
+                                   int* __restrict__ slot_of_entry, int* __restrict__ active, int* counter) {
+  extern __shared__ float lg[];  // [experts] logits, then 2 * experts ints for the plan
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const TX* xr = x + (size_t)t * hidden;
@@ -105,6 +156,20 @@ __global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restric
   }
   __syncthreads();
   if (threadIdx.x == 0) router_select(lg, experts, top_k, ids + (size_t)t * top_k, scores + (size_t)t * top_k);
+  if (!counter) return;
+  // The plan rides along: the block that finishes last (it sees every token's choice) groups the
+  // routing entries by expert, and leaves the counter at zero for the next launch.
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    is_last = atomicAdd(counter, 1) == (int)gridDim.x - 1;
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  plan_block(ids, (int)gridDim.x * top_k, experts, offsets, sorted_entry, slot_of_entry, active,
+             reinterpret_cast<int*>(lg + experts));
 }
 
 // Many tokens: a block takes ROUTER_TOK tokens x ROUTER_EXP experts with one warp per part of K;
@@ -192,52 +257,11 @@ __global__ void router_select_kernel(const float* __restrict__ logits, int n, in
 }
 
 // ------------------------------------------------------------------ plan
-// Stable counting sort of the n = tokens*top_k routing entries by expert, in one block:
-// offsets[e]..offsets[e+1] are the sorted slots of expert e, in entry order.
-// active[0] = number of experts with at least one row, active[1..] = their ids in order.
-__global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int experts, int* __restrict__ offsets,
+__global__ void moe_plan_kernel(const int* ids, int n, int experts, int* __restrict__ offsets,
                                 int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry,
                                 int* __restrict__ active) {
-  extern __shared__ int sm[];  // cnt[experts], base[experts]
-  int* cnt = sm;
-  int* base = sm + experts;
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
-  __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = ids[i];
-    if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0, n_active = 0;
-    for (int e = 0; e < experts; ++e) {
-      offsets[e] = run;
-      base[e] = run;
-      run += cnt[e];
-      if (cnt[e] > 0) active[1 + n_active++] = e;
-    }
-    offsets[experts] = run;
-    active[0] = n_active;
-  }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    const int lane = threadIdx.x;
-    for (int start = 0; start < n; start += 32) {
-      const int i = start + lane;
-      int e = i < n ? ids[i] : -1;
-      if (e >= experts) e = -1;
-      const unsigned peers = __match_any_sync(0xffffffffu, e);
-      const int rank = __popc(peers & ((1u << lane) - 1u));
-      if (e >= 0) {
-        const int slot = base[e] + rank;
-        sorted_entry[slot] = i;
-        slot_of_entry[i] = slot;
-      }
-      __syncwarp();
-      if (e >= 0 && rank == 0) base[e] += __popc(peers);
-      __syncwarp();
-    }
-  }
+  extern __shared__ int plan_sm[];  // cnt[experts], base[experts]
+  plan_block(ids, n, experts, offsets, sorted_entry, slot_of_entry, active, plan_sm);
 }
 
 // ------------------------------------------------------------------ grouped products, general form
@@ -475,9 +499,13 @@ int launch_grouped(bool dual, const void* A, int lda, const int* sorted_entry, i
 
 }  // namespace
 
-extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden,
-                              int experts, int top_k, float* logits_out, int* ids, float* scores,
-                              cudaStream_t stream) {
+namespace {
+
+// The router, and with `counter` (an int that is zero between launches) the plan as well: in the
+// same kernel when a block takes one token, by the plan's own kernel after the tiled one.
+int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts, int top_k,
+                  float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry, int* slot_of_entry,
+                  int* active, int* counter, cudaStream_t stream) {
   if (!x || !w || !ids || !scores || n < 0 || hidden <= 0 || experts <= 0 || top_k <= 0 || top_k > experts)
     return HB_ERR_BAD_ARG;
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
@@ -500,23 +528,56 @@ extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_d
       router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, ids, scores);
       HB_LAUNCH_CHECK();
     }
+    if (counter) {
+      moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, n * top_k, experts, offsets,
+                                                                              sorted_entry, slot_of_entry, active);
+      HB_LAUNCH_CHECK();
+    }
     return HB_OK;
   }
-  const size_t smem = (size_t)experts * sizeof(float);
+  const size_t smem = (size_t)experts * (sizeof(float) + (counter ? 2 * sizeof(int) : 0));
   const int threads = experts >= 16 ? 512 : (experts >= 8 ? 256 : 128);   // a warp per expert where that fits
   if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_F32)
     router_topk_kernel<float, float><<<n, threads, smem, stream>>>((const float*)x, (const float*)w, hidden, experts,
-                                                               top_k, logits_out, ids, scores);
+                                                               top_k, logits_out, ids, scores, offsets, sorted_entry,
+                                                               slot_of_entry, active, counter);
   else if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_BF16)
     router_topk_kernel<float, __nv_bfloat16><<<n, threads, smem, stream>>>(
-        (const float*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
+        (const float*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores, offsets,
+        sorted_entry, slot_of_entry, active, counter);
   else if (x_dtype == HB_DTYPE_BF16 && w_dtype == HB_DTYPE_BF16)
     router_topk_kernel<__nv_bfloat16, __nv_bfloat16><<<n, threads, smem, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores);
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores, offsets,
+        sorted_entry, slot_of_entry, active, counter);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();
   return HB_OK;
+}
+
+}  // namespace
+
+extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden,
+                              int experts, int top_k, float* logits_out, int* ids, float* scores,
+                              cudaStream_t stream) {
+  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, logits_out, ids, scores, nullptr, nullptr,
+                       nullptr, nullptr, nullptr, stream);
+}
+
+// Router and plan in one call; `counter` is one int that the caller zeroed once and then leaves alone.
+extern "C" int hb_router_plan(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
+                              int top_k, float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry,
+                              int* slot_of_entry, int* active, int* counter, cudaStream_t stream) {
+  if (!offsets || !sorted_entry || !slot_of_entry || !active || !counter) return HB_ERR_BAD_ARG;
+  if (experts <= 0 || experts > 4096) return experts <= 0 ? HB_ERR_BAD_ARG : HB_ERR_UNSUPPORTED;
+  if (n == 0) {  // nothing routed: an empty plan
+    moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, 0, experts, offsets, sorted_entry,
+                                                                            slot_of_entry, active);
+    HB_LAUNCH_CHECK();
+    return HB_OK;
+  }
+  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, logits_out, ids, scores, offsets,
+                       sorted_entry, slot_of_entry, active, counter, stream);
 }
 
 extern "C" int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,

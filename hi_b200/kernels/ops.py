@@ -31,6 +31,7 @@ _SIGNATURES = {
     "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
+    "hb_router_plan": [P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P],
     "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, P],
     "hb_moe_down": [P, I, P, P, P, I, P, I, I, I, I, P],
     "hb_gather_rows": [P, P, I, P, I, I, P],
@@ -437,18 +438,50 @@ class MoePlan:
         return iter((self.offsets, self.sorted_entry, self.slot_of_entry))
 
 
+def _empty_plan(n: int, experts: int, dev) -> MoePlan:
+    return MoePlan(torch.empty(experts + 1, dtype=torch.int32, device=dev),
+                   torch.empty(max(n, 1), dtype=torch.int32, device=dev),
+                   torch.empty(max(n, 1), dtype=torch.int32, device=dev),
+                   torch.empty(experts + 1, dtype=torch.int32, device=dev))
+
+
+_block_counters: dict = {}     # device -> one int32 that kernels leave at zero
+
+
+def _block_counter(dev) -> torch.Tensor:
+    c = _block_counters.get(dev)
+    if c is None:
+        c = _block_counters[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return c
+
+
+def router_plan(x: torch.Tensor, w: torch.Tensor, top_k: int):
+    """:func:`router_topk` and :func:`moe_plan` in one call: with few tokens one kernel does both
+    (the block that ends last groups the entries). Returns ids, scores and the plan."""
+    _need(x, "x"); _need(w, "router weight")
+    n, hidden = x.shape
+    experts = w.shape[0]
+    if w.shape[1] != hidden:
+        raise KernelError("router weight does not match the hidden size")
+    ids = torch.empty((n, top_k), dtype=torch.int32, device=x.device)
+    scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
+    logits = torch.empty((n, experts), dtype=torch.float32, device=x.device) if experts > 16 else None
+    plan = _empty_plan(n * top_k, experts, x.device)
+    _check(lib().hb_router_plan(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, _ptr(logits),
+                                _ptr(ids), _ptr(scores), _ptr(plan.offsets), _ptr(plan.sorted_entry),
+                                _ptr(plan.slot_of_entry), _ptr(plan.active), _ptr(_block_counter(x.device)),
+                                _stream()), "router_plan")
+    return ids, scores, plan
+
+
 def moe_plan(ids: torch.Tensor, experts: int) -> MoePlan:
     """Group the routing entries by expert, on the device."""
     _need(ids, "ids", torch.int32)
     n = ids.numel()
-    dev = ids.device
-    offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
-    sorted_entry = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
-    slot_of_entry = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
-    active = torch.empty(experts + 1, dtype=torch.int32, device=dev)
-    _check(lib().hb_moe_plan(_ptr(ids), n, experts, _ptr(offsets), _ptr(sorted_entry), _ptr(slot_of_entry),
-                             _ptr(active), _stream()), "moe_plan")
-    return MoePlan(offsets, sorted_entry, slot_of_entry, active)
+    plan = _empty_plan(n, experts, ids.device)
+    _check(lib().hb_moe_plan(_ptr(ids), n, experts, _ptr(plan.offsets), _ptr(plan.sorted_entry),
+                             _ptr(plan.slot_of_entry), _ptr(plan.active), _stream()), "moe_plan")
+    return plan
 
 
 def moe_gate_up(x: torch.Tensor, plan: MoePlan, top_k: int, w_gate: torch.Tensor,

@@ -134,10 +134,9 @@ class SigmoidRoutedExperts(Part):
         side = None
         if self.shared and self.OVERLAP_SHARED:
             shared, side = self._shared_on_side_stream(normed)
-        ids, scores, _ = ops.router_topk(normed if normed_f32 is None else normed_f32, self.w_router, self.top_k)
+        ids, scores, plan = ops.router_plan(normed if normed_f32 is None else normed_f32, self.w_router, self.top_k)
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.router_ids", ids)
-        plan = ops.moe_plan(ids, self.experts)
         tc = ops.moe_tc_supported(normed, self.w_gate)
         few = n * self.top_k <= (self.FEW_ROWS if tc else 128)
         if not few and tc:

@@ -402,6 +402,30 @@ def test_router_logits_do_not_depend_on_the_number_of_tokens(shape):
         close(logits_all, x.float() @ w.float().T, 1e-5, "router logits")
 
 
+@pytest.mark.parametrize("shape", [(96, 5, 2, 1), (200, 16, 1, 8), (72, 40, 3, 33), (128, 128, 1, 150), (64, 24, 2, 200)])
+def test_router_and_plan_in_one_call_match_the_two_calls(shape):
+    """With few tokens the plan is made by the router kernel's last block; launches follow one
+    another so the block counter has to come back to zero every time."""
+    o = ops()
+    H, E, k, n = shape
+    g = torch.Generator().manual_seed(H + E + n)
+    w = torch.randn(E, H, generator=g).to(torch.bfloat16).to(DEV)
+    for turn in range(4):
+        x = torch.randn(n, H, generator=g).to(DEV)
+        ids, scores, _ = o.router_topk(x, w, k)
+        plan = o.moe_plan(ids, E)
+        ids2, scores2, plan2 = o.router_plan(x, w, k)
+        assert torch.equal(ids, ids2) and torch.equal(scores, scores2)
+        m = n * k
+        n_active = int(plan.active[0])
+        assert torch.equal(plan.offsets, plan2.offsets), f"{shape} turn {turn}"
+        assert torch.equal(plan.sorted_entry[:m], plan2.sorted_entry[:m])
+        assert torch.equal(plan.slot_of_entry[:m], plan2.slot_of_entry[:m])
+        assert torch.equal(plan.active[: 1 + n_active], plan2.active[: 1 + n_active])
+    empty = o.router_plan(torch.zeros(0, H, device=DEV), w, k)[2]
+    assert empty.offsets.cpu().tolist() == [0] * (E + 1) and int(empty.active[0]) == 0
+
+
 def test_router_ties_go_to_the_lower_id():
     o = ops()
     x = torch.zeros(3, 16); x[:, 0] = 1.0
