@@ -81,7 +81,9 @@ __device__ __forceinline__ void router_part_range(int hidden, int part, int& run
   run_end = min(runs, run_begin + per);
 }
 
-// The k largest of a row of logits (ties to the lower id) and their sigmoids.
+// The k largest of a row of logits (ties to the lower id) and their sigmoids. THROUGH_L2: the row
+// was written by other blocks of this launch and is read past L1.
+template <bool THROUGH_L2 = false>
 __device__ __forceinline__ void router_select(const float* row, int experts, int top_k, int* ids, float* scores) {
   for (int r = 0; r < top_k; ++r) {
     int best = -1;
@@ -90,7 +92,7 @@ __device__ __forceinline__ void router_select(const float* row, int experts, int
       bool taken = false;
       for (int q = 0; q < r; ++q) taken |= (ids[q] == e);
       if (taken) continue;
-      const float v = row[e];
+      const float v = THROUGH_L2 ? __ldcg(row + e) : row[e];
       if (best < 0 || v > bv) { best = e; bv = v; }  // strict '>' keeps the lowest id on ties
     }
     ids[r] = best;
@@ -98,78 +100,89 @@ __device__ __forceinline__ void router_select(const float* row, int experts, int
   }
 }
 
-// Few tokens: one block per token; warps take experts in turn; the parts of K are independent
-// accumulators of the same lane, so their loads are in flight together.
+// Few tokens: a block takes one token and ROUTER_FEW_EXP experts, a warp one part of K of one
+// expert with up to four runs' loads in flight, so that a single token's router still spreads over
+// experts / ROUTER_FEW_EXP blocks and a handful of memory round trips (it runs beside kernels that
+// keep the memory system busy). With `counter` (zero between launches) the block that finishes
+// last selects for every token and makes the plan; without it router_select_kernel follows.
+constexpr int ROUTER_FEW_EXP = 4;
+
 template <typename TX, typename TW>
-__global__ void router_topk_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int hidden, int experts,
-                                   int top_k, float* __restrict__ logits_out, int* ids, float* __restrict__ scores,
-                                   int* __restrict__ offsets, int* __restrict__ sorted_entry,
-                                   int* __restrict__ slot_of_entry, int* __restrict__ active, int* counter) {
-  extern __shared__ float lg[];  // [experts] logits, then 2 * experts ints for the plan
+__global__ void __launch_bounds__(ROUTER_FEW_EXP * ROUTER_KPARTS * 32)
+router_few_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int n, int hidden, int experts, int top_k,
+                  float* logits, int* ids, float* scores, int* __restrict__ offsets,
+                  int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry, int* __restrict__ active,
+                  int* counter) {
+  __shared__ float partial[ROUTER_FEW_EXP][ROUTER_KPARTS];
+  __shared__ int is_last;
+  extern __shared__ int plan_scratch[];  // 2 * experts ints, for the block that makes the plan
   const int t = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const TX* xr = x + (size_t)t * hidden;
-  int rb[ROUTER_KPARTS], re[ROUTER_KPARTS];
-#pragma unroll
-  for (int q = 0; q < ROUTER_KPARTS; ++q) router_part_range(hidden, q, rb[q], re[q]);
-  const int per = re[0] - rb[0];
-  for (int e = warp; e < experts; e += nwarps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int part = warp % ROUTER_KPARTS, local = warp / ROUTER_KPARTS;
+  const int e = blockIdx.y * ROUTER_FEW_EXP + local;
+  int run_begin, run_end;
+  router_part_range(hidden, part, run_begin, run_end);
+  float s = 0.f;
+  if (e < experts) {
+    const TX* xr = x + (size_t)t * hidden;
     const TW* wr = w + (size_t)e * hidden;
-    float s[ROUTER_KPARTS];
-#pragma unroll
-    for (int q = 0; q < ROUTER_KPARTS; ++q) s[q] = 0.f;
     if ((hidden & 7) == 0) {   // rows are 16-byte aligned: 8 elements per load
-      for (int c = 0; c < per; ++c) {
-        float xv[ROUTER_KPARTS][8], wv[ROUTER_KPARTS][8];
-        bool on[ROUTER_KPARTS];
+      constexpr int U = 4;
+      for (int run = run_begin; run < run_end; run += U) {
+        float xv[U][8], wv[U][8];
+        bool on[U];
 #pragma unroll
-        for (int q = 0; q < ROUTER_KPARTS; ++q) {
-          const int j = (rb[q] + c) * 256 + lane * 8;
-          on[q] = rb[q] + c < re[q] && j < hidden;
-          if (on[q]) {
-            hb::load8(xr + j, xv[q]);
-            hb::load8(wr + j, wv[q]);
+        for (int u = 0; u < U; ++u) {
+          const int j = (run + u) * 256 + lane * 8;
+          on[u] = run + u < run_end && j < hidden;
+          if (on[u]) {
+            hb::load8(xr + j, xv[u]);
+            hb::load8(wr + j, wv[u]);
           }
         }
 #pragma unroll
-        for (int q = 0; q < ROUTER_KPARTS; ++q)
-          if (on[q])
+        for (int u = 0; u < U; ++u)
+          if (on[u])
 #pragma unroll
-            for (int i = 0; i < 8; ++i) s[q] += xv[q][i] * wv[q][i];
+            for (int i = 0; i < 8; ++i) s += xv[u][i] * wv[u][i];
       }
     } else {                   // any width: the same order, element by element
-#pragma unroll
-      for (int q = 0; q < ROUTER_KPARTS; ++q)
-        for (int run = rb[q]; run < re[q]; ++run)
-          for (int i = 0; i < 8; ++i) {
-            const int j = run * 256 + lane * 8 + i;
-            if (j < hidden) s[q] += hb::to_f32(xr[j]) * hb::to_f32(wr[j]);
-          }
-    }
-    float total = hb::warp_sum(s[0]);
-#pragma unroll
-    for (int q = 1; q < ROUTER_KPARTS; ++q) total += hb::warp_sum(s[q]);
-    if (lane == 0) {
-      lg[e] = total;
-      if (logits_out) logits_out[(size_t)t * experts + e] = total;
+      for (int run = run_begin; run < run_end; ++run)
+        for (int i = 0; i < 8; ++i) {
+          const int j = run * 256 + lane * 8 + i;
+          if (j < hidden) s += hb::to_f32(xr[j]) * hb::to_f32(wr[j]);
+        }
     }
   }
+  s = hb::warp_sum(s);
+  if (lane == 0) partial[local][part] = s;
   __syncthreads();
-  if (threadIdx.x == 0) router_select(lg, experts, top_k, ids + (size_t)t * top_k, scores + (size_t)t * top_k);
-  if (!counter) return;
-  // The plan rides along: the block that finishes last (it sees every token's choice) groups the
-  // routing entries by expert, and leaves the counter at zero for the next launch.
-  __shared__ int is_last;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < ROUTER_FEW_EXP) {
+    const int mine = blockIdx.y * ROUTER_FEW_EXP + threadIdx.x;
+    if (mine < experts) {
+      float total = partial[threadIdx.x][0];
+#pragma unroll
+      for (int q = 1; q < ROUTER_KPARTS; ++q) total += partial[threadIdx.x][q];
+      logits[(size_t)t * experts + mine] = total;
+    }
     __threadfence();
-    is_last = atomicAdd(counter, 1) == (int)gridDim.x - 1;
-    if (is_last) *counter = 0;
+  }
+  if (!counter) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int blocks = (int)(gridDim.x * gridDim.y);
+    is_last = atomicAdd(counter, 1) == blocks - 1;
+    if (is_last) *counter = 0;     // ready for the next launch
   }
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  plan_block(ids, (int)gridDim.x * top_k, experts, offsets, sorted_entry, slot_of_entry, active,
-             reinterpret_cast<int*>(lg + experts));
+  for (int tok = threadIdx.x; tok < n; tok += blockDim.x)
+    router_select<true>(logits + (size_t)tok * experts, experts, top_k, ids + (size_t)tok * top_k,
+                        scores + (size_t)tok * top_k);
+  __threadfence();
+  __syncthreads();
+  plan_block(ids, n * top_k, experts, offsets, sorted_entry, slot_of_entry, active, plan_scratch);
 }
 
 // Many tokens: a block takes ROUTER_TOK tokens x ROUTER_EXP experts with one warp per part of K;
@@ -535,23 +548,31 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
     }
     return HB_OK;
   }
-  const size_t smem = (size_t)experts * (sizeof(float) + (counter ? 2 * sizeof(int) : 0));
-  const int threads = experts >= 16 ? 512 : (experts >= 8 ? 256 : 128);   // a warp per expert where that fits
+  if (!logits_out) return HB_ERR_BAD_ARG;
+  const size_t smem = counter ? 2 * (size_t)experts * sizeof(int) : 0;
+  const int threads = ROUTER_FEW_EXP * ROUTER_KPARTS * 32;
+  const int columns = (experts + ROUTER_FEW_EXP - 1) / ROUTER_FEW_EXP;
+  if (columns > 65535) return HB_ERR_UNSUPPORTED;
+  const dim3 grid(n, columns);
   if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_F32)
-    router_topk_kernel<float, float><<<n, threads, smem, stream>>>((const float*)x, (const float*)w, hidden, experts,
-                                                               top_k, logits_out, ids, scores, offsets, sorted_entry,
-                                                               slot_of_entry, active, counter);
+    router_few_kernel<float, float><<<grid, threads, smem, stream>>>(
+        (const float*)x, (const float*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets, sorted_entry,
+        slot_of_entry, active, counter);
   else if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_BF16)
-    router_topk_kernel<float, __nv_bfloat16><<<n, threads, smem, stream>>>(
-        (const float*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores, offsets,
+    router_few_kernel<float, __nv_bfloat16><<<grid, threads, smem, stream>>>(
+        (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets,
         sorted_entry, slot_of_entry, active, counter);
   else if (x_dtype == HB_DTYPE_BF16 && w_dtype == HB_DTYPE_BF16)
-    router_topk_kernel<__nv_bfloat16, __nv_bfloat16><<<n, threads, smem, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, hidden, experts, top_k, logits_out, ids, scores, offsets,
+    router_few_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, smem, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets,
         sorted_entry, slot_of_entry, active, counter);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();
+  if (!counter) {
+    router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, ids, scores);
+    HB_LAUNCH_CHECK();
+  }
   return HB_OK;
 }
 

@@ -418,8 +418,7 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool 
         raise KernelError("router weight does not match the hidden size")
     ids = torch.empty((n, top_k), dtype=torch.int32, device=x.device)
     scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
-    # with more than 16 experts the many-token kernel selects from the stored logits
-    logits = torch.empty((n, experts), dtype=torch.float32, device=x.device) if want_logits or experts > 16 else None
+    logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)   # the blocks' meeting place
     _check(lib().hb_router_topk(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, _ptr(logits),
                                 _ptr(ids), _ptr(scores), _stream()), "router_topk")
     return ids, scores, logits if want_logits else None
@@ -465,7 +464,7 @@ def router_plan(x: torch.Tensor, w: torch.Tensor, top_k: int):
         raise KernelError("router weight does not match the hidden size")
     ids = torch.empty((n, top_k), dtype=torch.int32, device=x.device)
     scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
-    logits = torch.empty((n, experts), dtype=torch.float32, device=x.device) if experts > 16 else None
+    logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)   # the blocks' meeting place
     plan = _empty_plan(n * top_k, experts, x.device)
     _check(lib().hb_router_plan(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, _ptr(logits),
                                 _ptr(ids), _ptr(scores), _ptr(plan.offsets), _ptr(plan.sorted_entry),
