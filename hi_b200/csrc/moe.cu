@@ -392,8 +392,8 @@ __device__ __forceinline__ void gemv_rows(const T* __restrict__ A, int lda, cons
                                           const float* __restrict__ scores, void* __restrict__ out, int n_out,
                                           int K, int n, int r0, int lane) {
   // gate/up streams two weight rows per lane; the down projection has one, and needs twice the
-  // unroll and more for as many bytes in flight (measured: 5.25 -> 5.8 TB/s at 8 experts)
-  constexpr int GEMV_UNROLL = DUAL ? 4 : 16;
+  // unroll for as many bytes in flight (measured at three blocks per SM: 4 and 8 beat 2, 3 or 8 and 4 or 16)
+  constexpr int GEMV_UNROLL = DUAL ? 4 : 8;
   const T* arow[R];
   float sc[R];
 #pragma unroll
@@ -452,7 +452,7 @@ __device__ __forceinline__ void gemv_rows(const T* __restrict__ A, int lda, cons
 }
 
 template <typename T, bool DUAL>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+__global__ void __launch_bounds__(GEMV_WARPS * 32, 3)   // three blocks per SM (measured: +5 % on the batch-8 step over two)
 grouped_gemv_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry, int top_k,
                     const T* __restrict__ W0, const T* __restrict__ W1, const int* __restrict__ offsets,
                     const int* __restrict__ active, const float* __restrict__ scores, void* __restrict__ out,

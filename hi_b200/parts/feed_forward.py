@@ -72,7 +72,7 @@ class SigmoidRoutedExperts(Part):
 
     graph_safe = True
 
-    FEW_ROWS = 12    # up to this many routed rows the weight-streaming kernel is used (measured: from 16
+    FEW_ROWS = 10    # up to this many routed rows the weight-streaming kernel is used (measured: from 12
                      # rows the tcgen05 kernel streams the expert weights faster, even with nearly empty tiles)
     wants_f32_input = True   # the router reads the norm's float32 output
     OVERLAP_SHARED = True    # run the shared expert on a second stream beside the routed path
