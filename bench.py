@@ -295,7 +295,8 @@ def main(argv=None) -> int:
         "config": {"model": f"llama4-{args.model}-layers", "layers": args.layers, "layers_full": FULL_LAYERS,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "experts": cfg["num_local_experts"], "top_k": cfg["num_experts_per_tok"],
-                   "expert_inter": cfg["intermediate_size"], "vocab": vocab, "chunk": cfg["attention_chunk_size"],
+                   "expert_inter": cfg["intermediate_size"], "mlp_inter": cfg["intermediate_size_mlp"],
+                   "moe_every": cfg.get("interleave_moe_layer_step", 1), "vocab": vocab, "chunk": cfg["attention_chunk_size"],
                    "global_batch": args.batch, "seq_len": ctx_len, "page": page, "parallelism": "single-gpu",
                    "l2": "inputs larger than L2 (each step streams all weights it uses)",
                    "weights_load_s": round(load_s, 1)},

@@ -116,7 +116,62 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab, 
   }
 }
 
+// Argmax of every row with the row cut into gridDim.y parts, so that a few rows of a large
+// vocabulary are read by many SMs: each block leaves (value, lowest id) of its part, and the
+// block of a row that finishes last (a counter per row, zero between launches) picks among them.
+__global__ void argmax_parts_kernel(const float* __restrict__ logits, int vocab, float* part_val, int* part_idx,
+                                    int* counters, int* __restrict__ out) {
+  __shared__ float sval[ST];
+  __shared__ int sidx[ST];
+  const int r = blockIdx.x, part = blockIdx.y, parts = gridDim.y, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  const int slice = (vocab + parts - 1) / parts;
+  const int begin = min(part * slice, vocab), end = min(begin + slice, vocab);
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = begin + tid; i < end; i += ST) {
+    const float v = row[i];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  sval[tid] = bv; sidx[tid] = bi;
+  __syncthreads();
+  for (int s = ST / 2; s > 0; s >>= 1) {
+    if (tid < s) {
+      const float ov = sval[tid + s];
+      const int oi = sidx[tid + s];
+      if (ov > sval[tid] || (ov == sval[tid] && oi < sidx[tid])) { sval[tid] = ov; sidx[tid] = oi; }
+    }
+    __syncthreads();
+  }
+  if (tid != 0) return;
+  part_val[(size_t)r * parts + part] = sval[0];
+  part_idx[(size_t)r * parts + part] = sidx[0];
+  __threadfence();
+  if (atomicAdd(&counters[r], 1) != parts - 1) return;
+  counters[r] = 0;                 // ready for the next launch
+  __threadfence();
+  bv = -INFINITY; bi = 0x7fffffff;
+  for (int q = 0; q < parts; ++q) {
+    const float v = __ldcg(part_val + (size_t)r * parts + q);
+    const int i = __ldcg(part_idx + (size_t)r * parts + q);
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  out[r] = bi == 0x7fffffff ? 0 : bi;
+}
+
 }  // namespace
+
+// Greedy rows only, over many blocks. part_val / part_idx: [rows, parts] scratch; counters: [rows]
+// ints that are zero before the first call and are left at zero.
+extern "C" int hb_argmax_rows(const float* logits, int rows, int vocab, int parts, float* part_val, int* part_idx,
+                              int* counters, int* out, cudaStream_t stream) {
+  if (!logits || !out || !part_val || !part_idx || !counters || rows < 0 || vocab <= 0 || parts <= 0 || parts > 65535)
+    return HB_ERR_BAD_ARG;
+  if (rows == 0) return HB_OK;
+  argmax_parts_kernel<<<dim3(rows, parts), ST, 0, stream>>>(logits, vocab, part_val, part_idx, counters, out);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
 
 extern "C" int hb_sample_rows(const float* logits, int rows, int vocab, const float* temperatures,
                               const float* uniforms, int* out, cudaStream_t stream) {

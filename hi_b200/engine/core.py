@@ -156,7 +156,7 @@ class Engine:
             done += n
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], tap=None, feedback=None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], tap=None, feedback=None, borrow: bool = False) -> Optional[torch.Tensor]:
         """Run one batch. Returns float32 logits [wanted, vocab] on the device, in the order
         of the entries and of each entry's ``want`` (None if nothing is wanted). ``tap(name,
         tensor)``, if given, is called by parts that report intermediate tensors (router ids),
@@ -164,7 +164,10 @@ class Engine:
 
         ``feedback = (sampled, rows)``: an entry whose last token is ``IN_FLIGHT`` (-1) takes it on
         the device from ``sampled[rows[request_id]]``, an int32 tensor that the step before this
-        one filled (its sampled tokens): the step can be launched before the host has read them."""
+        one filled (its sampled tokens): the step can be launched before the host has read them.
+
+        ``borrow``: the caller uses the logits before it runs the next step (work queued on this
+        stream counts), so a captured step may hand out its own output buffer instead of a copy."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._resolve_status(wait=False)
         if not entries:
@@ -212,7 +215,7 @@ class Engine:
                     self._status = ops.PendingStatus(self.device)
                 self._status.enqueue()
                 self._status_pending = True
-            logits = graph.logits.clone()
+            logits = graph.logits if borrow else graph.logits.clone()
             ctx, logit_rows = graph.ctx, graph.logit_rows
         else:
             ctx, logit_rows = self._build_context(entries, feedback=feedback)

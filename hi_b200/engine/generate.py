@@ -139,7 +139,8 @@ class LLM:
                 raise RuntimeError("scheduler stalled: no request can take a step with the pages that are free")
             return done
         feedback = (previous.tokens_dev, previous.row_of) if previous is not None else None
-        logits = self.engine.step(self._entries(plan), feedback=feedback)
+        # the logits are sampled from (on this stream, or read back) before the next step is launched
+        logits = self.engine.step(self._entries(plan), feedback=feedback, borrow=True)
         sampling = [e.request for e in plan.entries if e.samples]
         done: List[Request] = []
         launched = None

@@ -37,6 +37,7 @@ _SIGNATURES = {
     "hb_gather_rows": [P, P, I, P, I, I, P],
     "hb_moe_gate_up_tc": [P, P, P, P, P, I, P, P, I, I, I, P, P],
     "hb_moe_down_tc": [P, P, P, I, P, I, I, I, P, P],
+    "hb_argmax_rows": [P, I, I, I, P, P, P, P, P],
     "hb_sample_rows": [P, I, I, P, P, P, P],
 }
 
@@ -613,11 +614,34 @@ def moe_down_tc(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan) -> torch
 
 
 # --------------------------------------------------------------------------- sampling
+ARGMAX_PARTS = 16            # blocks per row of the all-greedy sampler
+ARGMAX_MAX_ROWS = 1024
+ARGMAX_MIN_VOCAB = 8192
+_argmax_scratch: dict = {}   # device -> (values, ids, counters)
+
+
+def _argmax_buffers(dev):
+    b = _argmax_scratch.get(dev)
+    if b is None:
+        b = _argmax_scratch[dev] = (torch.empty(ARGMAX_MAX_ROWS * ARGMAX_PARTS, dtype=torch.float32, device=dev),
+                                    torch.empty(ARGMAX_MAX_ROWS * ARGMAX_PARTS, dtype=torch.int32, device=dev),
+                                    torch.zeros(ARGMAX_MAX_ROWS, dtype=torch.int32, device=dev))
+    return b
+
+
 def sample_rows(logits: torch.Tensor, temperatures: Optional[torch.Tensor],
                 uniforms: Optional[torch.Tensor]) -> torch.Tensor:
-    """One token per row of float32 logits: argmax where temperature <= 0, else inverse CDF."""
+    """One token per row of float32 logits: argmax where temperature <= 0, else inverse CDF.
+    Without temperatures (every row greedy) a few rows of a large vocabulary are cut over
+    ``ARGMAX_PARTS`` blocks each."""
     _need(logits, "logits", torch.float32)
     rows, vocab = logits.shape
+    if temperatures is None and rows <= ARGMAX_MAX_ROWS and vocab >= ARGMAX_MIN_VOCAB:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        vals, ids, counters = _argmax_buffers(logits.device)
+        _check(lib().hb_argmax_rows(_ptr(logits), rows, vocab, ARGMAX_PARTS, _ptr(vals), _ptr(ids), _ptr(counters),
+                                    _ptr(out), _stream()), "argmax_rows")
+        return out
     for t, nm in ((temperatures, "temperatures"), (uniforms, "uniforms")):
         if t is not None:
             _need(t, nm, torch.float32)

@@ -436,6 +436,27 @@ def test_router_ties_go_to_the_lower_id():
     close(scores[0], torch.sigmoid(torch.tensor([2.0, 2.0, 2.0, 0.5])), 1e-6)
 
 
+def test_greedy_rows_cut_over_many_blocks():
+    """Every row greedy and a large vocabulary: each row is read by several blocks and the last
+    one picks. Ties across parts go to the lower id; calls follow one another (the counters come
+    back to zero); more rows than the scratch holds take the one-block kernel."""
+    o = ops()
+    g = torch.Generator().manual_seed(9)
+    for rows, vocab in ((1, 8192), (8, 202048), (5, 8193), (64, 33333), (1100, 9000)):
+        for turn in range(3):
+            logits = torch.randn(rows, vocab, generator=g)
+            logits[0, vocab - 1] = logits[0, 7] = 50.0                 # first and last part tie
+            if rows > 2:
+                logits[2] = -float("inf")                              # nothing finite: id 0
+                logits[1, vocab // 2 + 1] = float("nan")
+            got = o.sample_rows(logits.to(DEV), None, None).cpu()
+            want = torch.stack([torch.argmax(torch.nan_to_num(r, nan=-float("inf"))) for r in logits])
+            if rows > 2:
+                want[2] = 0
+            assert got[0] == 7
+            assert torch.equal(got.long(), want), f"rows {rows} vocab {vocab} turn {turn}"
+
+
 def test_sampling_kernel_matches_the_plain_sampler():
     o = ops()
     g = torch.Generator().manual_seed(5)
