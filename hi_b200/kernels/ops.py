@@ -445,7 +445,8 @@ def _empty_plan(n: int, experts: int, dev) -> MoePlan:
                    torch.empty(experts + 1, dtype=torch.int32, device=dev))
 
 
-_block_counters: dict = {}     # device -> one int32 that kernels leave at zero
+_block_counters: dict = {}     # device -> one int32 that kernels leave at zero; launches that share it must
+                               # follow one another (the engine runs its steps on one stream)
 
 
 def _block_counter(dev) -> torch.Tensor:
@@ -617,7 +618,7 @@ def moe_down_tc(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan) -> torch
 ARGMAX_PARTS = 16            # blocks per row of the all-greedy sampler
 ARGMAX_MAX_ROWS = 1024
 ARGMAX_MIN_VOCAB = 8192
-_argmax_scratch: dict = {}   # device -> (values, ids, counters)
+_argmax_scratch: dict = {}   # device -> (values, ids, counters); shared by launches that follow one another
 
 
 def _argmax_buffers(dev):
