@@ -132,6 +132,18 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
   float* scratch = wgt + max_splits;
   const size_t th = blockIdx.x;
   const float* ml = part_ml + th * max_splits * 2;
+  // The partial rows of up to MERGE_AHEAD splits are asked for before anything else, so that they
+  // arrive while the weights are worked out (otherwise the merge is three trips to memory one
+  // after the other). A split beyond the token's range has an unwritten row: it may be loaded,
+  // but must not enter the sum (whatever the scratch holds there, even NaN); its weight is 0.
+  constexpr int MERGE_AHEAD = 32;
+  float ahead[MERGE_AHEAD];
+  const int d0 = threadIdx.x;
+  if (d0 < hd) {
+#pragma unroll
+    for (int s = 0; s < MERGE_AHEAD; ++s)
+      if (s < max_splits) ahead[s] = part_acc[(th * max_splits + s) * hd + d0];
+  }
   float m = -INFINITY;
   for (int s = threadIdx.x; s < max_splits; s += blockDim.x) m = fmaxf(m, ml[2 * s]);
   m = hb::block_max(m, scratch);
@@ -146,10 +158,19 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
   const float inv = l > 0.f ? 1.f / l : 0.f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
+    int s = 0;
+    if (d == d0) {
+#pragma unroll
+      for (int q = 0; q < MERGE_AHEAD; ++q) {
+        if (q < max_splits) {
+          const float ws = wgt[q];
+          if (ws != 0.f) o += ahead[q] * ws;
+        }
+      }
+      s = min(max_splits, MERGE_AHEAD);
+    }
 #pragma unroll 8
-    for (int s = 0; s < max_splits; ++s) {
-      // a split beyond the token's range has weight 0 and an unwritten row: it must not be read
-      // into the sum (whatever the scratch holds there, even NaN)
+    for (; s < max_splits; ++s) {
       const float ws = wgt[s];
       if (ws != 0.f) o += part_acc[(th * max_splits + s) * hd + d] * ws;
     }

@@ -94,7 +94,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const size_t src = row_map ? (size_t)row_map[r] : (size_t)r;
-  float4 v[NG];
+  float4 v[NG], wv[NG];
   float ss = 0.f;
   int slots[8];
   if (routed)
@@ -103,6 +103,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
   for (int g = 0; g < NG; ++g) {
     const int idx = (threadIdx.x + g * blockDim.x) * 4;
     if (idx < hidden) {
+      // the norm's weight is asked for now, so that it is there when the sum of squares is
+      wv[g] = w ? load4_any(w, w_dtype, idx) : make_float4(1.f, 1.f, 1.f, 1.f);
       float4 a = *reinterpret_cast<const float4*>(x + src * hidden + idx);
       if (delta) {
         const float4 d = load4_any(delta, delta_dtype, src * hidden + idx);
@@ -126,8 +128,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
     if (idx < hidden) {
       const float4 a = v[g];
       if (!row_map && (delta || routed)) *reinterpret_cast<float4*>(x + src * hidden + idx) = a;
-      const float4 wv = w ? load4_any(w, w_dtype, idx) : make_float4(1.f, 1.f, 1.f, 1.f);
-      const float4 o = make_float4(a.x * inv * wv.x, a.y * inv * wv.y, a.z * inv * wv.z, a.w * inv * wv.w);
+      const float4 o = make_float4(a.x * inv * wv[g].x, a.y * inv * wv[g].y, a.z * inv * wv[g].z, a.w * inv * wv[g].w);
       store4_any(y, y_dtype, (size_t)r * hidden + idx, o);
       if (y_f32) *reinterpret_cast<float4*>(y_f32 + (size_t)r * hidden + idx) = o;
     }
