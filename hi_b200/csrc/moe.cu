@@ -17,8 +17,9 @@ namespace {
 // Stable counting sort of the n = tokens*top_k routing entries by expert:
 // offsets[e]..offsets[e+1] are the sorted slots of expert e, in entry order.
 // active[0] = number of experts with at least one row, active[1..] = their ids in order.
-// `ids` is read past L1 (in the fused router + plan kernel other blocks wrote it).
+// `ids` is read past L1 (other blocks may have written it), or lies in shared memory (IDS_SHARED).
 // `sm` holds 2 * experts ints.
+template <bool IDS_SHARED = false>
 __device__ __forceinline__ void plan_block(const int* ids, int n, int experts, int* __restrict__ offsets,
                                            int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry,
                                            int* __restrict__ active, int* sm) {
@@ -27,7 +28,7 @@ __device__ __forceinline__ void plan_block(const int* ids, int n, int experts, i
   for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = __ldcg(ids + i);
+    const int e = IDS_SHARED ? ids[i] : __ldcg(ids + i);
     if (e >= 0 && e < experts) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
@@ -47,7 +48,7 @@ __device__ __forceinline__ void plan_block(const int* ids, int n, int experts, i
     const int lane = threadIdx.x;
     for (int start = 0; start < n; start += 32) {
       const int i = start + lane;
-      int e = i < n ? __ldcg(ids + i) : -1;
+      int e = i < n ? (IDS_SHARED ? ids[i] : __ldcg(ids + i)) : -1;
       if (e >= experts) e = -1;
       const unsigned peers = __match_any_sync(0xffffffffu, e);
       const int rank = __popc(peers & ((1u << lane) - 1u));
@@ -115,7 +116,7 @@ router_few_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int n, int
                   int* counter) {
   __shared__ float partial[ROUTER_FEW_EXP][ROUTER_KPARTS];
   __shared__ int is_last;
-  extern __shared__ int plan_scratch[];  // 2 * experts ints, for the block that makes the plan
+  extern __shared__ int plan_scratch[];  // 2 * experts + n * top_k ints, for the block that makes the plan
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = warp % ROUTER_KPARTS, local = warp / ROUTER_KPARTS;
@@ -177,12 +178,15 @@ router_few_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int n, int
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int tok = threadIdx.x; tok < n; tok += blockDim.x)
-    router_select<true>(logits + (size_t)tok * experts, experts, top_k, ids + (size_t)tok * top_k,
-                        scores + (size_t)tok * top_k);
-  __threadfence();
+  // the choices go to global memory for the kernels that follow and stay in shared memory for the plan
+  int* s_ids = plan_scratch + 2 * experts;          // [n * top_k]
+  for (int tok = threadIdx.x; tok < n; tok += blockDim.x) {
+    int* mine = s_ids + tok * top_k;
+    router_select<true>(logits + (size_t)tok * experts, experts, top_k, mine, scores + (size_t)tok * top_k);
+    for (int r = 0; r < top_k; ++r) ids[(size_t)tok * top_k + r] = mine[r];
+  }
   __syncthreads();
-  plan_block(ids, n * top_k, experts, offsets, sorted_entry, slot_of_entry, active, plan_scratch);
+  plan_block<true>(s_ids, n * top_k, experts, offsets, sorted_entry, slot_of_entry, active, plan_scratch);
 }
 
 // Many tokens: a block takes ROUTER_TOK tokens x ROUTER_EXP experts with one warp per part of K;
@@ -549,7 +553,11 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
     return HB_OK;
   }
   if (!logits_out) return HB_ERR_BAD_ARG;
-  const size_t smem = counter ? 2 * (size_t)experts * sizeof(int) : 0;
+  // one launch does it all while the choices of all tokens fit a block's shared memory; a longer
+  // step (float32 weights with an odd width, other dtypes) selects and plans in launches of their own
+  const size_t fused_smem = (2 * (size_t)experts + (size_t)n * top_k) * sizeof(int);
+  int* const fused = (counter && fused_smem <= 32 * 1024) ? counter : nullptr;
+  const size_t smem = fused ? fused_smem : 0;
   const int threads = ROUTER_FEW_EXP * ROUTER_KPARTS * 32;
   const int columns = (experts + ROUTER_FEW_EXP - 1) / ROUTER_FEW_EXP;
   if (columns > 65535) return HB_ERR_UNSUPPORTED;
@@ -557,21 +565,26 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
   if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_F32)
     router_few_kernel<float, float><<<grid, threads, smem, stream>>>(
         (const float*)x, (const float*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets, sorted_entry,
-        slot_of_entry, active, counter);
+        slot_of_entry, active, fused);
   else if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_BF16)
     router_few_kernel<float, __nv_bfloat16><<<grid, threads, smem, stream>>>(
         (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets,
-        sorted_entry, slot_of_entry, active, counter);
+        sorted_entry, slot_of_entry, active, fused);
   else if (x_dtype == HB_DTYPE_BF16 && w_dtype == HB_DTYPE_BF16)
     router_few_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, smem, stream>>>(
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets,
-        sorted_entry, slot_of_entry, active, counter);
+        sorted_entry, slot_of_entry, active, fused);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();
-  if (!counter) {
+  if (!fused) {
     router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, ids, scores);
     HB_LAUNCH_CHECK();
+    if (counter) {
+      moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, n * top_k, experts, offsets,
+                                                                              sorted_entry, slot_of_entry, active);
+      HB_LAUNCH_CHECK();
+    }
   }
   return HB_OK;
 }
