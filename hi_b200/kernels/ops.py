@@ -276,14 +276,15 @@ def _decode_splits(longest: int, groups: int) -> Tuple[int, int]:
     """How to cut ``longest`` keys for ``groups`` (token, kv head) pairs: the number of splits
     that minimises waves x (tiles per block + a block's fixed cost) + a cost per split (the
     merge) on 148 SMs x 3 resident blocks, none shorter than ATTENTION_SPLIT keys. Measured at
-    8 requests x 8,192 keys: 6 splits (one wave of 384 blocks) 57 us, 13 splits (two waves) 63 us.
+    8 requests x 8,192 keys: 6 splits (one wave of 384 blocks) 57 us, 13 splits (two waves) 63 us;
+    one request x 32,768 keys: 32 splits 33 us, 47 splits 36 us.
     The cut moves results by rounding only."""
     best = (None, 1, longest)
     for s in range(1, max(1, -(-longest // ATTENTION_SPLIT)) + 1):
         size = -(-(-(-longest // s)) // 64) * 64
         real = -(-longest // size)
         waves = -(-(real * groups) // DECODE_RESIDENT_BLOCKS)
-        cost = waves * (size // 64 + 1.5) + 0.2 * real
+        cost = waves * (size // 64 + 1.5) + 0.2 * real + 0.3 * max(0, real - 32)   # past 32 the merge reads in turns
         if best[0] is None or cost < best[0]:
             best = (cost, real, size)
     return best[2], best[1]
