@@ -65,10 +65,12 @@ def lib():
 
 
 LAUNCHES = [0]     # kernels of this library enqueued so far (benchmarks report the difference)
+CALLS: dict = {}   # ... and by entry point: which kernel family took the work (tests look here)
 
 
 def _check(code: int, name: str) -> None:
     LAUNCHES[0] += 1
+    CALLS[name] = CALLS.get(name, 0) + 1
     if code != 0:
         what = _ERRORS.get(code, f"CUDA error {code}")
         raise KernelError(f"{name}: {what}")
@@ -331,9 +333,10 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                                          _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size,
                                          int(chunk), int(window), float(scale), split_size, splits, _ptr(part_acc),
                                          _ptr(part_ml), _stream())
+        _check(code, "attention_decode")
     else:
         TC_USED[0] = True
-    _check(code, "attention_decode")
+        _check(code, "attention_decode_tma")
     if splits > 1:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
                                         _stream()), "attention_merge")
