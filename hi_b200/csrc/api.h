@@ -75,6 +75,8 @@ int hb_moe_down_tc(const void* act, const void* w_down, const int* offsets, int 
 
 int hb_sample_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* uniforms,
                    int* out, cudaStream_t stream);
+int hb_ranked_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* top_ps,
+                   const int* top_ks, const float* uniforms, int* out, cudaStream_t stream);
 int hb_argmax_rows(const float* logits, int rows, int vocab, int parts, float* part_val, int* part_idx, int* counters,
                    int* out, cudaStream_t stream);
 

@@ -159,6 +159,167 @@ __global__ void argmax_parts_kernel(const float* __restrict__ logits, int vocab,
   out[r] = bi == 0x7fffffff ? 0 : bi;
 }
 
+// ---------------------------------------------------------------- ranked rows (top-k / top-p)
+// One block per row, for rows with a temperature and a top-k below the vocabulary or a top-p
+// inside (0, 1); other rows are left as they are. The rule is the host sampler's
+// (crates/hi-cuda/src/qwen_cpu.rs:3692-3704, crates/hi-mlx/src/generate.rs:86-108):
+//   p = exp(l/T - max) / sum; order by p descending, ties by id; keep the first k; of those the
+//   shortest prefix whose running sum reaches top_p; draw = u * (sum of the kept); walk.
+// The kept ids are a prefix of that order, so the kernel first finds a boundary value t: the
+// largest p bit pattern such that the words with p >= t number at least k or hold at least top_p
+// of the mass (slightly more, so that rounding cannot leave one out). It finds t four bits at a
+// time, counting for fifteen thresholds in one pass over the row, with sums in a fixed order (no
+// atomics: the same row gives the same t). The words with p >= t are sorted in shared memory and
+// one thread applies the rule to them in the host's order. More than RANK_CAP such words (a nearly
+// flat distribution with a wide top-p), or logits that are not finite: out[r] = -1, and the caller
+// ranks that row on the host.
+constexpr int RANK_THREADS = 1024;
+constexpr int RANK_CAP = 4096;
+constexpr int RANK_WAYS = 15;
+
+__global__ void __launch_bounds__(RANK_THREADS)
+ranked_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temps,
+                   const float* __restrict__ top_ps, const int* __restrict__ top_ks,
+                   const float* __restrict__ uniforms, int* __restrict__ out) {
+  __shared__ float scratch[33];
+  __shared__ float red_mass[32][RANK_WAYS];
+  __shared__ int red_cnt[32][RANK_WAYS];
+  __shared__ float cand_p[RANK_CAP];
+  __shared__ int cand_id[RANK_CAP];
+  __shared__ unsigned s_prefix;
+  __shared__ int s_count;
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float temp = temps[r];
+  const int k_in = top_ks[r];
+  const bool has_k = k_in > 0 && k_in < vocab;
+  const float cutoff = fminf(fmaxf(top_ps[r], 0.f), 1.f);
+  const bool has_p = cutoff > 0.f && cutoff < 1.f;
+  if (!(temp > 0.f) || !isfinite(temp) || (!has_k && !has_p)) return;     // not a ranked row
+  const int k_eff = has_k ? k_in : vocab;
+  const float* row = logits + (size_t)r * vocab;
+
+  float mx = -INFINITY;
+  bool finite = true;
+  for (int i = tid; i < vocab; i += RANK_THREADS) {
+    const float z = row[i] / temp;
+    finite &= isfinite(z);
+    mx = fmaxf(mx, z);
+  }
+  mx = hb::block_max(mx, scratch);
+  const float bad = hb::block_sum(finite ? 0.f : 1.f, scratch);
+  if (bad > 0.f || !isfinite(mx)) {
+    if (tid == 0) out[r] = -1;
+    return;
+  }
+  float local = 0.f;
+  for (int i = tid; i < vocab; i += RANK_THREADS) local += expf(row[i] / temp - mx);
+  const float total = hb::block_sum(local, scratch);
+  // p of word i, the same expression wherever it is needed
+  auto prob = [&](int i) { return expf(row[i] / temp - mx) / total; };
+
+  // ---- the boundary, four bits at a time from the top
+  const float cut_mass = has_p ? cutoff * 1.0005f + 1e-6f : INFINITY;
+  if (tid == 0) { s_prefix = 0u; s_count = vocab; }
+  __syncthreads();
+  for (int shift = 28; shift >= 0; shift -= 4) {
+    const unsigned prefix = s_prefix;
+    int cnt[RANK_WAYS];
+    float mass[RANK_WAYS];
+#pragma unroll
+    for (int j = 0; j < RANK_WAYS; ++j) { cnt[j] = 0; mass[j] = 0.f; }
+    for (int i = tid; i < vocab; i += RANK_THREADS) {
+      const float p = prob(i);
+      const unsigned key = __float_as_uint(p);
+      if (key < prefix) continue;                       // below every threshold of this round
+#pragma unroll
+      for (int j = 0; j < RANK_WAYS; ++j)
+        if (key >= (prefix | ((unsigned)(j + 1) << shift))) { cnt[j] += 1; mass[j] += p; }
+    }
+#pragma unroll
+    for (int j = 0; j < RANK_WAYS; ++j) {
+      int c = cnt[j];
+      float m = mass[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) { c += __shfl_xor_sync(0xffffffffu, c, o); m += __shfl_xor_sync(0xffffffffu, m, o); }
+      if (lane == 0) { red_cnt[warp][j] = c; red_mass[warp][j] = m; }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int best = 0, best_count = s_count;
+      for (int j = RANK_WAYS - 1; j >= 0; --j) {        // the largest threshold that still holds enough
+        int c = 0;
+        float m = 0.f;
+        for (int w = 0; w < RANK_THREADS / 32; ++w) { c += red_cnt[w][j]; m += red_mass[w][j]; }
+        if (c >= k_eff || m >= cut_mass) { best = j + 1; best_count = c; break; }
+      }
+      s_prefix = prefix | ((unsigned)best << shift);
+      s_count = best_count;
+    }
+    __syncthreads();
+  }
+  const unsigned boundary = s_prefix;
+  const int n_cand = s_count;                           // words with p >= boundary
+  if (n_cand > RANK_CAP || n_cand < 1) {
+    if (tid == 0) out[r] = -1;
+    return;
+  }
+  // ---- gather the candidates, sort them by (p descending, id ascending)
+  if (tid == 0) s_count = 0;
+  __syncthreads();
+  for (int i = tid; i < vocab; i += RANK_THREADS) {
+    const float p = prob(i);
+    if (__float_as_uint(p) >= boundary) {
+      const int at = atomicAdd(&s_count, 1);
+      if (at < RANK_CAP) { cand_p[at] = p; cand_id[at] = i; }
+    }
+  }
+  __syncthreads();
+  int size = 1;
+  while (size < n_cand) size <<= 1;
+  for (int i = n_cand + tid; i < size; i += RANK_THREADS) { cand_p[i] = -1.f; cand_id[i] = 0x7fffffff; }   // padding sorts last
+  __syncthreads();
+  for (int span = 2; span <= size; span <<= 1) {
+    for (int step = span >> 1; step > 0; step >>= 1) {
+      for (int i = tid; i < size; i += RANK_THREADS) {
+        const int other = i ^ step;
+        if (other > i) {
+          const bool ascending_block = (i & span) != 0;     // blocks alternate so that the whole ends in order
+          const float pa = cand_p[i], pb = cand_p[other];
+          const int ia = cand_id[i], ib = cand_id[other];
+          const bool a_first = pa > pb || (pa == pb && ia < ib);  // a belongs before b in the wanted order
+          if (a_first == ascending_block) {
+            cand_p[i] = pb; cand_p[other] = pa;
+            cand_id[i] = ib; cand_id[other] = ia;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  // ---- the host's rule on the sorted candidates, by one thread in the host's order
+  if (tid == 0) {
+    int n = min(n_cand, k_eff);
+    if (has_p) {
+      float cum = 0.f;
+      int keep = n;
+      for (int i = 0; i < n; ++i) {
+        cum += cand_p[i];
+        if (cum >= cutoff) { keep = i + 1; break; }
+      }
+      n = max(keep, 1);
+    }
+    float kept = 0.f;
+    for (int i = 0; i < n; ++i) kept += cand_p[i];
+    float draw = uniforms[r] * kept;
+    int pick = cand_id[0];
+    for (int i = 0; i < n; ++i) {
+      if (draw <= cand_p[i]) { pick = cand_id[i]; break; }
+      draw -= cand_p[i];
+    }
+    out[r] = pick;
+  }
+}
+
 }  // namespace
 
 // Greedy rows only, over many blocks. part_val / part_idx: [rows, parts] scratch; counters: [rows]
@@ -169,6 +330,17 @@ extern "C" int hb_argmax_rows(const float* logits, int rows, int vocab, int part
     return HB_ERR_BAD_ARG;
   if (rows == 0) return HB_OK;
   argmax_parts_kernel<<<dim3(rows, parts), ST, 0, stream>>>(logits, vocab, part_val, part_idx, counters, out);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+// Rows with top-k / top-p, after hb_sample_rows has filled the others: see ranked_rows_kernel.
+// top_ks <= 0 or >= vocab means no top-k; out[r] = -1 asks the caller to rank row r on the host.
+extern "C" int hb_ranked_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* top_ps,
+                              const int* top_ks, const float* uniforms, int* out, cudaStream_t stream) {
+  if (!logits || !temperatures || !top_ps || !top_ks || !uniforms || !out || rows < 0 || vocab <= 0) return HB_ERR_BAD_ARG;
+  if (rows == 0) return HB_OK;
+  ranked_rows_kernel<<<rows, RANK_THREADS, 0, stream>>>(logits, vocab, temperatures, top_ps, top_ks, uniforms, out);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

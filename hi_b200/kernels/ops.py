@@ -38,6 +38,7 @@ _SIGNATURES = {
     "hb_moe_gate_up_tc": [P, P, P, P, P, I, P, P, I, I, I, P, P],
     "hb_moe_down_tc": [P, P, P, I, P, I, I, I, P, P],
     "hb_argmax_rows": [P, I, I, I, P, P, P, P, P],
+    "hb_ranked_rows": [P, I, I, P, P, P, P, P, P],
     "hb_sample_rows": [P, I, I, P, P, P, P],
 }
 
@@ -656,3 +657,20 @@ def sample_rows(logits: torch.Tensor, temperatures: Optional[torch.Tensor],
     _check(lib().hb_sample_rows(_ptr(logits), rows, vocab, _ptr(temperatures), _ptr(uniforms), _ptr(out), _stream()),
            "sample_rows")
     return out
+
+
+def ranked_rows(logits: torch.Tensor, temperatures: torch.Tensor, top_ps: torch.Tensor, top_ks: torch.Tensor,
+                uniforms: torch.Tensor, out: torch.Tensor) -> None:
+    """Top-k / top-p rows of float32 logits, sampled in place into ``out`` (int32 [R]) by the host
+    sampler's rule; rows without a temperature, or with neither a top-k below the vocabulary nor a
+    top-p inside (0, 1), are left as they are. ``out[r] == -1`` afterwards: the row has more than
+    4,096 candidates or logits that are not finite, and has to be ranked on the host."""
+    _need(logits, "logits", torch.float32)
+    rows = logits.shape[0]
+    for t, nm, dt in ((temperatures, "temperatures", torch.float32), (top_ps, "top_ps", torch.float32),
+                      (top_ks, "top_ks", torch.int32), (uniforms, "uniforms", torch.float32), (out, "out", torch.int32)):
+        _need(t, nm, dt)
+        if t.numel() != rows:
+            raise KernelError(f"{nm} needs one entry per row")
+    _check(lib().hb_ranked_rows(_ptr(logits), rows, logits.shape[1], _ptr(temperatures), _ptr(top_ps), _ptr(top_ks),
+                                _ptr(uniforms), _ptr(out), _stream()), "ranked_rows")

@@ -1,9 +1,11 @@
 """Sampling: greedy, temperature, and ranked (top-k / top-p), per request.
 
 Greedy and temperature-only rows are sampled on the GPU in one launch
-(``hi_b200/csrc/sampling.cu``); ranked rows are redone on the host from the row's logits, as
-the reference does by default (crates/hi-cuda/src/kernels.cu:8041-8072 and the comment above
-it; host sampler crates/hi-cuda/src/qwen_cpu.rs:3657-3732, crates/hi-mlx/src/generate.rs:50-110).
+(``hi_b200/csrc/sampling.cu``); ranked rows by a second kernel that follows the host sampler's rule
+(the reference ranks on the host by default: crates/hi-cuda/src/kernels.cu:8041-8072 and the
+comment above it; host sampler crates/hi-cuda/src/qwen_cpu.rs:3657-3732,
+crates/hi-mlx/src/generate.rs:50-110). :func:`ranked_sample` is that rule on the host; it takes the
+rows the kernel hands back (more than 4,096 candidates).
 Each request owns its generator and draws exactly one uniform per sampled token, so its
 stream does not depend on what else is in the batch (crates/hi-cuda/src/lib.rs:5658-5662).
 """
@@ -112,11 +114,20 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequenc
     if all(p.greedy for p in params):
         return ops.sample_rows(logits, None, None).tolist()
     uniforms = [0.0 if p.greedy else rng.next_f32() for p, rng in zip(params, rngs)]
-    # ranked rows get temperature 0 on the device (a placeholder argmax) and are redone here
-    temps = [0.0 if (p.greedy or p.ranked(vocab)) else float(p.temperature) for p in params]
-    host = torch.tensor([temps, uniforms], dtype=torch.float32).to(logits.device, non_blocking=True)
-    out = ops.sample_rows(logits, host[0].contiguous(), host[1].contiguous()).tolist()
+    ranked = [p.ranked(vocab) for p in params]
+    # the one-launch sampler takes the greedy and the temperature-only rows (ranked rows: a
+    # placeholder argmax); the ranked kernel then takes the rows with top-k / top-p
+    temps = [0.0 if (p.greedy or rk) else float(p.temperature) for p, rk in zip(params, ranked)]
+    rank_temps = [float(p.temperature) if rk else 0.0 for p, rk in zip(params, ranked)]
+    top_ps = [float(p.top_p) for p in params]
+    host = torch.tensor([temps, uniforms, rank_temps, top_ps], dtype=torch.float32).to(logits.device, non_blocking=True)
+    out_dev = ops.sample_rows(logits, host[0].contiguous(), host[1].contiguous())
+    if any(ranked):
+        top_ks = torch.tensor([int(p.top_k or 0) for p in params], dtype=torch.int32).to(logits.device, non_blocking=True)
+        ops.ranked_rows(logits, host[2].contiguous(), host[3].contiguous(), top_ks, host[1].contiguous(), out_dev)
+    out = out_dev.tolist()
     for r, p in enumerate(params):
-        if p.ranked(vocab):
+        if ranked[r] and out[r] < 0:
+            # more candidates than the kernel sorts (a nearly flat distribution with a wide top-p): the host ranks
             out[r] = ranked_sample(logits[r].cpu().numpy(), p.temperature, p.top_p, p.top_k, uniforms[r])
     return out

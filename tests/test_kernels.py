@@ -458,6 +458,50 @@ def test_greedy_rows_cut_over_many_blocks():
             assert torch.equal(got.long(), want), f"rows {rows} vocab {vocab} turn {turn}"
 
 
+def test_ranked_rows_follow_the_host_sampler():
+    """top-k / top-p on the GPU against the host's rule, row by row: peaked and flatter rows, ties,
+    several vocabularies; rows that are not ranked stay as they were; a row with more candidates
+    than the kernel sorts comes back as -1."""
+    from hi_b200.sampling import ranked_sample
+
+    o = ops()
+    g = torch.Generator().manual_seed(31)
+    handed_back = 0
+    for vocab, scale in ((17, 2.0), (515, 3.0), (5000, 1.0), (50000, 4.0), (202048, 3.0), (202048, 6.0)):
+        rows = 12
+        logits = torch.randn(rows, vocab, generator=g) * scale
+        logits[1, 3] = logits[1, vocab - 2] = logits[1].max() + 1.0          # the two largest tie
+        logits[2, : min(vocab, 40)] = 5.0 * scale                             # a run of equal words
+        temps = torch.tensor([0.7, 1.0, 1.3, 0.5, 1.0, 0.0, 0.9, 1.0, 2.0, 1.0, 0.8, 1.0])
+        top_ps = torch.tensor([0.9, 0.5, 1.0, 0.1, 0.95, 0.9, 1.0, 0.3, 0.8, 1.0, 0.999, 0.6])
+        top_ks = torch.tensor([0, 5, 50, 0, 3, 7, 0, 1, 20, vocab + 5, 0, 64], dtype=torch.int32)
+        for turn in range(3):
+            us = torch.rand(rows, generator=g)
+            before = torch.full((rows,), -7, dtype=torch.int32)
+            out = before.to(DEV)
+            o.ranked_rows(logits.to(DEV), temps.to(DEV), top_ps.to(DEV), top_ks.to(DEV), us.to(DEV), out)
+            got = out.cpu().tolist()
+            for r in range(rows):
+                k = int(top_ks[r])
+                is_ranked = float(temps[r]) > 0 and ((0 < k < vocab) or 0.0 < float(top_ps[r]) < 1.0)
+                if not is_ranked:
+                    assert got[r] == -7, f"row {r} is not ranked and was touched"
+                    continue
+                want = ranked_sample(logits[r].numpy(), float(temps[r]), float(top_ps[r]), k or None, float(us[r]))
+                if got[r] == -1:
+                    handed_back += 1
+                    assert not (0 < k <= 64), f"vocab {vocab} row {r}: a small top-k was handed back"
+                    continue
+                assert got[r] == want, f"vocab {vocab} scale {scale} row {r} turn {turn}: {got[r]} != {want}"
+    assert handed_back < 30, "too many rows went back to the host"
+    # a flat row with a wide top-p has more candidates than the kernel sorts
+    flat = torch.zeros(1, 5000)
+    out = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.ranked_rows(flat.to(DEV), torch.ones(1, device=DEV), torch.full((1,), 0.9, device=DEV),
+                  torch.zeros(1, dtype=torch.int32, device=DEV), torch.full((1,), 0.5, device=DEV), out)
+    assert int(out[0]) == -1
+
+
 def test_sampling_kernel_matches_the_plain_sampler():
     o = ops()
     g = torch.Generator().manual_seed(5)
