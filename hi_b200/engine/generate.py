@@ -51,7 +51,8 @@ class LLM:
     runs: its decode tokens are taken on the device from what that step sampled, and the host reads
     the sampled tokens one step late (finished requests and ``on_token`` calls come one ``step()``
     later; a request that ends leaves one unread row in the step that was already launched). Rows
-    that sample with top-k / top-p are ranked on the host and make their step wait.
+    that sample with top-k / top-p make their step wait: the kernel that ranks them may hand a row
+    back to the host (more candidates than it sorts), so the host reads its result at once.
 
     ``model`` is a model folder, or a config dict together with ``random_seed`` (weights are
     then generated on the device). Options are the reference's serve flags
@@ -151,7 +152,7 @@ class LLM:
                 launched = _Launched(plan, sampling, tokens_dev, self._token_buffers[self._turn], self._token_events[self._turn])
         if previous is not None:                       # the step before: its tokens have had a whole step to arrive
             done += self._read(previous, on_token)
-        if launched is None:                           # read this step's samples now (host-side sampling, or no lookahead)
+        if launched is None:                           # read this step's samples now (ranked rows, or no lookahead)
             tokens = sample(logits, [r.params for r in sampling], [r.rng for r in sampling]) if sampling else []
             done += self._commit(plan, sampling, tokens, on_token)
         self._launched = launched

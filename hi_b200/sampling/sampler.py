@@ -91,8 +91,9 @@ def ranked_sample(row: np.ndarray, temperature: float, top_p: float, top_k: Opti
 def sample_on_device(logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[Lcg]
                      ) -> Optional[torch.Tensor]:
     """One token for each row of float32 ``logits`` [R, V], left on the device as int32 [R] (no
-    wait for the GPU), or None if a row samples with top-k / top-p: those are ranked on the host
-    (use :func:`sample`; no generator has been advanced then)."""
+    wait for the GPU), or None if a row samples with top-k / top-p: the kernel that ranks them may
+    hand a row back to the host, so its result has to be read at once (use :func:`sample`; no
+    generator has been advanced then)."""
     rows, vocab = logits.shape
     if rows != len(params) or rows != len(rngs):
         raise ValueError("one SamplingParams and one generator per row are needed")
