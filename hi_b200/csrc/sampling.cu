@@ -301,12 +301,16 @@ ranked_rows_kernel(const float* __restrict__ logits, int vocab, const float* __r
     int n = min(n_cand, k_eff);
     if (has_p) {
       float cum = 0.f;
-      int keep = n;
+      int keep = -1;
       for (int i = 0; i < n; ++i) {
         cum += cand_p[i];
         if (cum >= cutoff) { keep = i + 1; break; }
       }
-      n = max(keep, 1);
+      if (keep < 0 && n < k_eff) {      // the running sum fell short of top_p within the candidates (rounding of
+        out[r] = -1;                    // a long sum): the host's prefix is longer than what was gathered
+        return;
+      }
+      n = keep < 0 ? n : keep;
     }
     float kept = 0.f;
     for (int i = 0; i < n; ++i) kept += cand_p[i];
