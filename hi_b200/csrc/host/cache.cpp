@@ -98,6 +98,25 @@ void CacheManager::pages_needed(int64_t request, int n_new, int64_t length, int*
   }
 }
 
+void CacheManager::peak_pages_needed(int64_t request, int64_t n_new, int64_t length, int* out) {
+  const RequestCache* rc = request >= 0 ? find(request) : nullptr;
+  if (rc) length = rc->length;
+  const int64_t need_blocks = (length + n_new + page_size_ - 1) / page_size_;
+  for (size_t g = 0; g < windows_.size(); ++g) {
+    const int64_t have = rc ? (int64_t)rc->tables[g].size() : 0;
+    const int64_t first_live = windows_[g].first_live(length) / page_size_;
+    int64_t need = std::max<int64_t>(0, need_blocks - std::max(have, first_live));
+    if (windows_[g].kind != HBH_WINDOW_NONE) {
+      int64_t held = 0;
+      if (rc)
+        for (int page : rc->tables[g]) held += page != HBH_FREED;
+      const int64_t most = (windows_[g].size + page_size_ - 1) / page_size_ + 1;
+      need = std::min(need, std::max<int64_t>(0, most - held));
+    }
+    out[g] = (int)need;
+  }
+}
+
 bool CacheManager::fits(int64_t request, int n_new, int64_t length, const int* promised) {
   std::vector<int> need(windows_.size());
   pages_needed(request, n_new, length, need.data());

@@ -69,6 +69,10 @@ class CacheManager {
   int open(int64_t request, int* slot);
   int close(int64_t request);
   void pages_needed(int64_t request, int n_new, int64_t length, int* out);
+  // the most new pages the next n_new tokens can need at any one time when they are fed in
+  // portions that may be as short as one token: a windowed group never has to hold more than its
+  // window and the page being written
+  void peak_pages_needed(int64_t request, int64_t n_new, int64_t length, int* out);
   bool fits(int64_t request, int n_new, int64_t length, const int* promised);
   int reserve(int64_t request, int n_new, int* fail);
   int unreserve(int64_t request, const int* table_lengths);

@@ -3,11 +3,13 @@
 // length, tokens generated, tokens in the cache); the token values stay with the caller.
 //
 // When pages run out, in this order:
-//   1. no new request is admitted;
+//   1. no new request is admitted; while an older request is still in its prompt a new one is
+//      admitted only if the rest of every such prompt and the whole new prompt fit together;
 //   2. prompt portions are shrunk to the pages that are free, or wait a step;
-//   3. if a DECODE token cannot get its page, the most recently admitted running request is
-//      preempted: its pages and slot go back, and it returns to the head of the waiting queue
-//      with prompt + generated tokens as its prompt;
+//   3. if a DECODE token cannot get its page, or if every running request is in its prompt and
+//      none of them can get a page for even one token (no step runs, so no later step would free
+//      one), the most recently admitted running request is preempted: its pages and slot go back,
+//      and it returns to the head of the waiting queue with prompt + generated tokens as its prompt;
 //   4. a request that could never fit is refused when it is added (insufficient_gpu_memory,
 //      crates/hi-cuda/src/lib.rs:845-858).
 //
@@ -134,6 +136,13 @@ class Scheduler {
     int64_t n = 0;
     for (const Entry& e : entries_) n += e.count;
     return n;
+  }
+  // pages the rest of r's tokens still needs after the first `planned` of them, fed in portions
+  void add_later_need(const Request* r, int64_t planned, std::vector<int>& later) const {
+    std::vector<int> all(later.size()), now(later.size());
+    cache_->peak_pages_needed(r->id, r->pending(), r->computed, all.data());
+    needed(r, planned, now);
+    for (size_t g = 0; g < later.size(); ++g) later[g] += std::max(0, all[g] - now[g]);
   }
   void preempt(Request* victim);
   void plan_portion(Request* r, std::vector<int>& promised, int64_t budget);
@@ -275,20 +284,55 @@ int Scheduler::plan() {
   }
 
   // 2. running requests still in their prompt get portions, oldest first
-  for (Request* r : std::vector<Request*>(running_)) {
-    if (budget <= 0 || (int)entries_.size() >= max_batch_) break;
-    if (std::find(planned.begin(), planned.end(), r) != planned.end() || r->pending() <= 0 || !r->may_sample_more())
-      continue;                                  // planned, or only waiting for its last sample to be committed
-    plan_portion(r, promised, budget);
-    budget = budget_ - planned_tokens();
+  const auto portions = [&]() {
+    for (Request* r : std::vector<Request*>(running_)) {
+      if (budget <= 0 || (int)entries_.size() >= max_batch_) break;
+      if (std::find(planned.begin(), planned.end(), r) != planned.end() || r->pending() <= 0 || !r->may_sample_more())
+        continue;                                  // planned, or only waiting for its last sample to be committed
+      plan_portion(r, promised, budget);
+      budget = budget_ - planned_tokens();
+    }
+  };
+  int64_t stalled_before = stalled;
+  portions();
+  // every running request waits for a page and no step is in flight whose end could free one:
+  // the youngest goes back to the queue until one of the older ones can move
+  while (entries_.empty() && stalled > stalled_before && outstanding_.empty() && running_.size() >= 2) {
+    preempt(running_.back());
+    std::fill(promised.begin(), promised.end(), 0);
+    budget = budget_;
+    stalled_before = stalled;
+    portions();
   }
 
   // 3. admit waiting requests into what is left
   if (preempted_.empty()) {
+    // what the prompts that are under way will still ask for after this step
+    std::vector<int> later(cache_->n_groups(), 0);
+    bool prompt_under_way = false;
+    for (Request* r : running_) {
+      int64_t count = 0;
+      for (const Entry& e : entries_)
+        if (e.request == r) count = e.count;
+      if (r->computed + count < r->prompt_len + r->output_len) {
+        prompt_under_way = true;
+        add_later_need(r, count, later);
+      }
+    }
     int slots_left = cache_->free_slots();
     while (!waiting_.empty() && budget > 0 && (int)entries_.size() < max_batch_ && (int)running_.size() < max_active() &&
            slots_left > 0) {
       Request* r = waiting_.front();
+      if (prompt_under_way) {
+        // both have to be able to finish their prompts: else they would fill the pool between
+        // them and neither could go on
+        std::vector<int> whole(later.size());
+        cache_->peak_pages_needed(r->id, r->pending(), r->computed, whole.data());
+        bool room = true;
+        for (size_t g = 0; g < whole.size(); ++g)
+          if (promised[g] + later[g] + whole[g] > cache_->pool((int)g).free_pages()) room = false;
+        if (!room) break;
+      }
       const size_t before = entries_.size();
       plan_portion(r, promised, budget);
       if (entries_.size() == before) break;          // no page for even one token: wait
@@ -298,6 +342,11 @@ int Scheduler::plan() {
       ++admitted;
       --slots_left;
       budget = budget_ - planned_tokens();
+      const int64_t count = entries_.back().count;
+      if (r->computed + count < r->prompt_len + r->output_len) {
+        prompt_under_way = true;
+        add_later_need(r, count, later);
+      }
     }
   }
   // the plan is taken as carried out: its tokens count as computed, its samples as in flight

@@ -126,6 +126,46 @@ def test_a_decode_that_cannot_get_a_page_preempts_the_youngest_request():
     assert all(p.free == p.total for p in mgr.pools)
 
 
+def test_two_prompts_that_fit_only_one_at_a_time_both_finish():
+    """Two 96-token prompts, each of which fits the pool alone, cut into 16-token portions: the
+    second is not admitted while the first is in its prompt (both would fill the pool and neither
+    could go on); every request still finishes and nothing leaks."""
+    mgr, s = make(pages=(32, 32), page=4, max_batched_tokens=64, max_batch_size=4, max_prefill_portion=16)
+    a, b = req("a", 96, max_tokens=3), req("b", 96, max_tokens=3)
+    s.add(a); s.add(b)
+    p1, _ = run_step(mgr, s)
+    assert [(e.request.request_id, len(e.tokens)) for e in p1.entries] == [("a", 16)]
+    steps = 1
+    while s.has_work():
+        plan, _ = run_step(mgr, s)
+        assert plan.entries or plan.preempted, "the scheduler stalled"
+        steps += 1
+        assert steps < 200
+    assert a.status == FINISHED and b.status == FINISHED and len(a.output) == 3 and len(b.output) == 3
+    assert all(p.free == p.total for p in mgr.pools) and not mgr.requests
+
+
+def test_when_every_running_request_waits_for_a_page_the_youngest_is_preempted():
+    """Both requests are in their prompts and hold the whole pool between them (pages taken by
+    another user of the cache made the admission's estimate too kind): no step could run and no
+    later step would free a page, so the youngest goes back to the queue and the older one moves."""
+    mgr, s = make(pages=(32, 32), page=4, max_batched_tokens=64, max_batch_size=4, max_prefill_portion=16)
+    a, b = req("a", 60, max_tokens=2), req("b", 60, max_tokens=2)
+    s.add(a); s.add(b)
+    run_step(mgr, s)                                   # a 16, and b 16: both fit to the end (15 + 15 pages)
+    assert [r.request_id for r in s.running] == ["a", "b"]
+    mgr.open("guest"); mgr.reserve("guest", 4 * 24)     # someone else takes 24 pages of each group
+    plan, _ = run_step(mgr, s)                         # nothing is free: b is preempted, a moves on
+    assert [r.request_id for r in plan.preempted] == ["b"] and b.preemptions == 1
+    assert [(e.request.request_id, len(e.tokens)) for e in plan.entries] == [("a", 16)]
+    mgr.close("guest")
+    while s.has_work():
+        plan, _ = run_step(mgr, s)
+        assert plan.entries or plan.preempted
+    assert a.status == FINISHED and b.status == FINISHED and len(b.output) == 2
+    assert all(p.free == p.total for p in mgr.pools) and not mgr.requests
+
+
 def test_seeded_generators_survive_preemption():
     r = req("x", 3, temperature=1.0, seed=42)
     first = [r.rng.next_f32() for _ in range(3)]
@@ -234,3 +274,39 @@ def test_a_plan_made_ahead_marks_the_token_in_flight_and_a_third_plan_is_refused
     done = s.commit(p3, {"a": 42})
     assert [r.request_id for r in done] == ["a"] and done[0].output == [40, 41, 42] and done[0].finish_reason == "length"
     assert not s.has_work()
+
+
+def test_abort_of_waiting_running_and_in_flight_requests():
+    """abort() between steps: a waiting request never runs; a running one gives its pages and its
+    slot back at once; one that has an entry in a plan made ahead leaves that entry void (it runs,
+    nobody reads it); an unknown id is refused. The others go on to their ends."""
+    mgr, s = make(pages=(64, 64), page=4, slots=3, max_batched_tokens=64, max_batch_size=3, max_active_requests=3)
+    reqs = {n: req(n, 9, max_tokens=6) for n in "abcd"}
+    for r in reqs.values():
+        s.add(r)
+    run_step(mgr, s)                                   # a, b, c are prefilled; d waits for a slot
+    assert [r.request_id for r in s.waiting] == ["d"]
+    assert s.abort("d") is reqs["d"] and reqs["d"].finish_reason == "aborted" and not s.waiting
+    assert s.abort("nobody") is None and s.abort("d") is None
+    used = mgr.pools[0].total - mgr.pools[0].free
+    assert s.abort("b") is reqs["b"] and not mgr.is_open("b")
+    assert mgr.pools[0].total - mgr.pools[0].free == used - 3 and mgr.free_slots == 1
+    mgr.check_invariants()
+    # a plan made ahead holds an entry of c; c is aborted before that plan is committed
+    p1 = s.plan()
+    for e in p1.entries:
+        mgr.reserve(e.request.request_id, len(e.tokens)); mgr.commit(e.request.request_id, len(e.tokens))
+    p2 = s.plan()
+    assert sorted(e.request.request_id for e in p2.entries) == ["a", "c"]
+    assert s.abort("c") is reqs["c"] and not mgr.is_open("c")
+    before = len(reqs["c"].output)
+    s.commit(p1, {"a": 5, "c": 5})
+    for e in p2.entries:
+        if mgr.is_open(e.request.request_id):
+            mgr.reserve(e.request.request_id, len(e.tokens)); mgr.commit(e.request.request_id, len(e.tokens))
+    s.commit(p2, {"a": 6, "c": 6})
+    assert len(reqs["c"].output) == before and reqs["c"].status == FINISHED
+    while s.has_work():
+        run_step(mgr, s)
+    assert reqs["a"].finish_reason == "length" and len(reqs["a"].output) == 6
+    assert all(p.free == p.total for p in mgr.pools) and mgr.free_slots == 3 and not mgr.requests
