@@ -376,6 +376,13 @@ extern "C" long long hb_attention_decode_static_need(int n_tokens, int nh, int h
   return (long long)n_tokens * nh * max_splits * ((long long)hd + 2);
 }
 
+extern "C" int hb_attention_decode_static_fits(int n_tokens, int nh, int hd, int max_splits) {
+  if (n_tokens < 0 || nh <= 0 || hd <= 0 || max_splits < 1) return 0;
+  if (max_splits == 1) return 1;
+  const long long rows = (long long)n_tokens * nh * max_splits;
+  return rows * hd <= HB_STATIC_SCRATCH_ACC_FLOATS && rows * 2 <= HB_STATIC_SCRATCH_ML_FLOATS ? 1 : 0;
+}
+
 extern "C" int hb_attention_decode_static(const void* q, const void* k_pages, const void* v_pages,
                                           const int* block_table, int table_stride, const int* seq_of_token,
                                           const int* positions, void* out, int n_tokens, int nh, int nkv, int hd,
@@ -386,7 +393,7 @@ extern "C" int hb_attention_decode_static(const void* q, const void* k_pages, co
   if (max_splits > 1) {
     const long long acc_need = (long long)n_tokens * nh * max_splits * hd;
     const long long ml_need = (long long)n_tokens * nh * max_splits * 2;
-    if (acc_need > HB_STATIC_SCRATCH_ACC_FLOATS || ml_need > HB_STATIC_SCRATCH_ML_FLOATS) {
+    if (!hb_attention_decode_static_fits(n_tokens, nh, hd, max_splits)) {
       fprintf(stderr,
               "hb_attention_decode_static: %d tokens x %d heads x %d splits x head_dim %d need %lld + %lld floats of "
               "scratch; the built-in array holds %d + %d. Use fewer splits or hb_attention_decode.\n",

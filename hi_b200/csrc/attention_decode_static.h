@@ -14,10 +14,14 @@
 //
 // Limits and rules:
 //   * The scratch holds HB_STATIC_SCRATCH_FLOATS floats (8 MiB + 256 KiB; every GPU that loads
-//     the library holds that much until the process exits). A call needs
-//         n_tokens * nh * max_splits * (hd + 2)   floats
-//     and is refused with HB_ERR_SCRATCH_CAPACITY (and a line on stderr) if that is more; use
-//     fewer splits, or the allocating entry point.
+//     the library holds that much until the process exits), in two parts that are checked
+//     each on its own: the splits' partial outputs need
+//         n_tokens * nh * max_splits * hd   <= HB_STATIC_SCRATCH_ACC_FLOATS   floats
+//     and their running maxima and sums
+//         n_tokens * nh * max_splits * 2    <= HB_STATIC_SCRATCH_ML_FLOATS    floats.
+//     A call that breaks either bound is refused with HB_ERR_SCRATCH_CAPACITY (and a line on
+//     stderr); use fewer splits, or the allocating entry point.
+//     hb_attention_decode_static_fits() answers the question up front.
 //   * All calls share the one array and it keeps what the last call left. Nothing in it needs
 //     to start at zero: every row a call reads back it has written itself, and rows it did not
 //     write (splits past a token's range) carry weight zero in the merge and are skipped.
@@ -48,8 +52,13 @@ int hb_attention_decode_static(const void* q, const void* k_pages, const void* v
                                int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
                                float scale, int split_size, int max_splits, cudaStream_t stream);
 
-// Floats of scratch a call with these sizes needs (to check against HB_STATIC_SCRATCH_* up front).
+// Floats of scratch a call with these sizes needs, both parts together (a total within
+// HB_STATIC_SCRATCH_FLOATS does not yet mean that each part fits: ask the function below).
 long long hb_attention_decode_static_need(int n_tokens, int nh, int hd, int max_splits);
+
+// 1 if a call with these sizes fits the built-in scratch (each of the two parts within its own
+// bound), 0 if it would be refused with HB_ERR_SCRATCH_CAPACITY.
+int hb_attention_decode_static_fits(int n_tokens, int nh, int hd, int max_splits);
 
 #ifdef __cplusplus
 }

@@ -149,7 +149,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           *reinterpret_cast<uint4*>(vt + (rest / 8) * HALF_BYTES + r * 128 + (rest % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
-    __syncthreads();                               // q rows and zeroed rows are visible to every warp
+    // q rows and zeroed rows are visible to every warp; and the block agrees on whether the tile
+    // arrived (a wait that ran out in some threads only must not split the block at a barrier)
+    ok = __syncthreads_and(ok);
     if (!ok) break;
     if (tile == 0) {
 #pragma unroll

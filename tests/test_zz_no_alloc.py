@@ -25,6 +25,8 @@ def library():
     fn.restype = c_int
     lib.hb_attention_decode_static_need.argtypes = [c_int] * 4
     lib.hb_attention_decode_static_need.restype = c_longlong
+    lib.hb_attention_decode_static_fits.argtypes = [c_int] * 4
+    lib.hb_attention_decode_static_fits.restype = c_int
     return lib
 
 
@@ -84,6 +86,13 @@ def test_static_entry_point_refuses_what_its_scratch_cannot_hold():
     q, kp, vp, bt, sot, pos = case(9, 2, 40, 8, 128, 64, [200, 100])
     # 2 tokens x 40 heads x 400 splits x 128 dims is more than the built-in array holds
     rc, _ = call_static(lib, q, kp, vp, bt, sot, pos, 0, 0, 128 ** -0.5, 64, 400)
+    assert rc == HB_ERR_SCRATCH_CAPACITY
+    # each part of the scratch has its own bound: 2 x 40 x 205 rows of 128 floats are 2,048 floats more than
+    # the part for partial outputs holds, although both parts together would have room for them
+    assert lib.hb_attention_decode_static_fits(2, 40, 128, 204) == 1
+    assert lib.hb_attention_decode_static_fits(2, 40, 128, 205) == 0
+    assert lib.hb_attention_decode_static_need(2, 40, 128, 205) <= (1 << 21) + (1 << 16)
+    rc, _ = call_static(lib, q, kp, vp, bt, sot, pos, 0, 0, 128 ** -0.5, 64, 205)
     assert rc == HB_ERR_SCRATCH_CAPACITY
     # one split needs no scratch at all
     rc, got = call_static(lib, q, kp, vp, bt, sot, pos, 0, 0, 128 ** -0.5, 256, 1)
