@@ -80,6 +80,10 @@ int hb_ranked_rows(const float* logits, int rows, int vocab, const float* temper
 int hb_argmax_rows(const float* logits, int rows, int vocab, int parts, float* part_val, int* part_idx, int* counters,
                    int* out, cudaStream_t stream);
 
+// seeded random weights: out[i] = value of element first + i of the tensor with `key` (random_fill.cu)
+int hb_random_normal(void* out, int dtype, long long n, long long first, unsigned long long key, float scale,
+                     cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

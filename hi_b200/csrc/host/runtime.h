@@ -122,6 +122,10 @@ int hbh_sched_queue(void* sched, int which, int64_t* out, int cap);    // 0 wait
 int64_t hbh_sched_counter(void* sched, int what);
 void hbh_sched_forget(void* sched, int64_t request);           // drop the record of a finished request
 
+// ---- seeded random weights (the same bits as the device kernel hb_random_normal)
+// out[i] = value of element first + i of the tensor with `key`, i < n; scale = std / (sigma * 2^24)
+int hbh_random_normal(float* out, int64_t n, int64_t first, uint64_t key, float scale);
+
 #ifdef __cplusplus
 }
 #endif

@@ -96,6 +96,7 @@ _SIGNATURES = {
     "hbh_sched_plan": (I, [P, P, P, I, P, P, I, P, P, I, P]), "hbh_sched_commit": (I, [P, L, P, I, P, I, P]),
     "hbh_sched_request_stat": (L, [P, L, I]), "hbh_sched_queue": (I, [P, I, P, I]), "hbh_sched_counter": (L, [P, I]),
     "hbh_sched_forget": (None, [P, L]),
+    "hbh_random_normal": (I, [P, L, L, ctypes.c_uint64, ctypes.c_float]),
 }
 
 # the C interface's codes (hi_b200/csrc/host/runtime.h)

@@ -7,7 +7,7 @@ on a CUDA device, or a library that cannot be built, raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional, Tuple
 
 import torch
@@ -40,6 +40,7 @@ _SIGNATURES = {
     "hb_argmax_rows": [P, I, I, I, P, P, P, P, P],
     "hb_ranked_rows": [P, I, I, P, P, P, P, P, P],
     "hb_sample_rows": [P, I, I, P, P, P, P],
+    "hb_random_normal": [P, I, c_longlong, c_longlong, c_uint64, F, P],
 }
 
 _UNSUPPORTED = 1002
@@ -192,6 +193,16 @@ def moe_combine(y: torch.Tensor, slot_of_entry: torch.Tensor, shared: Optional[t
     out = torch.empty((n, hidden), dtype=torch.float32, device=y.device)
     _check(lib().hb_moe_combine(_ptr(y), _ptr(slot_of_entry), _ptr(shared), _dt(shared) if shared is not None else 0,
                                 _ptr(out), n, hidden, top_k, _stream()), "moe_combine")
+    return out
+
+
+def random_normal(out: torch.Tensor, key: int, scale: float, first: int = 0) -> torch.Tensor:
+    """Fill ``out`` (float32 or bfloat16, contiguous) with the seeded values of elements
+    ``first ..`` of the tensor with ``key``; ``scale`` = std / (sigma * 2**24) as float32
+    (``hi_b200/weights/random_values.py`` computes the same bits on the host)."""
+    _need(out, "out")
+    _check(lib().hb_random_normal(_ptr(out), _dt(out), out.numel(), int(first), int(key), float(scale), _stream()),
+           "random_normal")
     return out
 
 
@@ -559,18 +570,24 @@ class PendingStatus:
         self.host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self.event = torch.cuda.Event()
         self.device = device
+        self.pending = False
+        self.claimed = False         # someone other than the engine has taken it and will resolve it
 
     def enqueue(self) -> None:
         self.host.copy_(_tc_status(self.device), non_blocking=True)
         self.event.record()
+        self.pending = True
 
     def resolve(self, wait: bool = True) -> bool:
         """Read the copied word; raises if a kernel reported a failed wait. With ``wait=False`` it
         returns False, without blocking, while the copy has not run yet (the word on the device
         stays set until it is read, so a later look still sees it)."""
+        if not self.pending:
+            return True
         if not wait and not self.event.query():
             return False
         self.event.synchronize()
+        self.pending = False
         if int(self.host[0]) != 0:
             check_tc_status()          # raises with the reason, and clears the word
         return True

@@ -8,13 +8,13 @@ crates/hi-mlx/src/models.rs:10723, crates/hi-mlx/src/weights.rs:94-103).
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
 from typing import Callable, Dict, List, Optional
 
 import torch
 
+from . import random_values
 from .safetensors_io import Checkpoint, SafetensorsError, write_safetensors
 
 
@@ -45,6 +45,14 @@ def check_names(specs, available: Dict[str, tuple], where: str) -> None:
         raise WeightError("\n".join(lines), missing, unexpected, wrong)
 
 
+class DerivedTensor:
+    """A tensor the parts ask for that the checkpoint holds in another layout: ``make`` builds it
+    (on the device) from the tensors named ``sources``, which count as used."""
+
+    def __init__(self, sources, shape, make):
+        self.sources, self.shape, self.make = list(sources), tuple(shape), make
+
+
 def _to_engine(t: torch.Tensor, engine_dtype: torch.dtype, device) -> torch.Tensor:
     if t.dtype in (torch.int8, torch.int16, torch.int32, torch.int64, torch.uint8, torch.bool):
         return t.to(device=device, dtype=torch.int32)
@@ -57,8 +65,10 @@ def _to_engine(t: torch.Tensor, engine_dtype: torch.dtype, device) -> torch.Tens
     return t.to(device=device)        # BF16 stays bfloat16, F32 stays float32
 
 
-def load_from_dir(model, model_dir: str, normalize: Callable[[str], Optional[str]]) -> None:
-    """Fill ``model`` (a :class:`hi_b200.parts.model.Model`) from the safetensors of ``model_dir``."""
+def load_from_dir(model, model_dir: str, normalize: Callable[[str], Optional[str]], derive=None) -> None:
+    """Fill ``model`` (a :class:`hi_b200.parts.model.Model`) from the safetensors of ``model_dir``.
+    ``derive({name: shape}) -> {name: DerivedTensor}``: tensors to be made from others the
+    checkpoint stores in another layout."""
     try:
         ckpt = Checkpoint(model_dir)
     except SafetensorsError as e:
@@ -79,9 +89,17 @@ def load_from_dir(model, model_dir: str, normalize: Callable[[str], Optional[str
                        if ckpt.describe(o)[0] not in ("F32", "BF16", "F16", "F64", "I32", "I64", "I16", "I8", "U8"))
     if bad_dtype:
         raise WeightError(f"{model_dir}: quantized or packed tensors are not supported: " + ", ".join(bad_dtype))
+    derived: Dict[str, DerivedTensor] = derive(dict(shapes)) if derive is not None else {}
+    for name, d in derived.items():
+        shapes[name] = d.shape
+        for src in d.sources:
+            shapes.pop(src, None)
     check_names(model.tensor_specs(), shapes, model_dir)
 
     def fetch(name: str):
+        if name in derived:
+            d = derived[name]
+            return d.make([_to_engine(ckpt.tensor(by_part_name[src]), model.dtype, model.device) for src in d.sources])
         original = by_part_name.get(name)
         if original is None:
             return None
@@ -91,29 +109,29 @@ def load_from_dir(model, model_dir: str, normalize: Callable[[str], Optional[str
 
 
 # --------------------------------------------------------------------------- random weights
-def _tensor_seed(seed: int, name: str) -> int:
-    digest = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF
-
-
 def random_tensor(spec, seed: int, std: float, device="cpu", dtype=torch.bfloat16) -> torch.Tensor:
-    """The seeded value of one tensor: N(0, std) or ones/zeros, keyed by (seed, name)."""
+    """The seeded value of one tensor: N(0, std) or ones/zeros, keyed by (seed, name, element
+    index). The numbers come from a counter-based generator in integer arithmetic
+    (:mod:`hi_b200.weights.random_values`), so a tensor made on the host and the same tensor made
+    on the device by ``hb_random_normal`` hold the same bits."""
     if spec.dtype == "int32":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     if spec.init == "ones":
         return torch.ones(spec.shape, dtype=dtype, device=device)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=dtype, device=device)
-    gen = torch.Generator(device=device)
-    gen.manual_seed(_tensor_seed(seed, spec.name))
-    out = torch.empty(spec.shape, dtype=dtype, device=device)
-    # generated in slices so a large tensor never needs a float32 copy of itself
-    flat = out.view(-1)
-    step = 1 << 26
-    for begin in range(0, flat.numel(), step):
-        end = min(begin + step, flat.numel())
-        flat[begin:end] = (torch.randn(end - begin, generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
-    return out
+    key = random_values.tensor_key(seed, spec.name)
+    if torch.device(device).type == "cuda":
+        from ..kernels import ops
+
+        out = torch.empty(spec.shape, dtype=dtype, device=device)
+        ops.random_normal(out, key, float(random_values.scale_for(std)))
+        return out
+    n = 1
+    for d in spec.shape:
+        n *= int(d)
+    values = torch.from_numpy(random_values.normal_values(key, 0, n, std))
+    return values.view(tuple(spec.shape)).to(dtype)
 
 
 def load_random(model, seed: int, std: float = 0.02) -> None:

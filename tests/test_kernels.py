@@ -531,3 +531,22 @@ def test_kernels_refuse_what_they_cannot_do():
         o.paged_attention(q, pages, pages, bt, z, z, 0, 0, 1.0)                     # head_dim 24
     with pytest.raises(KernelError):
         o.router_topk(torch.zeros(2, 8, device=DEV), torch.zeros(3, 8, device=DEV), 4)   # k > experts
+
+
+def test_random_fill_has_the_hosts_bits():
+    """hb_random_normal against the same arithmetic written out in numpy (and the host runtime's
+    C++): float32 and bfloat16, sizes that are no multiple of anything, an offset into the tensor,
+    indices past 2^32."""
+    import numpy as np
+
+    from hi_b200.weights import random_values as rv
+
+    o = ops()
+    for n, first, std, seed in ((1, 0, 0.02, 0), (1023, 0, 0.02, 1), (70001, 7, 0.08, 2), (4096, (1 << 33) + 5, 1.0, 3)):
+        key = rv.tensor_key(seed, f"t{n}")
+        want = rv.normal_values_numpy(key, first, n, std)
+        assert (rv.normal_values(key, first, n, std).view(np.uint32) == want.view(np.uint32)).all()
+        got32 = o.random_normal(torch.empty(n, dtype=torch.float32, device=DEV), key, float(rv.scale_for(std)), first)
+        assert (got32.cpu().numpy().view(np.uint32) == want.view(np.uint32)).all(), f"float32, n {n}"
+        got16 = o.random_normal(torch.empty(n, dtype=torch.bfloat16, device=DEV), key, float(rv.scale_for(std)), first)
+        assert torch.equal(got16.cpu(), torch.from_numpy(want).to(torch.bfloat16)), f"bfloat16, n {n}"

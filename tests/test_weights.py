@@ -131,3 +131,81 @@ def test_sharded_checkpoint_with_index(tmp_path):
     arch, model = fake_model(TINY_A)
     load_from_dir(model, str(sharded), arch.normalize_tensor_name)
     assert torch.equal(model.embedding.table, ck.tensor("model.embed_tokens.weight"))
+
+
+def test_random_values_are_the_written_out_definition_and_look_normal():
+    """The host runtime's generator against the same arithmetic written out in numpy; values are
+    a function of (seed, name, element index) alone; their moments are a normal distribution's."""
+    import numpy as np
+
+    from hi_b200.weights import random_values as rv
+
+    key = rv.tensor_key(7, "model.layers.0.self_attn.q_proj.weight")
+    a = rv.normal_values(key, 0, 70001, 0.02)
+    b = rv.normal_values_numpy(key, 0, 70001, 0.02)
+    assert a.dtype == np.float32 and (a.view(np.uint32) == b.view(np.uint32)).all()
+    assert (rv.normal_values(key, 12345, 100, 0.02) == a[12345:12445]).all(), "a value depends on more than its index"
+    assert rv.tensor_key(7, "x") != rv.tensor_key(8, "x") != rv.tensor_key(8, "y")
+    other = rv.normal_values(rv.tensor_key(8, "model.layers.0.self_attn.q_proj.weight"), 0, 70001, 0.02)
+    assert abs(float(np.corrcoef(a, other)[0, 1])) < 0.02
+    big = rv.normal_values(key, 0, 2_000_000, 1.0).astype(np.float64)
+    assert abs(big.mean()) < 3e-3 and abs(big.std() - 1.0) < 3e-3
+    assert abs((big ** 3).mean()) < 1e-2 and abs((big ** 4).mean() - 3.0) < 3e-2
+    assert 4.0 < np.abs(big).max() < 16.1
+    # consecutive elements are not correlated
+    assert abs(float(np.corrcoef(big[:-1], big[1:])[0, 1])) < 3e-3
+
+
+def test_random_model_is_a_function_of_the_seed(tmp_path):
+    d1 = write_random_model(TINY_A, str(tmp_path / "a"), seed=5, std=0.02)
+    d2 = write_random_model(TINY_A, str(tmp_path / "b"), seed=5, std=0.02)
+    d3 = write_random_model(TINY_A, str(tmp_path / "c"), seed=6, std=0.02)
+    c1, c2, c3 = Checkpoint(d1), Checkpoint(d2), Checkpoint(d3)
+    name = "model.layers.1.feed_forward.experts.up_proj.weight"
+    assert torch.equal(c1.tensor(name), c2.tensor(name)) and not torch.equal(c1.tensor(name), c3.tensor(name))
+    assert torch.equal(c1.tensor("model.norm.weight"), torch.ones(64, dtype=torch.bfloat16))
+    assert abs(float(c1.tensor(name).float().std()) - 0.02) < 1e-3
+
+
+def test_fused_expert_layout_and_biases_by_presence(tmp_path):
+    """The routed experts stored as one fused, input-major tensor per layer without a ``.weight``
+    suffix (``experts.gate_up_proj`` [E, H, 2I], ``experts.down_proj`` [E, I, H]) load into the same
+    weights as the converted layout; q/k/v/o biases are used iff their tensors exist; a fused
+    tensor of the wrong shape is reported by the name the model asks for."""
+    d = write_random_model(TINY_A, str(tmp_path / "m"), seed=9)
+    ck = Checkpoint(d)
+    tensors = {n: ck.tensor(n).clone() for n in ck.names()}
+    fused = {}
+    for n, t in tensors.items():
+        if n.endswith("experts.gate_proj.weight"):
+            up = tensors[n.replace("gate_proj", "up_proj")]
+            fused[n.replace("gate_proj.weight", "gate_up_proj")] = torch.cat([t, up], dim=1).transpose(1, 2).contiguous()
+        elif n.endswith("experts.up_proj.weight"):
+            continue
+        elif n.endswith("experts.down_proj.weight"):
+            fused[n[: -len(".weight")]] = t.transpose(1, 2).contiguous()
+        else:
+            fused[n] = t
+    fused["model.layers.0.self_attn.k_proj.bias"] = torch.full((2 * 16,), 0.5, dtype=torch.bfloat16)
+    out = tmp_path / "fused"
+    os.makedirs(out)
+    write_safetensors(str(out / "model.safetensors"), fused)
+    json.dump(TINY_A, open(out / "config.json", "w"))
+    arch, plain_model = fake_model(TINY_A)
+    load_from_dir(plain_model, d, arch.normalize_tensor_name, arch.derive_tensors)
+    arch, model = fake_model(TINY_A)
+    load_from_dir(model, str(out), arch.normalize_tensor_name, arch.derive_tensors)
+    for a, b in zip(plain_model.layers, model.layers):
+        for w in ("w_gate", "w_up", "w_down"):
+            assert torch.equal(getattr(a.feed_forward, w), getattr(b.feed_forward, w)), w
+    assert plain_model.layers[0].mixer.b_qkv is None and model.layers[1].mixer.b_qkv is None
+    b_qkv = model.layers[0].mixer.b_qkv
+    assert b_qkv.shape == ((4 + 2 + 2) * 16,) and float(b_qkv[: 4 * 16].abs().max()) == 0.0
+    assert torch.equal(b_qkv[4 * 16: 6 * 16], torch.full((32,), 0.5, dtype=torch.bfloat16))
+    # a fused tensor of the wrong width
+    fused["model.layers.0.feed_forward.experts.down_proj"] = torch.zeros(4, 100, 64, dtype=torch.bfloat16)
+    write_safetensors(str(out / "model.safetensors"), fused)
+    arch, model = fake_model(TINY_A)
+    with pytest.raises(WeightError) as e:
+        load_from_dir(model, str(out), arch.normalize_tensor_name, arch.derive_tensors)
+    assert e.value.wrong_shape and e.value.wrong_shape[0][0] == "model.layers.0.feed_forward.experts.down_proj.weight"
