@@ -1,4 +1,5 @@
-"""hi_b200: a small, whole Llama 4 text-decoder inference engine for one B200 GPU."""
+"""hi_b200: a small, whole decoder inference engine for one B200 GPU; the architecture it brings
+is the Llama 4 text decoder (``hi_b200/architectures.py``)."""
 from .engine import LLM, Engine, GenerationOutput, StepEntry, generate
 from .sampling import SamplingParams
 

@@ -4,6 +4,7 @@
     python -m hi_b200 run MODEL_PATH --tokens "1,2,3" [--max-tokens N] [--top-k 5] [--temperature T]
                           [--top-p P] [--seed S] [--include-logits] [--dtype bfloat16|float32]
                           [--max-batch-size 8] [--max-batched-tokens 8192] [--kv-page-size 64]
+                          [--random-weights [--weights-seed S] [--weights-std 0.02]]
     python -m hi_b200 random-weights CONFIG_JSON OUT_DIR [--seed S] [--std 0.02]
 
 ``run`` is the counterpart of ``hi-local qwen-cpu``: token ids in, pretty JSON out with the same
@@ -29,7 +30,7 @@ def parse_token_ids(value: str) -> List[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="hi_b200", description="Llama 4 text-decoder inference on one B200")
+    p = argparse.ArgumentParser(prog="hi_b200", description="decoder inference on one B200; the model class is chosen by config.json")
     sub = p.add_subparsers(dest="command", required=True)
     i = sub.add_parser("inspect", help="inspect a model folder")
     i.add_argument("model_path")
@@ -48,6 +49,10 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--max-active-requests", type=int, default=None)
     r.add_argument("--max-batched-tokens", type=int, default=8192)
     r.add_argument("--kv-page-size", type=int, default=64)
+    r.add_argument("--random-weights", action="store_true",
+                   help="MODEL_PATH is a config.json (or a folder with one); weights are seeded random numbers")
+    r.add_argument("--weights-seed", type=int, default=0)
+    r.add_argument("--weights-std", type=float, default=0.02)
     w = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
     w.add_argument("config_json")
     w.add_argument("out_dir")
@@ -86,6 +91,11 @@ def cmd_inspect(args) -> int:
             m = arch.normalize_tensor_name(n)
             if m is not None:
                 names[m] = ckpt.describe(n)[1]
+        if arch.derive_tensors is not None:          # tensors stored in another layout of the same weights
+            for name, d in arch.derive_tensors(dict(names)).items():
+                names[name] = d.shape
+                for src in d.sources:
+                    names.pop(src, None)
         check_names(specs, names, args.model_path)
         report["tensors"] = {"count": len(names), "status": "ok"}
     except (WeightError, ValueError) as e:
@@ -105,30 +115,44 @@ def cmd_run(args) -> int:
 
     from .engine.core import StepEntry
     from .engine.generate import LLM
+    from .kernels import ops
     from .sampling.sampler import SamplingParams
 
-    llm = LLM(args.model_path, dtype=args.dtype, max_batch_size=args.max_batch_size,
+    model = args.model_path
+    if args.random_weights:
+        # MODEL_PATH names a config.json (or a folder with one): weights are generated on the device
+        import os
+
+        path = os.path.join(model, "config.json") if os.path.isdir(model) else model
+        with open(path) as f:
+            model = json.load(f)
+    llm = LLM(model, random_seed=args.weights_seed, random_std=args.weights_std, dtype=args.dtype, max_batch_size=args.max_batch_size,
               max_active_requests=args.max_active_requests, max_batched_tokens=args.max_batched_tokens,
               kv_page_size=args.kv_page_size,
               kv_cache_tokens=max(args.max_batched_tokens, len(tokens) + args.max_tokens + args.kv_page_size))
     logits = llm.engine.step([StepEntry("inspect", tokens, [len(tokens) - 1])])[0]
     llm.engine.finish("inspect")
-    top = torch.topk(logits, min(args.top_k, logits.numel())) if args.top_k > 0 else None
-    host = logits.cpu()
-    order = sorted(range(host.numel()), key=lambda i: (-float(host[i]), i))[:max(args.top_k, 0)]
+    next_token = int(ops.sample_rows(logits[None].contiguous(), None, None)[0])     # the lowest id on ties
+    # the largest logits, ties by id: everything not below the k-th value is ranked on the host
+    k = min(max(args.top_k, 0), logits.numel())
+    top = []
+    if k > 0:
+        kth = torch.topk(logits, k).values[-1]
+        ids = (logits >= kth).nonzero().flatten()
+        top = sorted(zip(ids.tolist(), logits[ids].tolist()), key=lambda p: (-p[1], p[0]))[:k]
     generated: List[int] = []
     if args.max_tokens > 0:
         out = llm.generate([tokens], SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature,
                                                     top_p=args.top_p, seed=args.seed))[0]
         generated = out.token_ids
     result = {
-        "backend": f"hi_b200-cuda-{args.dtype}", "input_tokens": tokens, "next_token": order[0] if order else int(host.argmax()),
+        "backend": f"hi_b200-cuda-{args.dtype}", "input_tokens": tokens, "next_token": next_token,
         "next_text": "", "generated_tokens": generated, "generated_text": "",
-        "top_logits": [{"token_id": i, "token": None, "logit": float(host[i])} for i in order],
-        "logit_count": host.numel(),
+        "top_logits": [{"token_id": i, "token": None, "logit": v} for i, v in top],
+        "logit_count": logits.numel(),
     }
     if args.include_logits:
-        result["logits"] = [float(v) for v in host]
+        result["logits"] = logits.cpu().tolist()
     print(json.dumps(result, indent=2))
     return 0
 

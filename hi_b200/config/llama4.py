@@ -13,14 +13,10 @@ architecture needs them; the reference hard-wires NoPE to every 4th layer
 """
 from __future__ import annotations
 
-import json
-import os
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, Optional, Tuple
 
-
-class ConfigError(ValueError):
-    """A config.json that cannot describe a runnable model; the message names the key."""
+from .base import ConfigError, get_key as _get, read_config_files, token_ids as _token_ids
 
 
 @dataclass(frozen=True)
@@ -31,41 +27,6 @@ class RopeScaling:
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
     original_max_position_embeddings: float = 8192.0
-
-
-def _get(raw: Dict[str, Any], key: str, kind, default=None, required=False):
-    if key not in raw or raw[key] is None:
-        if required:
-            raise ConfigError(f"config.json: required key '{key}' is missing")
-        return default
-    value = raw[key]
-    try:
-        if kind is bool:
-            if isinstance(value, (bool, int)):
-                return bool(value)
-            raise TypeError
-        if kind is int:
-            if isinstance(value, bool) or (isinstance(value, float) and value != int(value)):
-                raise TypeError
-            return int(value)
-        if kind is float:
-            if isinstance(value, bool):
-                raise TypeError
-            return float(value)
-    except (TypeError, ValueError):
-        raise ConfigError(f"config.json: key '{key}' has value {value!r}, expected {kind.__name__}")
-    return value
-
-
-def _token_ids(raw: Dict[str, Any], key: str) -> List[int]:
-    value = raw.get(key)
-    if isinstance(value, bool):
-        return []
-    if isinstance(value, int):
-        return [value] if value >= 0 else []
-    if isinstance(value, list):
-        return [int(v) for v in value if isinstance(v, int) and not isinstance(v, bool) and v >= 0]
-    return []
 
 
 @dataclass(frozen=True)
@@ -252,23 +213,3 @@ class Llama4TextConfig:
     @staticmethod
     def from_dir(model_dir: str) -> "Llama4TextConfig":
         return Llama4TextConfig.from_json(*read_config_files(model_dir))
-
-
-def read_config_files(model_dir: str):
-    path = os.path.join(model_dir, "config.json")
-    if not os.path.isfile(path):
-        raise ConfigError(f"{model_dir}: no config.json")
-    try:
-        with open(path, "r", encoding="utf-8") as f:
-            raw = json.load(f)
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"{path}: not valid JSON ({e})")
-    gen = None
-    gpath = os.path.join(model_dir, "generation_config.json")
-    if os.path.isfile(gpath):
-        try:
-            with open(gpath, "r", encoding="utf-8") as f:
-                gen = json.load(f)
-        except json.JSONDecodeError:
-            gen = None
-    return raw, gen

@@ -11,7 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional
 
-from .llama4 import ConfigError, Llama4TextConfig, read_config_files
+from .base import ConfigError, read_config_files
 
 
 @dataclass(frozen=True)
@@ -20,6 +20,9 @@ class Architecture:
     parse_config: Callable[[Dict[str, Any], Optional[Dict[str, Any]]], Any]
     build_spec: Callable[[Any], Any]                       # typed config -> ModelSpec
     normalize_tensor_name: Callable[[str], Optional[str]]  # checkpoint name -> part name, None = not ours
+    # other layouts of the same weights: {normalised name: shape} of the checkpoint -> {part name:
+    # DerivedTensor} for tensors that have to be made from others (split, transposed); optional
+    derive_tensors: Optional[Callable[[Dict[str, tuple]], Dict[str, Any]]] = None
 
 
 _BY_NAME: Dict[str, Architecture] = {}
@@ -31,10 +34,25 @@ def register_architecture(names: List[str], arch: Architecture) -> None:
 
 
 def registered_architectures() -> List[str]:
+    _load_builtin()
     return sorted(_BY_NAME)
 
 
+_builtin_loaded = False
+
+
+def _load_builtin() -> None:
+    """The architectures this package brings register themselves when their module is imported."""
+    global _builtin_loaded
+    if not _builtin_loaded:
+        _builtin_loaded = True
+        import importlib
+
+        importlib.import_module("hi_b200.architectures")
+
+
 def lookup(raw_config: Dict[str, Any]) -> Architecture:
+    _load_builtin()
     archs = raw_config.get("architectures") or []
     if isinstance(archs, str):
         archs = [archs]
@@ -51,14 +69,3 @@ def load_architecture(model_dir: str):
     raw, gen = read_config_files(model_dir)
     arch = lookup(raw)
     return arch, arch.parse_config(raw, gen), raw
-
-
-def _register_builtin() -> None:
-    from ..parts.llama4 import build_llama4_spec, normalize_llama4_tensor_name
-
-    arch = Architecture(name="llama4_text", parse_config=Llama4TextConfig.from_json,
-                        build_spec=build_llama4_spec, normalize_tensor_name=normalize_llama4_tensor_name)
-    register_architecture(["Llama4ForConditionalGeneration", "Llama4ForCausalLM", "llama4", "llama4_text"], arch)
-
-
-_register_builtin()

@@ -4,7 +4,8 @@
 //   temperature  > 0 : weights exp(l/T - max) walked in vocabulary order; the first id whose
 //                      running sum exceeds u * total (kernels.cu:7327-7352). u is drawn by the
 //                      host, one per request per step, so streams do not depend on batching.
-// Ranked sampling (top-k / top-p) is done on the host, as the reference does by default.
+// Ranked sampling (top-k / top-p): ranked_rows_kernel below, by the host sampler's rule and in its
+// order; a row with more candidates than it sorts is handed back to the host.
 #include "api.h"
 #include "common.cuh"
 

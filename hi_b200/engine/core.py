@@ -89,7 +89,8 @@ class Engine:
 
     def __init__(self, model: Model, *, kv_page_size: int = 64, kv_cache_tokens: int = 8192,
                  windowed_cache_tokens: Optional[int] = None, max_active_requests: int = 8,
-                 debug_poison: bool = False, use_cuda_graphs: bool = True):
+                 debug_poison: bool = False, use_cuda_graphs: bool = True, graph_context_bucket: int = 1024,
+                 max_graphs: int = 16):
         _require_cuda(model.device)
         self.model = model
         self.device = model.device
@@ -108,9 +109,17 @@ class Engine:
         self.debug_poison = debug_poison
         self.use_cuda_graphs = use_cuda_graphs and model.graph_safe
         self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
+        if graph_context_bucket < 1 or max_graphs < 1:
+            raise ValueError("graph_context_bucket and max_graphs must be positive")
+        # a captured decode step serves contexts up to a multiple of this many tokens
+        self.context_bucket = -(-int(graph_context_bucket) // self.page_size) * self.page_size
+        self.max_graphs = int(max_graphs)
         self.last_step_h2d_bytes = 0
-        self._status = None            # ops.PendingStatus, made when a captured step uses the tcgen05 kernels
-        self._status_pending = False
+        # captured steps whose kernels wait with a limit: their status word follows them to pinned
+        # memory (four tickets used in turn) and is read later, by whoever uses the step's result
+        self._status_ring: List[ops.PendingStatus] = []
+        self._status_turn = 0
+        self.last_status: Optional[ops.PendingStatus] = None    # the ticket of the step run last (None: checked already)
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -118,7 +127,7 @@ class Engine:
         """Load a model folder (config.json + safetensors); the model class is chosen by config.json."""
         arch, cfg, _raw = load_architecture(model_dir)
         model = Model(arch.build_spec(cfg), parse_dtype(dtype), device)
-        load_from_dir(model, model_dir, arch.normalize_tensor_name)
+        load_from_dir(model, model_dir, arch.normalize_tensor_name, arch.derive_tensors)
         return Engine(model, **options)
 
     @staticmethod
@@ -156,7 +165,8 @@ class Engine:
             done += n
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], tap=None, feedback=None, borrow: bool = False) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], tap=None, feedback=None, borrow: bool = False,
+             forced=None) -> Optional[torch.Tensor]:
         """Run one batch. Returns float32 logits [wanted, vocab] on the device, in the order
         of the entries and of each entry's ``want`` (None if nothing is wanted). ``tap(name,
         tensor)``, if given, is called by parts that report intermediate tensors (router ids),
@@ -203,23 +213,31 @@ class Engine:
                 self.manager.close(rid)
             raise
 
-        graph = self._decode_graph_for(entries) if tap is None else None
+        self.last_status = None
+        graph = self._decode_graph_for(entries, feedback) if forced is None else None
         if graph is not None:
             self._build_context(entries, widths=graph.widths, static=graph, feedback=feedback)
             graph.graph.replay()
             _count_launches(graph.kernels)
+            if tap is not None:                  # what the parts reported at capture sits in the graph's own
+                for name, tensor in graph.taps.items():     # buffers, refilled by every replay
+                    tap(name, tensor)
             if graph.uses_tensor_core_experts:
-                # no sync here: the status word follows the kernels to pinned memory and is read
-                # at the start of the next step (or when the engine is asked for its state)
-                if self._status is None:
-                    self._status = ops.PendingStatus(self.device)
-                self._status.enqueue()
-                self._status_pending = True
+                # no sync here: the status word follows the kernels to pinned memory; a caller that
+                # commits the step's result resolves `last_status` first, and whatever is still
+                # open is read at the start of a later step or when the engine is asked for its state
+                if not self._status_ring:
+                    self._status_ring = [ops.PendingStatus(self.device) for _ in range(4)]
+                ticket = self._status_ring[self._status_turn % len(self._status_ring)]
+                self._status_turn += 1
+                ticket.enqueue()
+                ticket.claimed = False
+                self.last_status = ticket
             logits = graph.logits if borrow else graph.logits.clone()
             ctx, logit_rows = graph.ctx, graph.logit_rows
         else:
             ctx, logit_rows = self._build_context(entries, feedback=feedback)
-            ctx.tap = tap
+            ctx.tap, ctx.forced = tap, forced
             logits = self.model.forward(ctx, self.cache.views, logit_rows)
             _check_kernel_status()
         for e in entries:
@@ -336,20 +354,18 @@ class Engine:
         return ctx, logit_rows
 
     # ------------------------------------------------------------------ captured decode steps
-    CONTEXT_BUCKET = 1024     # a decode graph serves contexts up to a multiple of this
-
-    def _decode_graph_for(self, entries: Sequence[StepEntry]) -> Optional["_DecodeGraph"]:
+    def _decode_graph_for(self, entries: Sequence[StepEntry], feedback=None) -> Optional["_DecodeGraph"]:
         """A CUDA graph of the whole step for batches of single decoded tokens that all want
         their logits: same kernels as the eager step, launched once. Keyed by batch size and the
         context bucket (which fixes the block-table widths and the attention splits)."""
         if not self.use_cuda_graphs or any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
             return None
         longest = max(self.manager.length(e.request_id) for e in entries) + 1
-        bucket = -(-longest // self.CONTEXT_BUCKET) * self.CONTEXT_BUCKET
+        bucket = -(-longest // self.context_bucket) * self.context_bucket
         key = (len(entries), bucket)
         graph = self._graphs.get(key)
         if graph is None:
-            if len(self._graphs) >= 16:
+            if len(self._graphs) >= self.max_graphs:          # the one captured longest ago makes room
                 self._graphs.pop(next(iter(self._graphs)))
             graph = _DecodeGraph(self, len(entries), bucket)
             self._graphs[key] = graph
@@ -357,14 +373,23 @@ class Engine:
             if graph.eager_runs < 1:          # the first step of a shape runs eagerly (library warm-up)
                 graph.eager_runs += 1
                 return None
-            graph.capture(entries)
+            graph.capture(entries, feedback)
         return graph
 
     def _resolve_status(self, wait: bool = True) -> None:
-        """Read the status word that followed a captured step's kernels; without ``wait`` only if
-        its copy has run already (the next look, or ``snapshot``, catches up)."""
-        if self._status_pending and self._status.resolve(wait):
-            self._status_pending = False
+        """Read the status words that followed captured steps' kernels; without ``wait`` only those
+        whose copy has run already (the next look, or ``snapshot``, catches up)."""
+        for ticket in self._status_ring:
+            if ticket.pending and not ticket.claimed:
+                ticket.resolve(wait)
+
+    def take_status(self) -> Optional[ops.PendingStatus]:
+        """The status ticket of the step run last, for a caller that resolves it itself before it
+        uses the step's result (the engine then leaves it alone). None: that step was checked when it ran."""
+        ticket = self.last_status
+        if ticket is not None:
+            ticket.claimed = True
+        return ticket
 
     # ------------------------------------------------------------------ bookkeeping
     def snapshot(self) -> dict:
@@ -408,10 +433,12 @@ class _DecodeGraph:
         self.row_version = np.full(n_seqs, -1, dtype=np.int64)    # into each table row
         self.kernels = 0
         self.uses_tensor_core_experts = False
+        self.taps: Dict[str, torch.Tensor] = {}     # what parts reported while the step was captured
 
-    def capture(self, entries: Sequence[StepEntry]) -> None:
+    def capture(self, entries: Sequence[StepEntry], feedback=None) -> None:
         eng = self.engine
-        eng._build_context(entries, widths=self.widths, static=self)     # valid inputs for the capture run
+        # valid inputs for the capture run: the tokens fed on the device included
+        eng._build_context(entries, widths=self.widths, static=self, feedback=feedback)
         torch.cuda.synchronize()
         stream = torch.cuda.Stream()
         stream.wait_stream(torch.cuda.current_stream())
@@ -422,8 +449,11 @@ class _DecodeGraph:
         before = ops.LAUNCHES[0]
         ops.TC_USED[0] = False
         self.graph = torch.cuda.CUDAGraph()
+        self.taps = {}
+        self.ctx.tap = self.taps.__setitem__
         with torch.cuda.graph(self.graph):
             self.logits = eng.model.forward(self.ctx, eng.cache.views, self.logit_rows)
+        self.ctx.tap = None
         self.kernels = ops.LAUNCHES[0] - before      # this library's kernels in one replay
         self.uses_tensor_core_experts = ops.TC_USED[0]
         ops.TC_USED[0] = False

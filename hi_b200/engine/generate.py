@@ -33,15 +33,25 @@ class _Launched:
     """A step that runs on the GPU while the host goes on: its plan, the requests it samples
     for, and the sampled tokens on the device, on their way to pinned host memory."""
 
-    __slots__ = ("plan", "sampling", "tokens_dev", "tokens_host", "copied", "row_of")
+    __slots__ = ("plan", "sampling", "tokens_dev", "tokens_host", "copied", "row_of", "status")
 
-    def __init__(self, plan, sampling, tokens_dev, host_buffer, copied):
+    def __init__(self, plan, sampling, tokens_dev, host_buffer, copied, status=None):
         self.plan, self.sampling, self.tokens_dev = plan, sampling, tokens_dev
+        self.status = status                 # the step's kernel-status ticket (None: checked when it ran)
         self.row_of = {r.request_id: i for i, r in enumerate(sampling)}
         self.tokens_host = host_buffer[: tokens_dev.numel()]
         self.tokens_host.copy_(tokens_dev, non_blocking=True)
         self.copied = copied
         self.copied.record()
+
+
+class _Unread:
+    """A step that ran but whose samples are read at once: only its plan matters to a later look."""
+
+    __slots__ = ("plan",)
+
+    def __init__(self, plan):
+        self.plan = plan
 
 
 class LLM:
@@ -123,9 +133,28 @@ class LLM:
                     on_token(r.request_id, r.output[-1])
         return done
 
-    def _read(self, launched: _Launched, on_token) -> List[Request]:
-        """The host catches up with a launched step: waits for its sampled tokens and commits them."""
-        launched.copied.synchronize()
+    def _checked(self, status, *plans) -> None:
+        """Before a step's samples are committed: did one of its kernels give up a bounded wait? Then
+        its samples, and those of a step launched on top of them, mean nothing: the requests of
+        ``plans`` are aborted (pages and slots go back), nothing is committed, and the error is raised."""
+        if status is None:
+            return
+        try:
+            status.resolve(wait=True)
+        except Exception:
+            plans = [p for p in plans if p is not None]
+            for plan in plans:
+                for e in plan.entries:
+                    self.scheduler.abort(e.request.request_id)
+            for plan in plans:           # oldest first; every entry is void by now, nothing is appended
+                self.scheduler.commit(plan, {})
+            raise
+
+    def _read(self, launched: _Launched, on_token, later: Optional[_Launched] = None) -> List[Request]:
+        """The host catches up with a launched step: waits for its sampled tokens and commits them.
+        ``later``: the step launched after it, which took its samples on the device."""
+        launched.copied.synchronize()            # the status word was copied before the tokens
+        self._checked(launched.status, launched.plan, later.plan if later is not None else None)
         return self._commit(launched.plan, launched.sampling, launched.tokens_host.tolist(), on_token)
 
     def step(self, on_token: Optional[Callable[[Hashable, int], None]] = None) -> List[Request]:
@@ -142,6 +171,7 @@ class LLM:
         feedback = (previous.tokens_dev, previous.row_of) if previous is not None else None
         # the logits are sampled from (on this stream, or read back) before the next step is launched
         logits = self.engine.step(self._entries(plan), feedback=feedback, borrow=True)
+        status = self.engine.take_status()
         sampling = [e.request for e in plan.entries if e.samples]
         done: List[Request] = []
         launched = None
@@ -149,11 +179,13 @@ class LLM:
             tokens_dev = sample_on_device(logits, [r.params for r in sampling], [r.rng for r in sampling])
             if tokens_dev is not None:
                 self._turn ^= 1
-                launched = _Launched(plan, sampling, tokens_dev, self._token_buffers[self._turn], self._token_events[self._turn])
+                launched = _Launched(plan, sampling, tokens_dev, self._token_buffers[self._turn], self._token_events[self._turn],
+                                     status)
         if previous is not None:                       # the step before: its tokens have had a whole step to arrive
-            done += self._read(previous, on_token)
+            done += self._read(previous, on_token, launched if launched is not None else _Unread(plan))
         if launched is None:                           # read this step's samples now (ranked rows, or no lookahead)
             tokens = sample(logits, [r.params for r in sampling], [r.rng for r in sampling]) if sampling else []
+            self._checked(status, plan)
             done += self._commit(plan, sampling, tokens, on_token)
         self._launched = launched
         return done

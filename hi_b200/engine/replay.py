@@ -7,6 +7,11 @@ crates/hi-local/src/main.rs:60-83, and the captured-batch replay of
 crates/hi-mlx/src/models.rs:11709-11831.)
 
     trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+              [--page-size P] [--num-pages-global G] [--num-pages-chunk K] [--max-live R]
+
+``--max-tokens`` sizes every page pool (rounded up to whole pages); ``--num-pages-global`` and
+``--num-pages-chunk`` size the pool of the layers that keep every key and the pool of the
+windowed layers on their own, so a trace can be driven into the exhaustion of one of them.
 
 Standard input: one JSON object per line,
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
@@ -23,6 +28,7 @@ import sys
 
 PAGE_SIZE = 64
 MAX_LIVE_REQUESTS = 8
+PAGE_SIZES = (8, 16, 32, 64, 128)      # the reference's page sizes and one larger (crates/hi-cuda/src/lib.rs:634-636)
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -33,6 +39,12 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens live requests hold at any time (each rounded up to the page size)")
     p.add_argument("--device", default="cuda:0")
+    p.add_argument("--page-size", type=int, default=PAGE_SIZE, choices=PAGE_SIZES, help="tokens per cache page")
+    p.add_argument("--num-pages-global", type=int, default=None,
+                   help="pages of the pool of layers that keep every key (default: --max-tokens in pages)")
+    p.add_argument("--num-pages-chunk", type=int, default=None,
+                   help="pages of the pool of windowed layers (default: --max-tokens in pages)")
+    p.add_argument("--max-live", type=int, default=MAX_LIVE_REQUESTS, help="requests that may be live at a time")
     p.add_argument("--dump-taps", action="store_true",
                    help="debug: also write <step>.taps.json with the integer tensors parts report "
                         "(the router's expert choices, in the step's flat token order)")
@@ -47,9 +59,15 @@ def run(args, stdin=None, stdout=None) -> int:
     from .core import Engine, StepEntry
 
     os.makedirs(args.out, exist_ok=True)
-    capacity = max(PAGE_SIZE, -(-args.max_tokens // PAGE_SIZE) * PAGE_SIZE)
-    engine = Engine.from_dir(args.model, dtype=args.dtype, device=args.device, kv_page_size=PAGE_SIZE,
-                             kv_cache_tokens=capacity, max_active_requests=MAX_LIVE_REQUESTS)
+    page = args.page_size
+    if args.max_tokens < 1 or args.max_live < 1 or (args.num_pages_global or 1) < 1 or (args.num_pages_chunk or 1) < 1:
+        raise SystemExit("trace_run: --max-tokens, --max-live and the page counts must be positive")
+    # each request's count is rounded up to 64 tokens (to the page, where that is larger)
+    capacity = -(-args.max_tokens // max(page, PAGE_SIZE)) * max(page, PAGE_SIZE)
+    engine = Engine.from_dir(args.model, dtype=args.dtype, device=args.device, kv_page_size=page,
+                             kv_cache_tokens=args.num_pages_global * page if args.num_pages_global else capacity,
+                             windowed_cache_tokens=args.num_pages_chunk * page if args.num_pages_chunk else capacity,
+                             max_active_requests=args.max_live)
     for line in stdin:
         line = line.strip()
         if not line:

@@ -25,7 +25,10 @@ class AttentionMixer(Part):
       ``qk_norm``, ``qk_norm_eps``   weightless L2 norm of q and k after the rotation
       ``temperature``  None | (floor_scale, attn_scale): q *= 1 + attn_scale*ln(1 + floor((pos+1)/floor_scale))
       ``scale``        softmax scale; default head_dim ** -0.5 (models.rs:5963)
-    tensors: ``<prefix>.{q,k,v,o}_proj.weight``.
+      ``bias``         the random-weights writer makes ``<prefix>.{q,k,v,o}_proj.bias`` too
+    tensors: ``<prefix>.{q,k,v,o}_proj.weight``, and each projection's ``.bias`` where the
+    checkpoint has one (a bias is used iff its tensor exists: crates/hi-mlx/src/models.rs:1808,
+    1843-1845).
     """
 
     graph_safe = True
@@ -45,18 +48,26 @@ class AttentionMixer(Part):
         self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
         self.temperature = tuple(p["temperature"]) if p.get("temperature") else None
         self.scale = float(p.get("scale") or self.hd ** -0.5)
+        self.bias = bool(p.get("bias", False))
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
+        self.b_qkv: Optional[torch.Tensor] = None
+        self.b_o: Optional[torch.Tensor] = None
 
     def cache_spec(self):
         return CacheSpec(kv_heads=self.nkv, head_dim=self.hd, window=self.window)
 
     def tensor_specs(self):
         h, nh, nkv, hd = self.hidden, self.nh, self.nkv, self.hd
+        init = "normal" if self.bias else "absent"     # "absent": the random-weights writer leaves them out
         return [TensorSpec(f"{self.prefix}.q_proj.weight", (nh * hd, h)),
                 TensorSpec(f"{self.prefix}.k_proj.weight", (nkv * hd, h)),
                 TensorSpec(f"{self.prefix}.v_proj.weight", (nkv * hd, h)),
-                TensorSpec(f"{self.prefix}.o_proj.weight", (h, nh * hd))]
+                TensorSpec(f"{self.prefix}.o_proj.weight", (h, nh * hd)),
+                TensorSpec(f"{self.prefix}.q_proj.bias", (nh * hd,), init=init, optional=True),
+                TensorSpec(f"{self.prefix}.k_proj.bias", (nkv * hd,), init=init, optional=True),
+                TensorSpec(f"{self.prefix}.v_proj.bias", (nkv * hd,), init=init, optional=True),
+                TensorSpec(f"{self.prefix}.o_proj.bias", (h,), init=init, optional=True)]
 
     def load(self, fetch):
         q, k, v = (fetch(f"{self.prefix}.{n}_proj.weight") for n in "qkv")
@@ -64,9 +75,17 @@ class AttentionMixer(Part):
             q, k, v = q.float(), k.float(), v.float()
         self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()     # one product for q, k and v
         self.w_o = fetch(f"{self.prefix}.o_proj.weight").contiguous()
+        biases = [fetch(f"{self.prefix}.{n}_proj.bias") for n in "qkv"]
+        if any(b is not None for b in biases):          # a projection without one adds zeros
+            sizes = (self.nh * self.hd, self.nkv * self.hd, self.nkv * self.hd)
+            biases = [torch.zeros(n, dtype=self.w_qkv.dtype, device=self.w_qkv.device) if b is None else b
+                      for b, n in zip(biases, sizes)]
+            self.b_qkv = torch.cat([b.to(self.w_qkv.dtype) for b in biases]).contiguous()
+        b_o = fetch(f"{self.prefix}.o_proj.bias")
+        self.b_o = None if b_o is None else b_o.to(self.w_o.dtype).contiguous()
 
     def forward(self, normed, ctx, cache):
-        qkv = linear(normed, self.w_qkv)
+        qkv = linear(normed, self.w_qkv, bias=self.b_qkv)
         positions = ctx.positions
         table = self.position.rotary_table()
         if table is None and hasattr(self.position, "apply"):
@@ -105,4 +124,4 @@ class AttentionMixer(Part):
         else:
             o = ops.paged_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
                                     chunk, sliding, self.scale, ctx.max_context)
-        return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o)
+        return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)

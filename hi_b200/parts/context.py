@@ -30,6 +30,9 @@ class StepContext:
     page_size: int = 0
     max_context: int = 0          # longest start_pos + n_new in the step
     tap: Optional[Callable[[str, torch.Tensor], None]] = None   # debug: parts report named tensors
+    # debug: choices a part is told to take instead of its own, by the name it reports them under
+    # (the router's expert ids, int32 [N, k] in the step's flat token order)
+    forced: Optional[Dict[str, torch.Tensor]] = None
     # mixed steps only: flat rows of the requests that bring ONE token (int64 [D]) and the longest
     # context among them; None when the step is all portions or all single tokens
     decode_rows: Optional[torch.Tensor] = None

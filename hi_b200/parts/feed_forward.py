@@ -134,7 +134,17 @@ class SigmoidRoutedExperts(Part):
         side = None
         if self.shared and self.OVERLAP_SHARED:
             shared, side = self._shared_on_side_stream(normed)
-        ids, scores, plan = ops.router_plan(normed if normed_f32 is None else normed_f32, self.w_router, self.top_k)
+        router_in = normed if normed_f32 is None else normed_f32
+        forced = ctx.forced.get(f"{self.prefix}.router_ids") if ctx.forced else None
+        if forced is None:
+            ids, scores, plan = ops.router_plan(router_in, self.w_router, self.top_k)
+        else:
+            # debug: another run's expert choices, scored with this run's own logits (two runs in
+            # different precisions can then be compared token by token)
+            _own, _s, logits = ops.router_topk(router_in, self.w_router, self.top_k, want_logits=True)
+            ids = forced.to(device=logits.device, dtype=torch.int32).reshape(n, self.top_k).contiguous()
+            scores = torch.sigmoid(torch.gather(logits, 1, ids.long())).contiguous()
+            plan = ops.moe_plan(ids, self.experts)
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.router_ids", ids)
         tc = ops.moe_tc_supported(normed, self.w_gate)

@@ -17,8 +17,10 @@ def configure_matmul_precision() -> None:
     torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """``x @ weight.T`` for ``x`` [N, K] and ``weight`` [M, K].
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+           bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T`` (``+ bias`` [M], added to the float32 sums by the library's epilogue) for
+    ``x`` [N, K] and ``weight`` [M, K].
 
     A weight kept in float32 while activations are bfloat16 (a tensor stored in 32-bit stays
     so) is multiplied in float32. ``out_dtype=torch.float32`` asks for a float32 result from
@@ -30,7 +32,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         raise RuntimeError("TF32 matrix products are switched on; hi_b200 needs them off")
     if weight.dtype != x.dtype:
         y = torch.mm(x.to(torch.float32), weight.to(torch.float32).t())
+        if bias is not None:
+            y += bias.to(torch.float32)
         return y.to(out_dtype or x.dtype)
+    if bias is not None:
+        y = torch.addmm(bias.to(x.dtype), x, weight.t())
+        return y if out_dtype in (None, x.dtype) else y.to(out_dtype)
     if out_dtype is not None and out_dtype != x.dtype:
         if x.dtype == torch.bfloat16 and out_dtype == torch.float32:
             return torch.mm(x, weight.t(), out_dtype=torch.float32)

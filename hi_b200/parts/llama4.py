@@ -18,8 +18,6 @@ from .spec import LayerSpec, ModelSpec, PartSpec
 
 
 def build_llama4_spec(cfg: Llama4TextConfig) -> ModelSpec:
-    if cfg.attention_bias:
-        raise ConfigError("config.json: 'attention_bias' = true is not supported")
     if cfg.head_dim % 16 != 0 or cfg.head_dim > 256:
         raise ConfigError(f"config.json: 'head_dim' {cfg.head_dim} is not supported (multiples of 16 up to 256)")
     scaling = asdict(cfg.rope_scaling) if cfg.rope_scaling else None
@@ -35,6 +33,7 @@ def build_llama4_spec(cfg: Llama4TextConfig) -> ModelSpec:
             "position": rope if rotary else PartSpec("none"),
             "qk_norm": cfg.use_qk_norm and rotary, "qk_norm_eps": cfg.qk_norm_eps,
             "temperature": (cfg.floor_scale, cfg.attn_scale) if (cfg.attn_temperature_tuning and not rotary) else None,
+            "bias": cfg.attention_bias,
         })
         if cfg.moe_layers[i]:
             ffn = PartSpec("moe_sigmoid", {
@@ -71,3 +70,28 @@ def normalize_llama4_tensor_name(name: str) -> Optional[str]:
     if name.startswith(("model.", "lm_head.")):
         return name
     return None
+
+
+def derive_llama4_tensors(shapes):
+    """The routed experts of a checkpoint in the original export layout, one fused tensor per layer
+    with the input dimension first and no ``.weight`` suffix: ``experts.gate_up_proj`` [E, H, 2I]
+    (gate columns, then up) and ``experts.down_proj`` [E, I, H]. The parts ask for the converted
+    layout the reference reads, ``experts.{gate,up}_proj.weight`` [E, I, H] and
+    ``experts.down_proj.weight`` [E, H, I] (crates/hi-mlx/src/models.rs:6070, 3138-3166); they are
+    cut and transposed here, on the device."""
+    from ..weights.loader import DerivedTensor
+
+    out = {}
+    for name, shape in shapes.items():
+        if name.endswith(".experts.gate_up_proj") and len(shape) == 3 and shape[2] % 2 == 0:
+            base = name[: -len("gate_up_proj")]
+            e, h, two_i = shape
+            half = two_i // 2
+            out[base + "gate_proj.weight"] = DerivedTensor(
+                [name], (e, half, h), lambda ts, half=half: ts[0][:, :, :half].transpose(1, 2).contiguous())
+            out[base + "up_proj.weight"] = DerivedTensor(
+                [name], (e, half, h), lambda ts, half=half: ts[0][:, :, half:].transpose(1, 2).contiguous())
+        elif name.endswith(".experts.down_proj") and len(shape) == 3:
+            e, i, h = shape
+            out[name + ".weight"] = DerivedTensor([name], (e, h, i), lambda ts: ts[0].transpose(1, 2).contiguous())
+    return out

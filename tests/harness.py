@@ -18,6 +18,10 @@ ROOT = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)),
 # tolerances: max |engine - plain| / max |plain| over the compared logits
 TOL_F32 = 2e-5
 TOL_BF16 = 2.5e-2
+# a bfloat16 engine may pick another expert than the plain model only where the plain model's k-th and
+# (k+1)-th router logits are closer than this (the router reads the norm's float32 output; what
+# reaches it in reduced precision is the residual stream's history)
+ROUTING_MARGIN = 0.02
 
 
 def make_model(path: str, cfg: dict, seed: int, std: float = 0.08, overrides=None) -> str:
@@ -151,12 +155,12 @@ def collect(steps: List[Step], per_step_logits: Dict[int, np.ndarray]) -> Dict[H
 
 
 def replay_subprocess(model_dir: str, dtype: str, steps: List[Step], max_tokens: int, out_dir: str,
-                      vocab: int, timeout: int = 600, dump_taps: bool = False):
+                      vocab: int, timeout: int = 600, dump_taps: bool = False, extra: Sequence[str] = ()):
     """Run bin/trace_run as a user would and read back its files. With ``dump_taps`` also
     returns the router's choices per request ({request: {layer prefix: ids [T, k]}})."""
     os.makedirs(out_dir, exist_ok=True)
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
-           "--out", out_dir, "--max-tokens", str(max_tokens)] + (["--dump-taps"] if dump_taps else [])
+           "--out", out_dir, "--max-tokens", str(max_tokens)] + (["--dump-taps"] if dump_taps else []) + list(extra)
     proc = subprocess.run(cmd, input=trace_json(steps), capture_output=True, text=True, timeout=timeout)
     assert proc.returncode == 0, f"trace_run failed ({proc.returncode}):\n{proc.stdout[-2000:]}\n{proc.stderr[-4000:]}"
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
@@ -191,16 +195,25 @@ def replay_subprocess(model_dir: str, dtype: str, steps: List[Step], max_tokens:
     return got, forced
 
 
-def replay_in_process(engine, steps: List[Step], record_routing: bool = False):
-    """Drive Engine.step directly; optionally gather the router's choices per request."""
+def replay_in_process(engine, steps: List[Step], record_routing: bool = False, forced_routing=None):
+    """Drive Engine.step directly; optionally gather the router's choices per request, or hand
+    choices back (``forced_routing`` {request: {layer prefix: ids [T, k]}} by position)."""
     from hi_b200.engine.core import StepEntry
 
     per_step = {}
     routing: Dict[Hashable, Dict[str, List[torch.Tensor]]] = {}
+    fed: Dict[Hashable, int] = {}
     for i, (entries, end) in enumerate(steps):
         taps: Dict[str, torch.Tensor] = {}
         tap = (lambda name, t: taps.__setitem__(name, t.clone())) if record_routing else None
-        logits = engine.step([StepEntry(r, t, w) for r, t, w in entries], tap=tap)
+        forced = None
+        if forced_routing is not None:
+            names = sorted({n for r, _t, _w in entries for n in forced_routing.get(r, {})})
+            forced = {f"{n}.router_ids": torch.cat([forced_routing[r][n][fed.get(r, 0): fed.get(r, 0) + len(t)]
+                                                    for r, t, _w in entries]).to(torch.int32) for n in names}
+        for r, t, _w in entries:
+            fed[r] = fed.get(r, 0) + len(t)
+        logits = engine.step([StepEntry(r, t, w) for r, t, w in entries], tap=tap, forced=forced)
         if logits is not None:
             per_step[i] = logits.float().cpu().numpy()
         if record_routing:

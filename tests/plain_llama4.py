@@ -165,15 +165,23 @@ def attention_core(q, k, v, chunk: Optional[int]) -> torch.Tensor:
     return out.reshape(T, nh * hd)
 
 
+def linear(w: Dict[str, torch.Tensor], prefix: str, x: torch.Tensor) -> torch.Tensor:
+    """x W^T, plus the bias iff a ``.bias`` tensor exists (Linear::load / forward,
+    models.rs:1808, 1843-1847)."""
+    y = x @ w[f"{prefix}.weight"].to(F32).T
+    bias = w.get(f"{prefix}.bias")
+    return y if bias is None else y + bias.to(F32)
+
+
 def attention(cfg: dict, w: Dict[str, torch.Tensor], prefix: str, i: int, x: torch.Tensor, inv_freq) -> torch.Tensor:
     """Llama4Attention::forward (models.rs:5978-6052) plus the chunk rule and temperature."""
     T = x.shape[0]
     nh, nkv = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"])
     hd = cfg.get("head_dim") or cfg["hidden_size"] // nh
     pos = torch.arange(T)
-    q = (x @ w[f"{prefix}.q_proj.weight"].to(F32).T).reshape(T, nh, hd)
-    k = (x @ w[f"{prefix}.k_proj.weight"].to(F32).T).reshape(T, nkv, hd)
-    v = (x @ w[f"{prefix}.v_proj.weight"].to(F32).T).reshape(T, nkv, hd)
+    q = linear(w, f"{prefix}.q_proj", x).reshape(T, nh, hd)
+    k = linear(w, f"{prefix}.k_proj", x).reshape(T, nkv, hd)
+    v = linear(w, f"{prefix}.v_proj", x).reshape(T, nkv, hd)
     use_rope = layer_uses_rope(cfg, i)
     if use_rope:
         inter = bool(cfg.get("rope_interleaved", False))
@@ -185,7 +193,7 @@ def attention(cfg: dict, w: Dict[str, torch.Tensor], prefix: str, i: int, x: tor
         q = attention_temperature(q, pos, float(cfg.get("floor_scale", 8192)), float(cfg.get("attn_scale", 0.1)))
     chunk = cfg.get("attention_chunk_size", 8192) if use_rope else None
     o = attention_core(q, k, v, chunk)
-    return o @ w[f"{prefix}.o_proj.weight"].to(F32).T
+    return linear(w, f"{prefix}.o_proj", o)
 
 
 def swiglu(x, wg, wu, wd) -> torch.Tensor:

@@ -95,7 +95,7 @@ def test_spec_follows_the_configuration_layer_by_layer():
     a = arch.build_spec(arch.parse_config(TINY_A, None))
     assert a.layers[1].mixer.params["temperature"] == (16.0, 0.1) and a.layers[0].mixer.params["temperature"] is None
     assert a.layers[0].mixer.params["qk_norm"] and not a.layers[1].mixer.params["qk_norm"]
-    with pytest.raises(ConfigError, match="attention_bias"):
-        arch.build_spec(arch.parse_config(dict(TINY_A, attention_bias=True), None))
+    biased = arch.build_spec(arch.parse_config(dict(TINY_A, attention_bias=True), None))
+    assert biased.layers[0].mixer.params["bias"] and not a.layers[0].mixer.params["bias"]
     with pytest.raises(ConfigError, match="head_dim"):
         arch.build_spec(arch.parse_config(dict(TINY_A, head_dim=24), None))

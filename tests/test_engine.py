@@ -28,7 +28,7 @@ def check(cfg, mdir, dtype, tol, steps, reqs, page, tokens, what, **kw):
     eng = engine_for(mdir, dtype, page, tokens, **kw)
     got, forced = h.replay_in_process(eng, steps, record_routing=(dtype == "bfloat16"))
     h.compare_with_plain(cfg, h.read_weights(mdir), reqs, got, tol, forced=forced if dtype == "bfloat16" else None,
-                         what=what, margin=0.1)
+                         what=what, margin=h.ROUTING_MARGIN)
     assert not eng.manager.requests, "requests left open"
     for pool in eng.manager.pools:
         assert pool.free == pool.total, "pages were lost"
@@ -218,6 +218,91 @@ def test_generation_with_so_few_pages_that_requests_are_preempted(model_dirs):
         assert all(o.finish_reason == "length" and o.completion_tokens == 40 for o in outs)
         tight.engine.manager.check_invariants()
         assert not tight.engine.manager.requests and all(p.free == p.total for p in tight.engine.manager.pools)
+
+
+def test_abort_frees_everything_also_with_a_step_in_flight(model_dirs):
+    """abort() between calls of step(), while a step launched ahead still holds a row of the request:
+    its pages and slot are back at once, the row is computed for nobody, a waiting request is
+    dropped without ever running, and the others end with the tokens they generate alone."""
+    import hi_b200
+
+    cfg, mdir = model_dirs["A"]
+    prompts = [h.random_tokens(cfg, n, seed=120 + n) for n in (14, 22, 9, 30)]
+    sp = hi_b200.SamplingParams(max_tokens=24, ignore_eos=True)
+    alone = [hi_b200.LLM(mdir, dtype="float32", kv_page_size=8, kv_cache_tokens=512).generate([p], sp)[0].token_ids
+             for p in prompts]
+    llm = hi_b200.LLM(mdir, dtype="float32", kv_page_size=8, max_batch_size=3, kv_cache_tokens=512, lookahead=True)
+    reqs = [llm.add_request(p, sp, request_id=f"r{i}") for i, p in enumerate(prompts)]
+    for _ in range(6):
+        llm.step()
+    assert llm._launched is not None and "r1" in llm._launched.row_of, "no step of r1 is in flight"
+    assert reqs[3].status == "waiting"
+    llm.abort("r3")
+    llm.abort("r1")
+    assert reqs[1].status == "finished" and reqs[1].finish_reason == "aborted" and reqs[3].finish_reason == "aborted"
+    assert not llm.engine.manager.is_open("r1") and reqs[3].output == []
+    llm.engine.manager.check_invariants()
+    kept = len(reqs[1].output)
+    while any(r.status != "finished" for r in reqs):
+        llm.step()
+    llm.step()                                                    # the last launched step is read
+    assert len(reqs[1].output) == kept and reqs[1].output == alone[1][:kept]
+    assert reqs[0].output == alone[0] and reqs[2].output == alone[2]
+    llm.engine.manager.check_invariants()
+    assert not llm.engine.manager.requests and all(p.free == p.total for p in llm.engine.manager.pools)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_weights_generated_on_the_device_are_the_folders_weights(dtype, tmp_path):
+    """Engine.from_config(seed) (weights made by a kernel on the device) and
+    Engine.from_dir(write_random_model(seed)) (the same numbers made on the host and stored) are
+    the same model: equal weights, and logits equal bit for bit."""
+    from hi_b200.engine.core import Engine, StepEntry
+    from hi_b200.weights import write_random_model
+
+    cfg = TINY_C
+    mdir = write_random_model(cfg, str(tmp_path / "m"), seed=77, std=0.05)
+    a = Engine.from_dir(mdir, dtype=dtype, kv_page_size=8, kv_cache_tokens=128, max_active_requests=2)
+    b = Engine.from_config(cfg, seed=77, std=0.05, dtype=dtype, kv_page_size=8, kv_cache_tokens=128, max_active_requests=2)
+    for la, lb in zip(a.model.layers, b.model.layers):
+        assert torch.equal(la.mixer.w_qkv, lb.mixer.w_qkv) and torch.equal(la.mixer.b_qkv, lb.mixer.b_qkv)
+        assert torch.equal(la.norm_mixer.weight, lb.norm_mixer.weight)
+    assert torch.equal(a.model.embedding.table, b.model.embedding.table)
+    toks = h.random_tokens(cfg, 50, seed=2)
+    la = a.step([StepEntry("x", toks, list(range(50)))])
+    lb = b.step([StepEntry("x", toks, list(range(50)))])
+    assert torch.equal(la, lb)
+
+
+def test_a_checkpoint_with_fused_experts_gives_the_same_logits(tmp_path, model_dirs):
+    """The routed experts stored fused and input-major (``experts.gate_up_proj`` [E, H, 2I],
+    ``experts.down_proj`` [E, I, H]) are cut and transposed at load: same logits as the converted layout."""
+    import json
+    import os
+
+    from hi_b200.engine.core import Engine, StepEntry
+    from hi_b200.weights import write_safetensors
+
+    cfg, mdir = model_dirs["B"]
+    w = h.read_weights(mdir)
+    fused = {}
+    for n, t in w.items():
+        if n.endswith("experts.gate_proj.weight"):
+            fused[n.replace("gate_proj.weight", "gate_up_proj")] = \
+                torch.cat([t, w[n.replace("gate_proj", "up_proj")]], dim=1).transpose(1, 2).contiguous()
+        elif n.endswith("experts.down_proj.weight"):
+            fused[n[: -len(".weight")]] = t.transpose(1, 2).contiguous()
+        elif not n.endswith("experts.up_proj.weight"):
+            fused["language_model." + n] = t                   # and the prefix of a multimodal checkpoint
+    out = tmp_path / "fused"
+    os.makedirs(out)
+    write_safetensors(str(out / "model.safetensors"), {("language_model." + n if not n.startswith("language_model.") else n): t
+                                                        for n, t in fused.items()})
+    json.dump(cfg, open(out / "config.json", "w"))
+    toks = h.random_tokens(cfg, 40, seed=8)
+    logits = [Engine.from_dir(d, dtype="float32", kv_page_size=16, kv_cache_tokens=64, max_active_requests=1)
+              .step([StepEntry("x", toks, list(range(40)))]) for d in (mdir, str(out))]
+    assert torch.equal(logits[0], logits[1])
 
 
 # --------------------------------------------------------------------------- a toy mixer with state

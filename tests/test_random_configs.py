@@ -64,7 +64,7 @@ def test_a_random_configuration_in_the_four_ways_of_cutting(seed, large, tmp_pat
                                   max_active_requests=4, debug_poison=True)
             got, forced = h.replay_in_process(eng, steps, record_routing=(dtype == "bfloat16"))
             h.compare_with_plain(cfg, weights, reqs, got, tol, forced=forced if dtype == "bfloat16" else None,
-                                 what=f"seed {seed} {cfg} page {page}: {dtype} {regime}", margin=0.1)
+                                 what=f"seed {seed} {cfg} page {page}: {dtype} {regime}", margin=h.ROUTING_MARGIN)
             assert not eng.manager.requests
             for pool in eng.manager.pools:
                 assert pool.free == pool.total, "pages were lost"

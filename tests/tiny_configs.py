@@ -30,7 +30,7 @@ TINY_B = {
     },
 }
 
-# a third shape for kernels and parts: 5 query heads per kv head, head_dim 48, odd widths
+# a third shape for kernels and parts: 5 query heads per kv head, head_dim 48, odd widths, biases on q/k/v/o
 TINY_C = {
     "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
     "vocab_size": 331, "hidden_size": 120, "num_hidden_layers": 3,
@@ -38,7 +38,7 @@ TINY_C = {
     "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
     "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 1.0,
                      "original_max_position_embeddings": 32},
-    "attention_chunk_size": 24, "no_rope_layers": [1, 0, 1], "rope_interleaved": True,
+    "attention_chunk_size": 24, "no_rope_layers": [1, 0, 1], "rope_interleaved": True, "attention_bias": True,
     "use_qk_norm": True, "attn_temperature_tuning": True, "floor_scale": 8, "attn_scale": 0.25,
     "moe_layers": [0, 2], "num_local_experts": 5, "num_experts_per_tok": 3,
     "intermediate_size": 72, "intermediate_size_mlp": 200,
