@@ -224,7 +224,9 @@ def moe_feed_forward(cfg: dict, w, prefix: str, x: torch.Tensor, forced_ids=None
     ``forced_ids`` [T, k] replaces the top-k choice (scores still come from this function's own
     logits): a reduced-precision engine may pick another expert where two logits are nearly
     equal, and its logits are then compared given ITS choice. ``record(prefix, ids, margin)``
-    receives this function's own choice and the gap between the k-th and (k+1)-th logit."""
+    receives this function's own choice and the gap between the k-th and (k+1)-th logit as a
+    fraction of the root mean square of the sequence's router logits in this layer (the size of
+    the numbers a rounding error of the input is proportional to)."""
     T, H = x.shape
     k = cfg.get("num_experts_per_tok", 1)
     logits = x @ w[f"{prefix}.router.weight"].to(F32).T
@@ -232,6 +234,7 @@ def moe_feed_forward(cfg: dict, w, prefix: str, x: torch.Tensor, forced_ids=None
     if record is not None:
         srt = torch.sort(logits, dim=-1, descending=True).values
         margin = srt[:, k - 1] - srt[:, k] if logits.shape[1] > k else torch.full((T,), float("inf"))
+        margin = margin / logits.pow(2).mean().sqrt().clamp_min(1e-30)
         record(prefix, ids.clone(), margin)
     if forced_ids is not None:
         ids = forced_ids.to(torch.long)

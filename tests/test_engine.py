@@ -77,7 +77,7 @@ def peaky_overrides(cfg, mdir, scale=6.0):
 # their rotary layers, so the sharpening lands on the global layers (every earlier key, with
 # temperature); B has no such norm, its scores grow with the square of the scale and its float32
 # oracle loses five digits at scale 2, so it is left out here.
-SHARPEN = {("A", "float32"): 5.0, ("A", "bfloat16"): 2.5, ("C", "float32"): 2.0, ("C", "bfloat16"): 2.0}
+SHARPEN = {("A", "float32"): 4.0, ("A", "bfloat16"): 2.5, ("C", "float32"): 2.0, ("C", "bfloat16"): 2.0}
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
@@ -464,8 +464,9 @@ def test_toy_position_and_toy_routed_feed_forward_against_a_plain_model():
         g = torch.Generator().manual_seed(11)
         w = {}
         for ts in model.tensor_specs():
-            w[ts.name] = torch.ones(ts.shape) if ts.init == "ones" else torch.randn(ts.shape, generator=g) * 0.25
-        model.load(lambda name: w[name].to("cuda:0"))
+            if ts.init != "absent":                     # optional tensors (projection biases) stay out
+                w[ts.name] = torch.ones(ts.shape) if ts.init == "ones" else torch.randn(ts.shape, generator=g) * 0.25
+        model.load(lambda name: w[name].to("cuda:0") if name in w else None)
         eng = Engine(model, kv_page_size=4, kv_cache_tokens=96, max_active_requests=2)
         assert sorted(str(gr.window) for gr in eng.manager.groups) == ["('chunk', 12)", "None"]
 
