@@ -1,7 +1,9 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the Llama 4 engine on one B200, with roofline fractions.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--model scout|maverick] [--layers L]
+                    [--batch B] [--context C] [--skip-extra]
+    python bench.py --case NAME [sizes ...]        # one kernel or one step alone, for ncu
 
 Default: the Scout-layer-sized 16-layer model with seeded random bfloat16 weights, batch 8,
 8,192-token contexts. Token ids are uniform over the vocabulary; the caches of the decode
@@ -11,13 +13,22 @@ decode step reads are the same). One JSON line is printed:
   e2e              the same through hi_b200.LLM (scheduler, sampler, host tokens in and out)
   prefill          one 2,048-token prompt in one step; frac = flops / time / bf16 peak
   roofline         bytes a decode step must read (every weight it uses once + live cache) / time
-  points           decode tokens per second at batch 1 and 64
+  points           decode tokens per second at batch 1 and 64, and the two further workloads:
+  long_context     the same model at 65,536-token contexts: decoding at batch 1 and 4, and a prompt
+                   fed in 4,096-token portions in the same steps as three decoding requests
+                   (tokens per second of each portion against its offset, pages in use of the
+                   chunked layers step by step: they fall back whenever the prompt passes 8,192)
+  maverick         the 4-layer Maverick-sized model (128 experts), batch 64 at 4,096-token contexts:
+                   tokens per second, roofline fraction, rows per expert of one step
+  cpu_baseline_s   wall time of the plain implementation (tests/plain_llama4.py, whole sequences, no
+                   cache, float32 on the CPU) on the two tiny workloads: the timed CPU baseline
 The reference (PipeNetwork/hi) runs Llama 4 only through Apple MLX/Metal, so ``--impl
 reference`` reports that it is unavailable here.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -45,6 +56,8 @@ MAVERICK = dict(SCOUT, num_hidden_layers=4, rope_scaling=None, use_qk_norm=False
                 num_local_experts=128)
 MODELS = {"scout": (SCOUT, 16), "maverick": (MAVERICK, 4)}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+PAGE = 64
+DEFAULT_STEPS = 64
 
 
 def peaks():
@@ -128,10 +141,203 @@ def model_bytes_and_flops(model, distinct_by_layer, context):
     return weight_bytes + head, kv_bytes, flops
 
 
+def attention_flops(model, first, count):
+    """Score and value flops of ``count`` new tokens at positions ``first ..`` (each query against
+    the keys it may read: all earlier ones, or those of its own chunk)."""
+    total = 0
+    for layer in model.layers:
+        mix = layer.mixer
+        if mix.window and mix.window[0] == "chunk":
+            c, keys, p, end = mix.window[1], 0, first, first + count
+            while p < end:                               # chunk by chunk: a query at p sees p % c + 1 keys
+                seg = min(end, (p // c + 1) * c) - p
+                keys += seg * (p % c) + seg * (seg + 1) // 2
+                p += seg
+        else:
+            keys = count * first + count * (count + 1) // 2
+        total += 4 * mix.nh * mix.hd * keys
+    return total
+
+
+def build_engine(cfg, global_tokens, chunked_tokens, slots):
+    """The model with random weights made on the device, pools of the given sizes (tokens), and
+    caches filled with seeded noise (decode steps are timed without the prefill that would fill them)."""
+    import torch
+
+    from hi_b200.engine.core import Engine
+
+    t0 = time.time()
+    engine = Engine.from_config(cfg, seed=0, std=0.02, dtype="bfloat16", kv_page_size=PAGE,
+                                kv_cache_tokens=global_tokens, windowed_cache_tokens=chunked_tokens,
+                                max_active_requests=slots)
+    torch.cuda.synchronize()
+    load_s = time.time() - t0
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    for view in engine.cache.views.values():
+        if view.k_pages is not None:
+            view.k_pages.normal_(0.0, 1.0, generator=gen)
+            view.v_pages.normal_(0.0, 1.0, generator=gen)
+    return engine, load_s
+
+
+def timed_decode(engine, batch, ctx_len, steps, warmup, vocab, cpu_gen, tag="d"):
+    """W + K single-token steps of ``batch`` requests whose contexts end at ``ctx_len``; the K
+    timed steps lie between two synchronisations, every step has its own event too (median)."""
+    import torch
+
+    from hi_b200.engine.core import StepEntry
+    from hi_b200.kernels import ops
+
+    total = warmup + steps + 1
+    ids = [f"{tag}{batch}-{i}" for i in range(batch)]
+    for rid in ids:
+        engine.assume_cached(rid, ctx_len - total)
+    toks = torch.randint(0, vocab, (total, batch), generator=cpu_gen).tolist()
+    # one step with a tap to see which experts a step touches, then the warm-up steps (the first
+    # step of a shape is eager, the second captures the CUDA graph of this shape)
+    taps = {}
+    engine.step([StepEntry(r, [toks[total - 1][i]], [0]) for i, r in enumerate(ids)],
+                tap=lambda n, t: taps.__setitem__(n, t.clone()))
+    routing = {int(n.split(".")[2]): t.flatten().tolist() for n, t in taps.items() if n.endswith("router_ids")}
+    distinct = {layer: len(set(chosen)) for layer, chosen in routing.items()}
+    for s in range(warmup):
+        engine.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
+    torch.cuda.synchronize()
+    launches0 = ops.LAUNCHES[0]
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    marks[0].record()
+    for k, s in enumerate(range(warmup, total - 1)):
+        engine.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
+        marks[k + 1].record()
+    torch.cuda.synchronize()
+    ms = marks[0].elapsed_time(marks[-1]) / steps
+    per_step = [marks[k].elapsed_time(marks[k + 1]) for k in range(steps)]
+    launches = ops.LAUNCHES[0] - launches0
+    for rid in ids:
+        engine.finish(rid)
+    wb, kv, _ = model_bytes_and_flops(engine.model, distinct, ctx_len)
+    return {"ms": ms, "ms_median": statistics.median(per_step), "tok_s": batch * 1000.0 / ms, "launches": launches,
+            "distinct": (sum(distinct.values()) / len(distinct) if distinct else 0.0), "bytes": wb + batch * kv,
+            "routing": routing}
+
+
+def release(engine):
+    import torch
+
+    engine.model = None
+    engine.cache = None
+    engine._graphs.clear()
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def long_context_point(engine, cfg, args, pk, vocab, cpu_gen):
+    """65,536-token contexts on the same model: decoding at batch 1 and 4, and one request's prompt
+    fed in 4,096-token portions in the same steps as three requests that decode."""
+    import torch
+
+    from hi_b200.engine.core import StepEntry
+
+    ctx = args.long_context
+    out = {"context": ctx}
+    steps = max(8, min(args.steps, 32))
+    for b in (1, 4):
+        r = timed_decode(engine, b, ctx, steps, args.warmup, vocab, cpu_gen, tag="L")
+        out[f"decode_b{b}"] = {"value": r["tok_s"], "ms_per_step": r["ms"],
+                               "frac": r["bytes"] / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"]}
+    portion = args.long_portion
+    n_portions = (ctx - portion) // portion
+    decoders = [f"Lm{i}" for i in range(3)]
+    for rid in decoders:
+        engine.assume_cached(rid, ctx - n_portions - 4)
+    prompt = torch.randint(0, vocab, (n_portions * portion,), generator=cpu_gen).tolist()
+    dec = torch.randint(0, vocab, (n_portions + 1, 3), generator=cpu_gen).tolist()
+    chunked = [g for g, spec in enumerate(engine.manager.groups) if spec.window]
+    portions, pages = [], []
+    # the first portion runs once untimed (warm-up of this step shape), as a request of its own
+    engine.step([StepEntry("Lwarm", prompt[:portion], [])] + [StepEntry(r, [dec[n_portions][i]], [0]) for i, r in enumerate(decoders)])
+    engine.finish("Lwarm")
+    torch.cuda.synchronize()
+    for p in range(n_portions):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        entries = [StepEntry("Lp", prompt[p * portion:(p + 1) * portion], [portion - 1] if p == n_portions - 1 else [])]
+        entries += [StepEntry(r, [dec[p][i]], [0]) for i, r in enumerate(decoders)]
+        start.record()
+        engine.step(entries)
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        _, _, fpt = model_bytes_and_flops(engine.model, {}, ctx)
+        flops = fpt * (portion + 3) + attention_flops(engine.model, p * portion, portion)
+        portions.append({"offset": p * portion, "ms": round(ms, 2), "tokens_per_s": round((portion + 3) * 1000.0 / ms),
+                         "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3)})
+        snap = engine.manager.snapshot()["groups"]
+        pages.append(sum(snap[g]["used"] for g in chunked))
+    for rid in decoders + ["Lp"]:
+        engine.finish(rid)
+    out["mixed_steps"] = {"portion_tokens": portion, "decoding_requests": 3, "portions": portions,
+                          "chunked_pages_in_use_after_each_step": pages, "page_tokens": PAGE}
+    return out
+
+
+def maverick_point(args, pk, cpu_gen):
+    """The Maverick-sized model (4 layers, two of them with 128 experts), batch 64, 4,096-token contexts."""
+    cfg, _full = MODELS["maverick"]
+    engine, load_s = build_engine(cfg, 64 * (4096 + PAGE) + 4 * PAGE, 64 * (4096 + 2 * PAGE) + 4 * PAGE, 66)
+    r = timed_decode(engine, 64, 4096, max(8, min(args.steps, 32)), args.warmup, cfg["vocab_size"], cpu_gen, tag="M")
+    rows = {}
+    for layer, chosen in r["routing"].items():
+        counts = {}
+        for e in chosen:
+            counts[e] = counts.get(e, 0) + 1
+        hist = {}
+        for c in counts.values():
+            hist[c] = hist.get(c, 0) + 1
+        rows[f"layer{layer}"] = {"experts_with_rows": len(counts), "max_rows": max(counts.values()),
+                                 "mean_rows": round(len(chosen) / len(counts), 2),
+                                 "experts_by_rows": {str(k): hist[k] for k in sorted(hist)}}
+    out = {"value": r["tok_s"], "ms_per_step": r["ms"], "batch": 64, "context": 4096, "layers": cfg["num_hidden_layers"],
+           "experts": cfg["num_local_experts"], "bytes_per_step": r["bytes"],
+           "frac": r["bytes"] / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], "rows_per_expert": rows,
+           "weights_load_s": round(load_s, 1)}
+    release(engine)
+    return out
+
+
+def cpu_baseline():
+    """Wall time of the plain implementation on the two tiny workloads (4 prompts of 7/19/33/48 tokens
+    + 16 generated tokens each on tiny A; 3 prompts of 5/40/70 + 24 on tiny B): greedy generation
+    that runs the whole sequence again for every token, float32 on the CPU."""
+    import tempfile
+
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_llama4 as plain
+    from harness import make_model, random_tokens, read_weights
+    from tiny_configs import TINY_A, TINY_B
+
+    out = {}
+    threads = torch.get_num_threads()
+    for name, cfg, prompts, new in (("tiny_a", TINY_A, (7, 19, 33, 48), 16), ("tiny_b", TINY_B, (5, 40, 70), 24)):
+        with tempfile.TemporaryDirectory() as d:
+            make_model(d, cfg, seed=11, std=0.08)
+            w = read_weights(d)
+        t0 = time.perf_counter()
+        for i, n in enumerate(prompts):
+            toks = random_tokens(cfg, n, seed=50 + i)
+            for _ in range(new):
+                toks.append(int(plain.forward(cfg, w, toks)[-1].argmax()))
+        out[name] = round(time.perf_counter() - t0, 2)
+    out["threads"] = threads
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=DEFAULT_STEPS)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="scout", choices=sorted(MODELS))
@@ -141,7 +347,16 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--points", default="1,64")
     ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--skip-extra", action="store_true", help="leave out the long-context, Maverick and CPU points")
+    ap.add_argument("--long-context", type=int, default=65536)
+    ap.add_argument("--long-portion", type=int, default=4096)
+    ap.add_argument("--case", nargs="+", default=None, metavar=("NAME", "SIZE"),
+                    help="run one kernel or one step alone a few times (for ncu): " + ", ".join(sorted(CASES)))
     args = ap.parse_args(argv)
+    if args.case:
+        CASES[args.case[0]](*[int(a) for a in args.case[1:]])
+        print("ok")
+        return 0
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "PipeNetwork/hi runs Llama 4 only through Apple MLX/Metal (crates/hi-mlx, macOS aarch64); "
@@ -156,8 +371,7 @@ def main(argv=None) -> int:
     import torch
 
     import hi_b200
-    from hi_b200.engine.core import Engine, StepEntry
-    from hi_b200.kernels import ops
+    from hi_b200.engine.core import StepEntry
     from hi_b200.sampling import SamplingParams
 
     pk = peaks()
@@ -167,67 +381,24 @@ def main(argv=None) -> int:
     cfg = dict(base_cfg, num_hidden_layers=args.layers)
     points = sorted({int(p) for p in args.points.split(",") if p} | {args.batch})
     max_batch = max(points)
-    page = 64
     ctx_len = args.context
-    cache_tokens = max_batch * (ctx_len + page) + args.prefill_tokens + 4 * page
-    # rotary layers keep one attention chunk per request (plus the pages being written)
-    chunk_tokens = max_batch * (min(ctx_len, cfg["attention_chunk_size"]) + 2 * page) + args.prefill_tokens + 4 * page
-    t0 = time.time()
-    engine = Engine.from_config(cfg, seed=0, std=0.02, dtype="bfloat16", kv_page_size=page,
-                                kv_cache_tokens=cache_tokens, windowed_cache_tokens=chunk_tokens,
-                                max_active_requests=max_batch + 2)
-    torch.cuda.synchronize()
-    load_s = time.time() - t0
-    gen = torch.Generator(device="cuda").manual_seed(1)
-    for view in engine.cache.views.values():            # seeded noise instead of a prefill
-        if view.k_pages is not None:
-            view.k_pages.normal_(0.0, 1.0, generator=gen)
-            view.v_pages.normal_(0.0, 1.0, generator=gen)
+    extra = not args.skip_extra and args.model == "scout" and args.layers == FULL_LAYERS
+    # pools: every request of the largest batch at the context length, the prompt of the prefill point and
+    # some slack; rotary layers keep one attention chunk per request (plus the pages being written).
+    # The long-context point reuses this engine: four requests of 65,536 tokens, one of them fed in portions
+    slack = args.prefill_tokens + 4 * PAGE
+    global_tokens = max_batch * (ctx_len + PAGE) + slack
+    chunked_tokens = max_batch * (min(ctx_len, cfg["attention_chunk_size"]) + 2 * PAGE) + slack
+    if extra:
+        global_tokens = max(global_tokens, 4 * (args.long_context + PAGE) + slack)
+        chunked_tokens = max(chunked_tokens, 4 * (cfg["attention_chunk_size"] + 2 * PAGE) + args.long_portion + slack)
+    engine, load_s = build_engine(cfg, global_tokens, chunked_tokens, max(max_batch, 4) + 2)
     vocab = cfg["vocab_size"]
     cpu_gen = torch.Generator().manual_seed(2)
     sampler = ClockSampler()
     sampler.start()
 
-    def timed_decode(batch):
-        """W + K single-token steps of `batch` requests whose contexts end at ctx_len."""
-        total = args.warmup + args.steps + 1
-        ids = [f"d{batch}-{i}" for i in range(batch)]
-        for rid in ids:
-            engine.assume_cached(rid, ctx_len - total)
-        toks = torch.randint(0, vocab, (total, batch), generator=cpu_gen).tolist()
-        # one step with a tap to count the distinct experts a step touches, then the warm-up
-        # steps (the first is eager, the second captures the CUDA graph of this shape)
-        taps = {}
-        engine.step([StepEntry(r, [toks[total - 1][i]], [0]) for i, r in enumerate(ids)],
-                    tap=lambda n, t: taps.__setitem__(n, t))
-        distinct = {int(n.split(".")[2]): len(set(t.flatten().tolist())) for n, t in taps.items()
-                    if n.endswith("router_ids")}
-        for s in range(args.warmup):
-            engine.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
-        torch.cuda.synchronize()
-        launches0 = ops.LAUNCHES[0]
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for s in range(args.warmup, total - 1):
-            logits = engine.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
-        end.record()
-        torch.cuda.synchronize()
-        ms = start.elapsed_time(end) / args.steps
-        launches = ops.LAUNCHES[0] - launches0
-        for rid in ids:
-            engine.finish(rid)
-        return ms, launches, distinct
-
-    def decode_bytes(batch, distinct):
-        wb, kv, _ = model_bytes_and_flops(engine.model, distinct, ctx_len)
-        return wb + batch * kv
-
-    results = {}
-    for b in points:
-        ms, launches, distinct = timed_decode(b)
-        results[b] = {"ms": ms, "tok_s": b * 1000.0 / ms, "launches": launches,
-                      "distinct": (sum(distinct.values()) / len(distinct) if distinct else 0.0),
-                      "bytes": decode_bytes(b, distinct)}
+    results = {b: timed_decode(engine, b, ctx_len, args.steps, args.warmup, vocab, cpu_gen) for b in points}
     main_r = results[args.batch]
 
     # ---- prefill: one prompt of --prefill-tokens in one step, logits at the last position
@@ -290,6 +461,7 @@ def main(argv=None) -> int:
     line = {
         "metric": f"decode tokens/s (Llama 4 {args.model.capitalize()} layer sizes, bf16)", "value": main_r["tok_s"], "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_r["ms"],
+        "ms_per_step_median": main_r["ms_median"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0,0.02), uniform random token ids, noise-filled KV cache",
         "config": {"model": f"llama4-{args.model}-layers", "layers": args.layers, "layers_full": FULL_LAYERS,
@@ -297,7 +469,7 @@ def main(argv=None) -> int:
                    "head_dim": cfg["head_dim"], "experts": cfg["num_local_experts"], "top_k": cfg["num_experts_per_tok"],
                    "expert_inter": cfg["intermediate_size"], "mlp_inter": cfg["intermediate_size_mlp"],
                    "moe_every": cfg.get("interleave_moe_layer_step", 1), "vocab": vocab, "chunk": cfg["attention_chunk_size"],
-                   "global_batch": args.batch, "seq_len": ctx_len, "page": page, "parallelism": "single-gpu",
+                   "global_batch": args.batch, "seq_len": ctx_len, "page": PAGE, "parallelism": "single-gpu",
                    "l2": "inputs larger than L2 (each step streams all weights it uses)",
                    "weights_load_s": round(load_s, 1)},
         "clocks": clocks,
@@ -314,8 +486,147 @@ def main(argv=None) -> int:
     }
     if prefill:
         line["prefill"] = prefill
+    if extra:
+        long_ctx = long_context_point(engine, cfg, args, pk, vocab, cpu_gen)
+        line["long_context"] = long_ctx
+        line["points"]["decode_b1_ctx65536"] = long_ctx["decode_b1"]["value"]
+        line["points"]["decode_b4_ctx65536"] = long_ctx["decode_b4"]["value"]
+        llm = None
+        release(engine)
+        mav = maverick_point(args, pk, cpu_gen)
+        line["maverick"] = mav
+        line["points"]["maverick_decode_b64_ctx4096"] = mav["value"]
+        line["cpu_baseline_s"] = cpu_baseline()
     print(json.dumps(line))
     return 0
+
+
+# --------------------------------------------------------------------------- one kernel or one step alone
+# Small, fixed cases at the Scout layer's sizes (40 heads, 8 kv heads, head_dim 128; hidden 5120,
+# 16 experts of 8192) for `ncu -k regex:<kernel>`: inputs larger than L2, a few GB at most.
+DEV = "cuda:0"
+
+
+def case_decode_attention(batch=8, context=8192, page=64):
+    import torch
+
+    from hi_b200.kernels import ops
+
+    nh, nkv, hd = 40, 8, 128
+    blocks = -(-context // page)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    kp = torch.randn(batch * blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    vp = torch.randn(batch * blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    bt = torch.randperm(batch * blocks, device=DEV, generator=g).to(torch.int32).view(batch, blocks).contiguous()
+    q = torch.randn(batch, nh, hd, device=DEV, generator=g).to(torch.bfloat16)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+    sot = torch.arange(batch, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        ops.decode_attention(q, kp, vp, bt, sot, pos, 0, 0, hd ** -0.5, context)
+    torch.cuda.synchronize()
+
+
+def _experts(experts, rows):
+    import torch
+
+    from hi_b200.kernels import ops
+
+    hidden, inter = 5120, 8192
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(rows, hidden, device=DEV, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(experts, inter, hidden, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    wu = (torch.randn(experts, inter, hidden, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(experts, hidden, inter, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    ids = torch.randint(0, experts, (rows, 1), device=DEV, generator=g).to(torch.int32)
+    scores = torch.rand(rows, 1, device=DEV, generator=g)
+    return x, wg, wu, wd, scores, ops.moe_plan(ids, experts)
+
+
+def case_expert_gemv(batch=8):
+    """The weight-streaming expert kernels at decode shape."""
+    import torch
+
+    from hi_b200.kernels import ops
+
+    x, wg, wu, wd, scores, plan = _experts(16, batch)
+    for _ in range(3):
+        act = ops.moe_gate_up(x, plan, 1, wg, wu, scores, True)
+        ops.moe_down(act, wd, plan, True)
+    torch.cuda.synchronize()
+
+
+def case_expert_tc(tokens=1024, experts=8):
+    """The tcgen05 grouped products at prefill shape: about 128 rows per expert."""
+    from hi_b200.kernels import ops
+
+    x, wg, wu, wd, scores, plan = _experts(experts, tokens)
+    for _ in range(3):
+        act = ops.moe_gate_up_tc(x, plan, 1, wg, wu, scores)
+        ops.moe_down_tc(act, wd, plan)
+    ops.check_tc_status()
+
+
+def case_prefill_attention(tokens=2048, cached=0, page=64):
+    """One portion of ``tokens`` new tokens behind ``cached`` earlier ones, both prefill kernels."""
+    import torch
+
+    from hi_b200.kernels import ops
+
+    nh, nkv, hd = 40, 8, 128
+    total = tokens + cached
+    blocks = -(-total // page)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    kp = torch.randn(blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    vp = torch.randn(blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    bt = torch.randperm(blocks, device=DEV, generator=g).to(torch.int32).view(1, blocks).contiguous()
+    q = torch.randn(tokens, nh, hd, device=DEV, generator=g).to(torch.bfloat16)
+    pos = torch.arange(cached, total, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        if cached == 0:
+            ops.prefill_attention(q, kp, vp, bt, cu, pos, 1, tokens, 0, 0, hd ** -0.5)
+        ops.prefill_attention_tc(q, kp, vp, bt, cu, pos, 1, tokens, 0, 0, hd ** -0.5)
+    ops.check_tc_status()
+
+
+def _case_engine(layers, tokens, slots):
+    from hi_b200.engine.core import Engine
+
+    return Engine.from_config(dict(SCOUT, num_hidden_layers=layers), seed=0, dtype="bfloat16", device=DEV,
+                              kv_page_size=PAGE, kv_cache_tokens=tokens, max_active_requests=slots, use_cuda_graphs=False)
+
+
+def case_decode_step(batch=8, context=8192, layers=2):
+    """Three decode steps of ``batch`` requests at ``context`` cached tokens, every kernel launched on its own."""
+    import torch
+
+    from hi_b200.engine.core import StepEntry
+
+    eng = _case_engine(layers, batch * (context + 128), batch + 1)
+    for i in range(batch):
+        eng.assume_cached(i, context - 8)
+    g = torch.Generator().manual_seed(0)
+    for _ in range(3):
+        eng.step([StepEntry(i, [int(torch.randint(0, 202048, (1,), generator=g))], [0]) for i in range(batch)])
+    torch.cuda.synchronize()
+
+
+def case_prefill_step(tokens=2048, layers=2):
+    """Three prompts of ``tokens`` tokens, each in one step."""
+    import torch
+
+    from hi_b200.engine.core import StepEntry
+
+    eng = _case_engine(layers, tokens + 128, 2)
+    g = torch.Generator().manual_seed(0)
+    for i in range(3):
+        eng.step([StepEntry(i, torch.randint(0, 202048, (tokens,), generator=g).tolist(), [tokens - 1])])
+        eng.finish(i)
+    torch.cuda.synchronize()
+
+
+CASES = {"decode_attention": case_decode_attention, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
+         "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step}
 
 
 if __name__ == "__main__":
