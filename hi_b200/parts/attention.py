@@ -32,6 +32,7 @@ class AttentionMixer(Part):
     """
 
     graph_safe = True
+    FUSED_DECODE = True      # decode steps: one launch for encoding, cache append, attention and merge
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -96,11 +97,19 @@ class AttentionMixer(Part):
             qkv = torch.cat([q.reshape(n, -1), k.reshape(n, -1), v], dim=1).to(normed.dtype).contiguous()
         inv_freq, interleaved = table if table is not None else (None, False)
         block_table = ctx.block_tables[cache.group]
+        chunk = self.window[1] if self.window and self.window[0] == "chunk" else 0
+        sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
+        if ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16:
+            # a step of single decoded tokens: encoding, cache append, attention and the merge of its
+            # splits in one launch, where the kernel takes the shapes
+            o = ops.decode_attention_fused(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
+                                           self.qk_norm_eps, self.temperature, ctx.seq_of_token, block_table,
+                                           cache.k_pages, cache.v_pages, chunk, sliding, self.scale, ctx.max_context)
+            if o is not None:
+                return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)
         q = ops.qkv_post(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
                          self.qk_norm_eps, self.temperature, ctx.seq_of_token, block_table, cache.k_pages,
                          cache.v_pages, ctx.page_size, cache.writes)
-        chunk = self.window[1] if self.window and self.window[0] == "chunk" else 0
-        sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
         if ctx.max_new == 1 and ops.decode_attention_supported(q.dtype, self.nh, self.nkv, self.hd):
             # every token of the step is one request's decoded token: the tensor-core kernel
             o = ops.decode_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,

@@ -526,7 +526,7 @@ def test_toy_position_and_toy_routed_feed_forward_against_a_plain_model():
 def test_the_tensor_core_kernels_take_the_sizes_they_are_built_for(tmp_path):
     """A silent fall to the general kernels would still give right logits: at head_dim 128 with
     64-token pages, a 300-token prompt and decoded tokens must go through the tcgen05 prefill
-    attention, the TMA decode attention, the tcgen05 expert products (prompt) and the
+    attention, the fused TMA decode attention, the tcgen05 expert products (prompt) and the
     weight-streaming expert kernel (decode) in bfloat16, and through the general kernels in float32."""
     from hi_b200.engine.core import Engine, StepEntry
     from hi_b200.kernels import ops
@@ -535,7 +535,7 @@ def test_the_tensor_core_kernels_take_the_sizes_they_are_built_for(tmp_path):
                attention_chunk_size=128, intermediate_size=128, intermediate_size_mlp=256, vocab_size=300)
     mdir = h.make_model(str(tmp_path / "m"), cfg, seed=3, std=0.04)
     toks = h.random_tokens(cfg, 310, seed=4)
-    want = {"bfloat16": {"attention_prefill_tc", "attention_decode_tma", "moe_gate_up_tc", "moe_down_tc", "moe_gate_up",
+    want = {"bfloat16": {"attention_prefill_tc", "attention_decode_fused", "moe_gate_up_tc", "moe_down_tc", "moe_gate_up",
                          "router_plan", "qkv_post", "add_rmsnorm"},
             "float32": {"paged_attention", "moe_gate_up", "moe_down", "router_plan"}}
     for dtype, tol in DTYPES:
@@ -550,5 +550,5 @@ def test_the_tensor_core_kernels_take_the_sizes_they_are_built_for(tmp_path):
         ran = {k for k, v in ops.CALLS.items() if v > before.get(k, 0)}
         assert want[dtype] <= ran, f"{dtype}: {sorted(want[dtype] - ran)} did not run (ran: {sorted(ran)})"
         if dtype == "float32":
-            assert not ran & {"attention_prefill_tc", "attention_decode_tma", "moe_gate_up_tc"}, "reduced-precision kernels on the 32-bit path"
+            assert not ran & {"attention_prefill_tc", "attention_decode_tma", "attention_decode_fused", "moe_gate_up_tc"}, "reduced-precision kernels on the 32-bit path"
             h.compare_with_plain(cfg, h.read_weights(mdir), {"a": toks}, {"a": rows}, tol, what="sizes of the fast kernels, float32")

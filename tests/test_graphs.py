@@ -115,8 +115,8 @@ def test_freed_chunks_under_captured_steps_and_graphs_that_are_evicted(dtype, to
     assert chunked and chunked[0]["peak"] <= 3 * (64 // 16 + 1), "the chunked group kept pages of dead chunks"
     assert chunked[0]["allocations"] > chunked[0]["total"], "pages of dead chunks were not used again"
     if dtype == "bfloat16":
-        assert ops.CALLS.get("attention_decode_tma", 0) > before.get("attention_decode_tma", 0), \
-            "the TMA decode kernel did not run"
+        assert ops.CALLS.get("attention_decode_fused", 0) > before.get("attention_decode_fused", 0), \
+            "the fused TMA decode kernel did not run"
 
 
 def test_a_captured_step_equals_the_same_step_run_eagerly(model_dirs):

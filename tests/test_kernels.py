@@ -550,3 +550,53 @@ def test_random_fill_has_the_hosts_bits():
         assert (got32.cpu().numpy().view(np.uint32) == want.view(np.uint32)).all(), f"float32, n {n}"
         got16 = o.random_normal(torch.empty(n, dtype=torch.bfloat16, device=DEV), key, float(rv.scale_for(std)), first)
         assert torch.equal(got16.cpu(), torch.from_numpy(want).to(torch.bfloat16)), f"bfloat16, n {n}"
+
+
+@pytest.mark.parametrize("shape", [(40, 8, 128, 64, 8192, True, True, False), (40, 8, 128, 64, 0, False, False, True),
+                                   (8, 8, 64, 16, 0, True, False, False), (32, 2, 64, 32, 512, True, True, True),
+                                   (16, 1, 128, 128, 64, False, True, False), (12, 4, 64, 16, 128, True, True, True)])
+def test_fused_decode_attention_equals_its_three_kernels(shape):
+    """hb_attention_decode_fused (encoding of q, k and v, cache append, attention, merge of the splits,
+    one launch) against qkv_post + the decode kernel + the merge kernel on the same inputs: the keys
+    and values it appends are the same bits, the outputs agree to bfloat16 rounding, and its counters
+    are zero again. Requests of very different lengths in one batch (one split and many), positions
+    on and beside page, tile and chunk edges; twice in a row on the same buffers."""
+    o = ops()
+    nh, nkv, hd, page, chunk, rope, norm, temp = shape
+    starts = [0, 1, 63, 64, 255, 256, 1030, 2500, 8191, 8192, 8200]
+    S = len(starts)
+    total = [s + 1 for s in starts]
+    g = torch.Generator().manual_seed(nh * 7 + hd)
+    n_pages = sum(-(-t // page) for t in total) + 2
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-t // page) for t in total)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    c = 0
+    for s in range(S):
+        for b in range(-(-total[s] // page)):
+            bt[s, b] = perm[c]; c += 1
+    dt = torch.bfloat16
+    kp = (torch.randn(n_pages, nkv, page, hd, generator=g)).to(dt)      # whatever earlier steps left, and stale rows
+    vp = (torch.randn(n_pages, nkv, page, hd, generator=g)).to(dt)
+    qkv = (torch.randn(S, (nh + 2 * nkv) * hd, generator=g) * 1.5).to(dt).to(DEV)
+    pos = torch.tensor(starts, dtype=torch.int32).to(DEV)
+    sot = torch.arange(S, dtype=torch.int32).to(DEV)
+    inv = plain.rope_inverse_frequencies(hd, 10000.0, None).to(DEV) if rope else None
+    temperature = (16.0, 0.1) if temp else None
+    interleaved = bool(nh % 3 == 0)
+    bt = bt.to(DEV)
+    for _round in range(2):
+        k1, v1, k2, v2 = kp.to(DEV), vp.to(DEV), kp.to(DEV), vp.to(DEV)
+        q = o.qkv_post(qkv, nh, nkv, hd, pos, inv, interleaved, norm, 1e-6, temperature, sot, bt, k1, v1, page, True)
+        want = o.decode_attention(q, k1, v1, bt, sot, pos, chunk, 0, hd ** -0.5, max(total))
+        got = o.decode_attention_fused(qkv, nh, nkv, hd, pos, inv, interleaved, norm, 1e-6, temperature, sot, bt, k2, v2,
+                                       chunk, 0, hd ** -0.5, max(total))
+        assert got is not None, "the fused kernel refused shapes it is written for"
+        torch.cuda.synchronize()
+        assert torch.equal(k1, k2) and torch.equal(v1, v2), "the appended keys or values differ"
+        close(got, want, 1e-2, f"fused decode attention {shape}")
+        assert int(o._fused_counter_buffer(torch.device(DEV)).abs().sum()) == 0, "the counters were not left at zero"
+    o.check_tc_status()
+    # a sliding window is not taken: the caller falls back
+    assert o.decode_attention_fused(qkv, nh, nkv, hd, pos, inv, interleaved, norm, 1e-6, temperature, sot, bt, k2, v2,
+                                    0, 100, hd ** -0.5, max(total)) is None

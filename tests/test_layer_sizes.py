@@ -166,7 +166,7 @@ def test_scout_sized_layers_across_the_chunk_edge():
     assert max(len(e) for e, _ in traces["mixed"]) >= 3
     # all keys: 129 + 5 + 11 + 4 pages; chunked: a's chunk (128) + b (5) + c (11) + the page a writes past the edge + 2
     snap = run_model(cfg, 3, reqs, traces, pools=(150, 147),
-                     expect_kernels={"attention_prefill_tc", "attention_decode_tma", "moe_gate_up_tc", "moe_down_tc",
+                     expect_kernels={"attention_prefill_tc", "attention_decode_tma", "attention_decode_fused", "moe_gate_up_tc", "moe_down_tc",
                                      "moe_gate_up", "moe_down", "router_plan"})
     chunked = [g for g in snap["groups"] if g["window"]][0]
     assert chunked["allocations"] > chunked["total"], "the dead chunk's pages were not used again"
@@ -189,7 +189,7 @@ def test_maverick_sized_layers_with_128_experts():
     }
     # chunked pool: a's chunk (16 pages) + its next page + b (8) + c (5) + d (3) + 2
     snap = run_model(cfg, 4, reqs, traces, pools=(52, 35),
-                     expect_kernels={"attention_prefill_tc", "attention_decode_tma", "moe_gate_up_tc", "moe_down_tc",
+                     expect_kernels={"attention_prefill_tc", "attention_decode_tma", "attention_decode_fused", "moe_gate_up_tc", "moe_down_tc",
                                      "moe_gate_up", "moe_down", "router_plan"})
     chunked = [g for g in snap["groups"] if g["window"]][0]
     assert chunked["allocations"] > chunked["total"], "dead chunks' pages were not used again"
