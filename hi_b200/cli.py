@@ -4,9 +4,11 @@
     python -m hi_b200 run MODEL_PATH --tokens "1,2,3" [--max-tokens N] [--top-k 5] [--temperature T]
                           [--top-p P] [--seed S] [--include-logits] [--dtype bfloat16|float32]
                           [--max-batch-size 8] [--max-batched-tokens 8192] [--kv-page-size 64]
-                          [--random-weights [--weights-seed S] [--weights-std 0.02]]
+                          [--random-weights [--weights-seed S] [--weights-std 0.02]] [--cpu]
     python -m hi_b200 random-weights CONFIG_JSON OUT_DIR [--seed S] [--std 0.02]
 
+``run --cpu`` runs the float32 CPU reference (``hi_b200/engine/cpu_reference.py``), as the
+reference's ``--execution cpu-reference`` does (crates/hi-cuda/src/lib.rs:205-226).
 ``run`` is the counterpart of ``hi-local qwen-cpu``: token ids in, pretty JSON out with the same
 fields (crates/hi-cuda/src/qwen_cpu.rs:62-81); ``--top-k`` is the number of top logits shown,
 as there. There is no ``serve``: servers are outside this engine.
@@ -49,6 +51,8 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--max-active-requests", type=int, default=None)
     r.add_argument("--max-batched-tokens", type=int, default=8192)
     r.add_argument("--kv-page-size", type=int, default=64)
+    r.add_argument("--cpu", action="store_true",
+                   help="run the float32 CPU reference (plain C++ loops, whole sequences, no GPU) instead of the engine")
     r.add_argument("--random-weights", action="store_true",
                    help="MODEL_PATH is a config.json (or a folder with one); weights are seeded random numbers")
     r.add_argument("--weights-seed", type=int, default=0)
@@ -111,6 +115,8 @@ def cmd_run(args) -> int:
     tokens = parse_token_ids(text)
     if not tokens:
         raise SystemExit("--tokens must include at least one token id")
+    if args.cpu:
+        return _run_on_cpu(args, tokens)
     import torch
 
     from .engine.core import StepEntry
@@ -153,6 +159,38 @@ def cmd_run(args) -> int:
     }
     if args.include_logits:
         result["logits"] = logits.cpu().tolist()
+    print(json.dumps(result, indent=2))
+    return 0
+
+
+def _run_on_cpu(args, tokens: List[int]) -> int:
+    """``run --cpu``: the same JSON from the float32 CPU reference."""
+    import numpy as np
+
+    from .engine.cpu_reference import CpuReference
+    from .sampling.sampler import SamplingParams
+
+    if args.random_weights:
+        raise SystemExit("--cpu reads a model folder; write one with `random-weights` first")
+    if args.dtype != "float32":
+        print("note: the CPU reference computes in float32 whatever --dtype says", file=sys.stderr)
+    ref = CpuReference.from_dir(args.model_path)
+    row = ref.forward(tokens, want=[len(tokens) - 1])[0].numpy()
+    k = min(max(args.top_k, 0), row.size)
+    order = np.lexsort((np.arange(row.size), -row))[:k]
+    generated: List[int] = []
+    if args.max_tokens > 0:
+        generated = ref.generate(tokens, args.max_tokens, SamplingParams(
+            max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p, seed=args.seed),
+            eos_token_ids=ref.model.spec.eos_token_ids)
+    result = {
+        "backend": "hi_b200-cpu-reference-float32", "input_tokens": tokens, "next_token": int(np.argmax(row)),
+        "next_text": "", "generated_tokens": generated, "generated_text": "",
+        "top_logits": [{"token_id": int(i), "token": None, "logit": float(row[i])} for i in order],
+        "logit_count": int(row.size),
+    }
+    if args.include_logits:
+        result["logits"] = row.tolist()
     print(json.dumps(result, indent=2))
     return 0
 

@@ -122,6 +122,39 @@ int hbh_sched_queue(void* sched, int which, int64_t* out, int cap);    // 0 wait
 int64_t hbh_sched_counter(void* sched, int what);
 void hbh_sched_forget(void* sched, int64_t request);           // drop the record of a finished request
 
+// ---- the CPU reference: a whole-sequence float32 forward in plain loops (cpu_forward.cpp)
+#define HBH_CPU_ATTENTION 1
+#define HBH_CPU_DENSE 1
+#define HBH_CPU_EXPERTS 2
+typedef struct {
+  int hidden, vocab;
+  float final_eps;
+  const float* embedding;     // [vocab, hidden]
+  const float* final_norm;    // [hidden]
+  const float* head;          // [vocab, hidden] (the embedding again when the head is tied)
+} hbh_cpu_model;
+typedef struct {
+  int mixer;                  // HBH_CPU_ATTENTION
+  int heads, kv_heads, head_dim;
+  int chunk, sliding;         // 0 = every earlier key
+  int interleaved, qk_norm, temperature;
+  float scale, qk_eps, floor_scale, attn_scale, norm_eps;
+  const float* inv_freq;      // [head_dim / 2] or null: no rotation
+  const float *norm_mixer, *norm_feed_forward;          // [hidden]
+  const float *wq, *wk, *wv, *wo, *bq, *bk, *bv, *bo;    // [out, in]; biases may be null
+  int feed_forward;           // HBH_CPU_DENSE or HBH_CPU_EXPERTS
+  int inter, experts, top_k, shared_inter;
+  const float *w_gate, *w_up, *w_down;                  // dense: [inter, hidden] x2, [hidden, inter]; experts: stacked
+  const float* router;        // [experts, hidden]
+  const float *shared_gate, *shared_up, *shared_down;   // null: no shared expert
+  const int* forced_ids;      // [tokens, top_k] choices to take instead of the router's own, or null
+} hbh_cpu_layer;
+// Logits [n_want, vocab] at positions want[] of ONE sequence of n_tokens tokens run whole through the
+// layers in the order schedule[] names them. router_ids (or null) receives the experts chosen,
+// [routed schedule entries, n_tokens, top_k].
+int hbh_cpu_forward(const hbh_cpu_model* model, const hbh_cpu_layer* layers, const int* schedule, int n_schedule,
+                    const int* tokens, int n_tokens, const int* want, int n_want, float* logits, int* router_ids);
+
 // ---- seeded random weights (the same bits as the device kernel hb_random_normal)
 // out[i] = value of element first + i of the tensor with `key`, i < n; scale = std / (sigma * 2^24)
 int hbh_random_normal(float* out, int64_t n, int64_t first, uint64_t key, float scale);

@@ -97,6 +97,7 @@ _SIGNATURES = {
     "hbh_sched_request_stat": (L, [P, L, I]), "hbh_sched_queue": (I, [P, I, P, I]), "hbh_sched_counter": (L, [P, I]),
     "hbh_sched_forget": (None, [P, L]),
     "hbh_random_normal": (I, [P, L, L, ctypes.c_uint64, ctypes.c_float]),
+    "hbh_cpu_forward": (I, [P, P, P, I, P, I, P, I, P, P]),
 }
 
 # the C interface's codes (hi_b200/csrc/host/runtime.h)

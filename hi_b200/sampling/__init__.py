@@ -1,3 +1,3 @@
-from .sampler import DEFAULT_SEED, Lcg, SamplingParams, ranked_sample, sample
+from .sampler import DEFAULT_SEED, Lcg, SamplingParams, ranked_sample, sample, sample_on_host
 
-__all__ = ["DEFAULT_SEED", "Lcg", "SamplingParams", "ranked_sample", "sample"]
+__all__ = ["DEFAULT_SEED", "Lcg", "SamplingParams", "ranked_sample", "sample", "sample_on_host"]

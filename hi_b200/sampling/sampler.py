@@ -88,6 +88,25 @@ def ranked_sample(row: np.ndarray, temperature: float, top_p: float, top_k: Opti
     return int(np.argmax(row))
 
 
+def sample_on_host(row: np.ndarray, params: SamplingParams, rng: Lcg) -> int:
+    """One token from one row of float32 logits on the host, by the rules of the kernels: the
+    largest logit (the lowest id on ties) when greedy; temperature alone: weights exp(l/T - max)
+    walked in vocabulary order, the first id whose running sum exceeds u * total
+    (crates/hi-cuda/src/kernels.cu:7327-7352); top-k / top-p: :func:`ranked_sample`. Draws one
+    uniform from ``rng`` unless greedy."""
+    row = np.asarray(row, dtype=np.float32)
+    if params.greedy:
+        return int(np.argmax(row))                    # numpy returns the first of equal maxima
+    u = rng.next_f32()
+    if params.ranked(row.size):
+        return ranked_sample(row, params.temperature, params.top_p, params.top_k, u)
+    z = row / np.float32(params.temperature)
+    w = np.exp(z - z.max(), dtype=np.float32)
+    cum = np.cumsum(w, dtype=np.float32)
+    i = int(np.searchsorted(cum, np.float32(u) * cum[-1], side="right"))
+    return min(i, int(np.nonzero(w > 0)[0][-1]))
+
+
 def sample_on_device(logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[Lcg]
                      ) -> Optional[torch.Tensor]:
     """One token for each row of float32 ``logits`` [R, V], left on the device as int32 [R] (no

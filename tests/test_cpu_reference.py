@@ -1,0 +1,100 @@
+"""The CPU reference (plain C++ loops in the host runtime, ``hi_b200/engine/cpu_reference.py``)
+against the test-suite's plain model: two statements of the formulas, written apart, that must
+agree on whole sequences of the four tiny configurations, with forced expert choices, with a
+schedule that names a layer twice, in greedy and in seeded sampled generation, and through
+``python -m hi_b200 run --cpu``. No GPU."""
+import dataclasses
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import harness as h
+import plain_llama4 as plain
+from test_cli import run_cli
+
+TOL = 1e-5     # relative to the largest |logit|: the two add in different orders, both in float32
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_the_two_plain_implementations_agree(name, model_dirs):
+    from hi_b200.engine.cpu_reference import CpuReference
+
+    cfg, mdir = model_dirs[name]
+    w = h.read_weights(mdir)
+    ref = CpuReference.from_dir(mdir)
+    for n, seed in ((1, 0), (37, 1), (120, 2)):
+        toks = h.random_tokens(cfg, n, seed=seed)
+        records = {}
+        want = plain.forward(cfg, w, toks, record=lambda nm, ids, gap: records.__setitem__(nm, (ids, gap)))
+        got, routing = ref.forward(toks, return_routing=True)
+        assert h.rel_err(got, want) <= TOL, f"{name}, {n} tokens"
+        for nm, (ids, gap) in records.items():
+            differs = (ids.sort(-1).values != routing[nm].long().sort(-1).values).any(-1)
+            assert not bool((differs & (gap > 1e-4)).any()), f"{name} {nm}: expert choices differ"
+        rows = [0, n - 1]
+        assert torch.equal(ref.forward(toks, want=rows), got[rows])
+
+
+def test_forced_choices_and_a_layer_named_twice(model_dirs):
+    from hi_b200.config.registry import load_architecture
+    from hi_b200.engine.cpu_reference import CpuReference
+    from hi_b200.parts.model import Model
+    from hi_b200.parts.spec import ScheduleEntry
+    from hi_b200.weights.loader import load_from_dir
+
+    cfg, mdir = model_dirs["B"]
+    w = h.read_weights(mdir)
+    toks = h.random_tokens(cfg, 50, seed=5)
+    ref = CpuReference.from_dir(mdir)
+    g = torch.Generator().manual_seed(3)
+    forced = {f"model.layers.{i}.feed_forward": torch.stack([torch.randperm(8, generator=g)[:2] for _ in toks])
+              for i in (1, 3, 5)}
+    want = plain.forward(cfg, w, toks, forced_routing=forced)
+    got, taken = ref.forward(toks, forced_routing=forced, return_routing=True)
+    assert h.rel_err(got, want) <= TOL
+    assert all(torch.equal(taken[n].long(), forced[n]) for n in forced)
+    with pytest.raises(ValueError, match="refused"):
+        ref.forward(toks, forced_routing={"model.layers.1.feed_forward": torch.full((50, 2), 8)})
+    with pytest.raises(ValueError, match="refused"):
+        ref.forward([0, 515])
+    # the order of layers is data here too
+    cfg_a, mdir_a = model_dirs["A"]
+    arch, typed, _ = load_architecture(mdir_a)
+    order = [0, 1, 0, 1, 1]
+    spec = dataclasses.replace(arch.build_spec(typed), schedule=tuple(ScheduleEntry(layer=l, cache=i) for i, l in enumerate(order)))
+    model = Model(spec, torch.float32, "cpu")
+    load_from_dir(model, mdir_a, arch.normalize_tensor_name, arch.derive_tensors)
+    toks = h.random_tokens(cfg_a, 40, seed=6)
+    assert h.rel_err(CpuReference(model).forward(toks), plain.forward(cfg_a, h.read_weights(mdir_a), toks, schedule=order)) <= TOL
+
+
+def test_generation_on_the_cpu_and_the_command_line(model_dirs):
+    from hi_b200.engine.cpu_reference import CpuReference
+    from hi_b200.sampling import SamplingParams
+
+    cfg, mdir = model_dirs["A"]
+    w = h.read_weights(mdir)
+    prompt = h.random_tokens(cfg, 12, seed=9)
+    ref = CpuReference.from_dir(mdir)
+    out = ref.generate(prompt, 6)
+    seq = list(prompt)
+    for tok in out:
+        assert tok == int(plain.forward(cfg, w, seq)[-1].argmax())
+        seq.append(tok)
+    # sampled: the plain sampler with the same generator gives the same tokens
+    sp = SamplingParams(max_tokens=6, temperature=0.9, seed=4, ignore_eos=True)
+    sampled = ref.generate(prompt, 6, sp)
+    rng, seq = plain.Lcg(4), list(prompt)
+    for tok in sampled:
+        assert tok == plain.sample(plain.forward(cfg, w, seq)[-1], 0.9, 1.0, 0, rng.next_f32())
+        seq.append(tok)
+    res = run_cli("run", mdir, "--cpu", "--tokens", ",".join(map(str, prompt)), "--max-tokens", "6", "--top-k", "3",
+                  "--dtype", "float32", "--include-logits")
+    assert res.returncode == 0, res.stderr[-2000:]
+    js = json.loads(res.stdout)
+    assert js["backend"] == "hi_b200-cpu-reference-float32" and js["generated_tokens"] == out
+    last = plain.forward(cfg, w, prompt)[-1]
+    assert js["next_token"] == int(last.argmax()) == js["top_logits"][0]["token_id"] and js["logit_count"] == 256
+    assert np.allclose(js["logits"], last.numpy(), atol=1e-4)

@@ -305,6 +305,21 @@ def test_a_checkpoint_with_fused_experts_gives_the_same_logits(tmp_path, model_d
     assert torch.equal(logits[0], logits[1])
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_the_float32_engine_against_the_cpu_reference(name, model_dirs):
+    """The engine's float32 path (CUDA kernels, paged cache, portions) against the product tree's own
+    CPU reference (plain C++ loops, whole sequence): within 1e-4 of the largest |logit|."""
+    from hi_b200.engine.cpu_reference import CpuReference
+
+    cfg, mdir = model_dirs[name]
+    toks = h.random_tokens(cfg, 110, seed=33)
+    want = CpuReference.from_dir(mdir).forward(toks)
+    eng = engine_for(mdir, "float32", 8)
+    got, _ = h.replay_in_process(eng, h.trace_portions({"x": toks}))
+    out = torch.tensor(np.stack([got["x"][p] for p in range(len(toks))]))
+    assert h.rel_err(out, want) <= 1e-4
+
+
 # --------------------------------------------------------------------------- a toy mixer with state
 def test_toy_mixer_with_state_registers_builds_and_steps(model_dirs):
     """A mixer defined here, with per-request state of fixed size (a running mean of a projection),
