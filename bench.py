@@ -526,6 +526,27 @@ def case_decode_attention(batch=8, context=8192, page=64):
     torch.cuda.synchronize()
 
 
+def case_decode_attention_fused(batch=8, context=8192, page=64):
+    """The one-launch form: q/k/v encoding, cache append, attention and merge, on a rotary chunked layer's settings."""
+    import torch
+
+    from hi_b200.kernels import ops
+
+    nh, nkv, hd = 40, 8, 128
+    blocks = -(-context // page)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    kp = torch.randn(batch * blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    vp = torch.randn(batch * blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    bt = torch.randperm(batch * blocks, device=DEV, generator=g).to(torch.int32).view(batch, blocks).contiguous()
+    qkv = torch.randn(batch, (nh + 2 * nkv) * hd, device=DEV, generator=g).to(torch.bfloat16)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+    sot = torch.arange(batch, dtype=torch.int32, device=DEV)
+    inv = torch.rand(hd // 2, device=DEV, generator=g)
+    for _ in range(3):
+        ops.decode_attention_fused(qkv, nh, nkv, hd, pos, inv, False, True, 1e-6, None, sot, bt, kp, vp, 8192, 0, hd ** -0.5, context)
+    torch.cuda.synchronize()
+
+
 def _experts(experts, rows):
     import torch
 
@@ -625,7 +646,7 @@ def case_prefill_step(tokens=2048, layers=2):
     torch.cuda.synchronize()
 
 
-CASES = {"decode_attention": case_decode_attention, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
+CASES = {"decode_attention": case_decode_attention, "decode_attention_fused": case_decode_attention_fused, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
          "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step}
 
 

@@ -11,11 +11,14 @@ extern "C" {
 int hb_feed_tokens(int* tokens, const int* dst, const int* src, const int* sampled, int n, cudaStream_t stream);
 int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int n, int hidden,
                     int vocab, cudaStream_t stream);
+// routed_weight (or null): [n * top_k] factors of the routed rows in the sum (a score that scales the
+// experts' outputs)
 int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed, const int* slot_of_entry,
-                   int top_k, const void* w, int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
+                   const float* routed_weight, int top_k, const void* w, int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
                    int rows, int hidden, float eps, cudaStream_t stream);
 int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream);
-int hb_moe_combine(const float* y, const int* slot_of_entry, const void* shared, int shared_dtype, float* out,
+int hb_moe_combine(const float* y, const int* slot_of_entry, const float* routed_weight, const void* shared,
+                   int shared_dtype, float* out,
                    int n, int hidden, int top_k, cudaStream_t stream);
 
 int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, int rot_pairs, int interleaved, int qk_norm,
@@ -42,6 +45,15 @@ int hb_attention_decode_tma(const void* q, const void* k_pages, const void* v_pa
                             int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int split_size,
                             int max_splits, float* part_acc, float* part_ml, int* status, cudaStream_t stream);
 
+// hb_qkv_post, hb_attention_decode_tma and hb_attention_merge in one launch (attention_decode_tma.cu)
+int hb_attention_decode_fused(const void* qkv, const float* inv_freq, int rot_pairs, int interleaved, int qk_norm,
+                              float qk_eps, int temp_on, float floor_scale, float attn_scale, void* k_pages,
+                              void* v_pages, int n_pages, const int* block_table, int table_stride,
+                              const int* seq_of_token, const int* positions, void* out, int n_tokens, int nh, int nkv,
+                              int hd, int page_size, int chunk, int window, float scale, int split_size,
+                              int max_splits, float* part_acc, float* part_ml, int* counters, int* status,
+                              cudaStream_t stream);
+
 int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                          int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_seqs,
                          int max_new, int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,
@@ -52,12 +64,14 @@ int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pa
                             int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
                             int window, float scale, int skip_single, int* status, cudaStream_t stream);
 
+// mode: bit 0 = scores are the softmax over all experts (clear: the sigmoid of the chosen logit),
+// bit 1 = the chosen scores are divided by their sum
 int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
-                   int top_k, float* logits_out, int* ids, float* scores, cudaStream_t stream);
+                   int top_k, int mode, float* logits_out, int* ids, float* scores, cudaStream_t stream);
 int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
                 int* slot_of_entry, int* active, cudaStream_t stream);
 int hb_router_plan(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts, int top_k,
-                   float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry, int* slot_of_entry,
+                   int mode, float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry, int* slot_of_entry,
                    int* active, int* counter, cudaStream_t stream);
 int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,
                    const void* w_up, const int* offsets, const int* active, int experts, const float* scores,

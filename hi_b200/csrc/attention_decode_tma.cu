@@ -55,7 +55,8 @@ struct Args {
 // What the fused form needs beside Args.
 struct Fuse {
   const __nv_bfloat16* qkv;      // [n_tokens, (nh + 2 nkv) * head_dim]: q heads, k heads, v heads
-  const float* inv_freq;         // [head_dim / 2], or null: no rotation
+  const float* inv_freq;         // [rot_pairs], or null: no rotation
+  int rot_pairs;                 // the first 2 * rot_pairs dims of a head rotate (a multiple of 8 pairs)
   __nv_bfloat16* k_pages;
   __nv_bfloat16* v_pages;
   int* counters;                 // [n_tokens * nkv], zero between launches
@@ -64,20 +65,23 @@ struct Fuse {
 };
 
 // One head of the q/k/v row as qkv_post.cu encodes it: head_dim / 16 neighbouring lanes, each with
-// 8 rotation pairs (a[i], b[i]): dims (j0 + i, head_dim / 2 + j0 + i), or (2 (j0 + i), 2 (j0 + i) + 1)
-// when interleaved. kind 0 = query (rotation, norm, temperature), 1 = key (rotation, norm),
+// 8 rotation pairs (a[i], b[i]): dims (j0 + i, rot_pairs + j0 + i), or (2 (j0 + i), 2 (j0 + i) + 1)
+// when interleaved; lanes past the rotated dims own 16 consecutive elements that pass through. kind 0 = query (rotation, norm, temperature), 1 = key (rotation, norm),
 // 2 = value (as it is). Every lane of the warp must call it (the norm's sum goes over lanes).
 // Returns the head's 16 values of this lane as two 16-byte chunks and the dims they start at.
 template <int HD>
 __device__ __forceinline__ void encode_head(const __nv_bfloat16* src, int kind, bool active, int sub, const Fuse& f,
                                             const float* cs_s, const float* sn_s, int pos, uint4& c0, uint4& c1,
                                             int& d0, int& d1) {
-  constexpr int HALF = HD / 2, LPH = HD / 16;
+  constexpr int LPH = HD / 16;
+  const int HALF = f.rot_pairs;
   const int j0 = sub * 8;
+  const bool rotates = j0 < f.rot_pairs;
+  const bool consecutive = f.interleaved || !rotates;
   float a[8], b[8];
   float ss = 0.f;
   if (active) {
-    if (f.interleaved) {
+    if (consecutive) {
       float lo[8], hi[8];
       hb::load8(src + 2 * j0, lo);
       hb::load8(src + 2 * j0 + 8, hi);
@@ -92,7 +96,7 @@ __device__ __forceinline__ void encode_head(const __nv_bfloat16* src, int kind, 
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      if (kind != 2 && f.inv_freq != nullptr) {
+      if (kind != 2 && f.inv_freq != nullptr && rotates) {
         const float sn = sn_s[j0 + i], cs = cs_s[j0 + i];
         const float ra = a[i] * cs - b[i] * sn;
         const float rb = b[i] * cs + a[i] * sn;
@@ -106,7 +110,7 @@ __device__ __forceinline__ void encode_head(const __nv_bfloat16* src, int kind, 
   if (kind != 2 && f.qk_norm) mul = rsqrtf(ss / (float)HD + f.qk_eps);
   if (kind == 0 && f.temp_on) mul *= logf(floorf(((float)pos + 1.f) / f.floor_scale) + 1.f) * f.attn_scale + 1.f;
   float lo[8], hi[8];
-  if (f.interleaved) {
+  if (consecutive) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       lo[2 * i] = a[i] * mul; lo[2 * i + 1] = b[i] * mul;
@@ -213,7 +217,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if constexpr (FUSED) {
     constexpr int LPH = HD / 16, HPW = 32 / LPH;
     if (f.inv_freq != nullptr)
-      for (int j = tid; j < HD / 2; j += NWARPS * 32) sincosf((float)pos * f.inv_freq[j], &sn_s[j], &cs_s[j]);
+      for (int j = tid; j < f.rot_pairs; j += NWARPS * 32) sincosf((float)pos * f.inv_freq[j], &sn_s[j], &cs_s[j]);
     for (int c = tid; c < (ROWS - G) * CHUNKS; c += NWARPS * 32)      // the tile's rows past the group are zeros
       *reinterpret_cast<uint4*>(q_s + (G + c / CHUNKS) * STRIDE + (c % CHUNKS) * 8) = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();                               // sines and cosines; the barriers are initialised
@@ -554,13 +558,13 @@ extern "C" int hb_attention_decode_tma(const void* q, const void* k_pages, const
 }
 
 // The fused form: `qkv` [n_tokens, (nh + 2 nkv) * hd] is the q/k/v projection's output; the kernel
-// encodes q, k and v as hb_qkv_post does (inv_freq [hd / 2] or null; pairs (j, j + hd/2) or
+// encodes q, k and v as hb_qkv_post does (inv_freq [rot_pairs] or null; pairs (j, j + rot_pairs) or
 // (2j, 2j + 1); weightless norm; temperature on q), appends the token's key and value to its page,
 // attends, and combines its own splits: `counters` holds n_tokens * nkv ints that are zero before
 // the call and zero after it. With `counters` null the splits are left in part_acc / part_ml for
 // hb_attention_merge, as hb_attention_decode_tma leaves them. Same shapes and refusals as hb_attention_decode_tma; every token is
 // one decode row whose page the host has reserved.
-extern "C" int hb_attention_decode_fused(const void* qkv, const float* inv_freq, int interleaved, int qk_norm,
+extern "C" int hb_attention_decode_fused(const void* qkv, const float* inv_freq, int rot_pairs, int interleaved, int qk_norm,
                                          float qk_eps, int temp_on, float floor_scale, float attn_scale, void* k_pages,
                                          void* v_pages, int n_pages, const int* block_table, int table_stride,
                                          const int* seq_of_token, const int* positions, void* out, int n_tokens,
@@ -573,6 +577,8 @@ extern "C" int hb_attention_decode_fused(const void* qkv, const float* inv_freq,
     return HB_ERR_BAD_ARG;
   if (temp_on && !(floor_scale > 0.f)) return HB_ERR_BAD_ARG;
   if (max_splits > 1 && (!part_acc || !part_ml)) return HB_ERR_BAD_ARG;
+  if (!inv_freq) rot_pairs = 0;
+  if (rot_pairs < 0 || 2 * rot_pairs > hd || rot_pairs % 8 != 0) return HB_ERR_UNSUPPORTED;
   if (nh / nkv > ROWS || n_tokens > 65535 || nkv > 65535) return HB_ERR_UNSUPPORTED;
   if (window > 0 || chunk % TILE != 0) return HB_ERR_UNSUPPORTED;
   if (!(page_size == 16 || page_size == 32 || page_size % TILE == 0)) return HB_ERR_UNSUPPORTED;
@@ -580,7 +586,7 @@ extern "C" int hb_attention_decode_fused(const void* qkv, const float* inv_freq,
   if (n_tokens == 0) return HB_OK;
   Args a{nullptr, block_table, seq_of_token, positions, (__nv_bfloat16*)out, part_acc, part_ml, status,
          table_stride, nh, nkv, page_size, chunk, split_size, max_splits, page_size < TILE ? page_size : TILE, scale};
-  Fuse f{(const __nv_bfloat16*)qkv, inv_freq, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, counters,
+  Fuse f{(const __nv_bfloat16*)qkv, inv_freq, rot_pairs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, counters,
          interleaved, qk_norm, temp_on, qk_eps, floor_scale, attn_scale};
   if (hd == 128) return launch<128, true>(k_pages, v_pages, n_pages, n_tokens, a, f, stream);
   if (hd == 64) return launch<64, true>(k_pages, v_pages, n_pages, n_tokens, a, f, stream);

@@ -53,7 +53,7 @@ __global__ void embed_gather_kernel(const void* table, int table_dtype, const in
 //   s = x[src] (+ delta[src]);  if no row_map: x[src] = s  (the residual sum, float32)
 //   y[r] = s * rsqrt(mean(s^2) + eps) * w     (crates/hi-cuda/src/kernels.cu:61-77)
 __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype, const float* routed,
-                                   const int* slot_of_entry, int top_k, const void* w,
+                                   const int* slot_of_entry, const float* routed_weight, int top_k, const void* w,
                                    int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
                                    int hidden, float eps) {
   __shared__ float scratch[33];
@@ -65,7 +65,8 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
     float s = x[src * hidden + j];
     if (delta) s += load_any(delta, delta_dtype, src * hidden + j);
     if (routed)
-      for (int q = 0; q < top_k; ++q) s += routed[(size_t)slot_of_entry[src * top_k + q] * hidden + j];
+      for (int q = 0; q < top_k; ++q)
+        s += routed[(size_t)slot_of_entry[src * top_k + q] * hidden + j] * (routed_weight ? routed_weight[src * top_k + q] : 1.f);
     row[j] = s;
     ss += s * s;
   }
@@ -88,7 +89,7 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
 template <int NG>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __restrict__ delta, int delta_dtype,
                                        const float* __restrict__ routed, const int* __restrict__ slot_of_entry,
-                                       int top_k, const void* __restrict__ w, int w_dtype, void* __restrict__ y,
+                                       const float* __restrict__ routed_weight, int top_k, const void* __restrict__ w, int w_dtype, void* __restrict__ y,
                                        int y_dtype, float* __restrict__ y_f32, const int* __restrict__ row_map,
                                        int hidden, float eps) {
   __shared__ float scratch[33];
@@ -97,8 +98,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
   float4 v[NG], wv[NG];
   float ss = 0.f;
   int slots[8];
+  float factor[8];
   if (routed)
-    for (int j = 0; j < top_k; ++j) slots[j] = slot_of_entry[src * top_k + j];
+    for (int j = 0; j < top_k; ++j) {
+      slots[j] = slot_of_entry[src * top_k + j];
+      factor[j] = routed_weight ? routed_weight[src * top_k + j] : 1.f;
+    }
 #pragma unroll
   for (int g = 0; g < NG; ++g) {
     const int idx = (threadIdx.x + g * blockDim.x) * 4;
@@ -113,7 +118,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
       if (routed) {
         for (int j = 0; j < top_k; ++j) {
           const float4 d = *reinterpret_cast<const float4*>(routed + (size_t)slots[j] * hidden + idx);
-          a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+          a.x += d.x * factor[j]; a.y += d.y * factor[j]; a.z += d.z * factor[j]; a.w += d.w * factor[j];
         }
       }
       v[g] = a;
@@ -150,13 +155,13 @@ __global__ void swiglu_kernel(const void* in, void* out, int dtype, size_t rows,
 
 // out[t, :] = shared[t, :] + sum_j y[slot_of_entry[t*k + j], :]   in rank order, no atomics
 // (crates/hi-cuda/src/kernels.cu:10661-10680; models.rs:6099 adds the shared expert).
-__global__ void moe_combine_kernel(const float* y, const int* slot_of_entry, const void* shared,
-                                   int shared_dtype, float* out, int hidden, int top_k) {
+__global__ void moe_combine_kernel(const float* y, const int* slot_of_entry, const float* routed_weight,
+                                   const void* shared, int shared_dtype, float* out, int hidden, int top_k) {
   const int t = blockIdx.x;
   for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
     float s = shared ? load_any(shared, shared_dtype, (size_t)t * hidden + j) : 0.f;
     for (int r = 0; r < top_k; ++r)
-      s += y[(size_t)slot_of_entry[t * top_k + r] * hidden + j];
+      s += y[(size_t)slot_of_entry[t * top_k + r] * hidden + j] * (routed_weight ? routed_weight[t * top_k + r] : 1.f);
     out[(size_t)t * hidden + j] = s;
   }
 }
@@ -193,7 +198,7 @@ extern "C" int hb_feed_tokens(int* tokens, const int* dst, const int* src, const
 }
 
 extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed,
-                              const int* slot_of_entry, int top_k, const void* w, int w_dtype, void* y, int y_dtype,
+                              const int* slot_of_entry, const float* routed_weight, int top_k, const void* w, int w_dtype, void* y, int y_dtype,
                               float* y_f32, const int* row_map, int rows, int hidden, float eps,
                               cudaStream_t stream) {
   if (!x || !y || rows < 0 || hidden <= 0 || !dtype_ok(y_dtype) || (delta && !dtype_ok(delta_dtype)) ||
@@ -206,7 +211,7 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
     const int threads = groups >= 512 ? 512 : ((groups + 31) / 32) * 32;
     const int ng = (groups + threads - 1) / threads;
 #define HB_NORM_LAUNCH(NG)                                                                                   \
-    add_rmsnorm_vec_kernel<NG><<<rows, threads, 0, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, top_k, \
+    add_rmsnorm_vec_kernel<NG><<<rows, threads, 0, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, routed_weight, top_k, \
                                                              w, w_dtype, y, y_dtype, y_f32, row_map, hidden, eps)
     if (ng <= 1) HB_NORM_LAUNCH(1);
     else if (ng <= 2) HB_NORM_LAUNCH(2);
@@ -223,7 +228,7 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = hidden >= 2048 ? 512 : 256;
-  add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, top_k, w, w_dtype,
+  add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, routed_weight, top_k, w, w_dtype,
                                                       y, y_dtype, y_f32, row_map, hidden, eps);
   HB_LAUNCH_CHECK();
   return HB_OK;
@@ -293,13 +298,13 @@ extern "C" int hb_swiglu(const void* in, void* out, int dtype, int rows, int int
   return HB_OK;
 }
 
-extern "C" int hb_moe_combine(const float* y, const int* slot_of_entry, const void* shared,
+extern "C" int hb_moe_combine(const float* y, const int* slot_of_entry, const float* routed_weight, const void* shared,
                               int shared_dtype, float* out, int n, int hidden, int top_k,
                               cudaStream_t stream) {
   if (!y || !slot_of_entry || !out || n < 0 || hidden <= 0 || top_k <= 0 || (shared && !dtype_ok(shared_dtype)))
     return HB_ERR_BAD_ARG;
   if (n == 0) return HB_OK;
-  moe_combine_kernel<<<n, 256, 0, stream>>>(y, slot_of_entry, shared, shared_dtype, out, hidden, top_k);
+  moe_combine_kernel<<<n, 256, 0, stream>>>(y, slot_of_entry, routed_weight, shared, shared_dtype, out, hidden, top_k);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

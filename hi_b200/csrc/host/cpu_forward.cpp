@@ -67,8 +67,7 @@ void swiglu(const float* x, const float* wg, const float* wu, const float* wd, i
   }
 }
 
-void rotate(float* v, int hd, int pos, const float* inv_freq, int interleaved) {
-  const int half = hd / 2;
+void rotate(float* v, int half, int pos, const float* inv_freq, int interleaved) {   // the first 2 * half dims
   for (int j = 0; j < half; ++j) {
     const float ang = (float)pos * inv_freq[j];
     const float c = cosf(ang), s = sinf(ang);
@@ -109,7 +108,7 @@ extern "C" int hbh_cpu_forward(const hbh_cpu_model* m, const hbh_cpu_layer* laye
       linear(z.data(), L.wv, L.bv, H, nkv * hd, &v[(size_t)t * nkv * hd]);
       for (int h = 0; h < nh + nkv; ++h) {
         float* head = h < nh ? qt + (size_t)h * hd : kt + (size_t)(h - nh) * hd;
-        if (L.inv_freq) rotate(head, hd, t, L.inv_freq, L.interleaved);
+        if (L.inv_freq) rotate(head, L.rot_pairs, t, L.inv_freq, L.interleaved);
         float mul = 1.f;
         if (L.qk_norm) {
           float ss = 0.f;

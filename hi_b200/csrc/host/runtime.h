@@ -139,7 +139,8 @@ typedef struct {
   int chunk, sliding;         // 0 = every earlier key
   int interleaved, qk_norm, temperature;
   float scale, qk_eps, floor_scale, attn_scale, norm_eps;
-  const float* inv_freq;      // [head_dim / 2] or null: no rotation
+  const float* inv_freq;      // [rot_pairs] or null: no rotation
+  int rot_pairs;              // the first 2 * rot_pairs dims of a head rotate
   const float *norm_mixer, *norm_feed_forward;          // [hidden]
   const float *wq, *wk, *wv, *wo, *bq, *bk, *bv, *bo;    // [out, in]; biases may be null
   int feed_forward;           // HBH_CPU_DENSE or HBH_CPU_EXPERTS

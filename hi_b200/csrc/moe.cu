@@ -82,10 +82,23 @@ __device__ __forceinline__ void router_part_range(int hidden, int part, int& run
   run_end = min(runs, run_begin + per);
 }
 
-// The k largest of a row of logits (ties to the lower id) and their sigmoids. THROUGH_L2: the row
-// was written by other blocks of this launch and is read past L1.
+// The k largest of a row of logits (ties to the lower id) and their scores. THROUGH_L2: the row
+// was written by other blocks of this launch and is read past L1. `mode`: bit 0 clear = the sigmoid
+// of the chosen logit (crates/hi-mlx/src/models.rs:6090), set = its softmax over all experts
+// (the donor kernel's two scoring rules: crates/hi-cuda/src/kernels.cu:536-546); bit 1 = the chosen
+// scores are divided by their sum.
+constexpr int ROUTER_SOFTMAX = 1, ROUTER_RENORMALIZE = 2;
+
 template <bool THROUGH_L2 = false>
-__device__ __forceinline__ void router_select(const float* row, int experts, int top_k, int* ids, float* scores) {
+__device__ __forceinline__ void router_select(const float* row, int experts, int top_k, int mode, int* ids,
+                                              float* scores) {
+  float mx = -INFINITY, denom = 1.f;
+  if (mode & ROUTER_SOFTMAX) {
+    for (int e = 0; e < experts; ++e) mx = fmaxf(mx, THROUGH_L2 ? __ldcg(row + e) : row[e]);
+    denom = 0.f;
+    for (int e = 0; e < experts; ++e) denom += expf((THROUGH_L2 ? __ldcg(row + e) : row[e]) - mx);
+  }
+  float chosen = 0.f;
   for (int r = 0; r < top_k; ++r) {
     int best = -1;
     float bv = 0.f;
@@ -97,8 +110,11 @@ __device__ __forceinline__ void router_select(const float* row, int experts, int
       if (best < 0 || v > bv) { best = e; bv = v; }  // strict '>' keeps the lowest id on ties
     }
     ids[r] = best;
-    scores[r] = 1.f / (1.f + expf(-bv));
+    scores[r] = (mode & ROUTER_SOFTMAX) ? expf(bv - mx) / denom : 1.f / (1.f + expf(-bv));
+    chosen += scores[r];
   }
+  if (mode & ROUTER_RENORMALIZE)
+    for (int r = 0; r < top_k; ++r) scores[r] /= chosen;
 }
 
 // Few tokens: a block takes one token and ROUTER_FEW_EXP experts, a warp one part of K of one
@@ -111,7 +127,7 @@ constexpr int ROUTER_FEW_EXP = 4;
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(ROUTER_FEW_EXP * ROUTER_KPARTS * 32)
 router_few_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int n, int hidden, int experts, int top_k,
-                  float* logits, int* ids, float* scores, int* __restrict__ offsets,
+                  int mode, float* logits, int* ids, float* scores, int* __restrict__ offsets,
                   int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry, int* __restrict__ active,
                   int* counter) {
   __shared__ float partial[ROUTER_FEW_EXP][ROUTER_KPARTS];
@@ -182,7 +198,7 @@ router_few_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int n, int
   int* s_ids = plan_scratch + 2 * experts;          // [n * top_k]
   for (int tok = threadIdx.x; tok < n; tok += blockDim.x) {
     int* mine = s_ids + tok * top_k;
-    router_select<true>(logits + (size_t)tok * experts, experts, top_k, mine, scores + (size_t)tok * top_k);
+    router_select<true>(logits + (size_t)tok * experts, experts, top_k, mode, mine, scores + (size_t)tok * top_k);
     for (int r = 0; r < top_k; ++r) ids[(size_t)tok * top_k + r] = mine[r];
   }
   __syncthreads();
@@ -200,7 +216,7 @@ constexpr int ROUTER_TOK = 4, ROUTER_EXP = 16;
 template <typename TW>
 __global__ void __launch_bounds__(ROUTER_KPARTS * 32)
 router_logits_tiled_kernel(const float* __restrict__ x, const TW* __restrict__ w, int n, int hidden, int experts,
-                           int top_k, float* __restrict__ logits, int* __restrict__ ids,
+                           int top_k, int mode, float* __restrict__ logits, int* __restrict__ ids,
                            float* __restrict__ scores) {
   __shared__ float partial[ROUTER_KPARTS][ROUTER_TOK][ROUTER_EXP];
   __shared__ float lg[ROUTER_TOK][ROUTER_EXP];
@@ -262,15 +278,15 @@ router_logits_tiled_kernel(const float* __restrict__ x, const TW* __restrict__ w
   __syncthreads();
   if (threadIdx.x < ROUTER_TOK && t0 + threadIdx.x < n) {
     const size_t t = t0 + threadIdx.x;
-    router_select(lg[threadIdx.x], experts, top_k, ids + t * top_k, scores + t * top_k);
+    router_select(lg[threadIdx.x], experts, top_k, mode, ids + t * top_k, scores + t * top_k);
   }
 }
 
 // Selection from stored logits, one thread per token (more experts than one block column holds).
-__global__ void router_select_kernel(const float* __restrict__ logits, int n, int experts, int top_k,
+__global__ void router_select_kernel(const float* __restrict__ logits, int n, int experts, int top_k, int mode,
                                      int* __restrict__ ids, float* __restrict__ scores) {
   const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < (size_t)n) router_select(logits + t * experts, experts, top_k, ids + t * top_k, scores + t * top_k);
+  if (t < (size_t)n) router_select(logits + t * experts, experts, top_k, mode, ids + t * top_k, scores + t * top_k);
 }
 
 // ------------------------------------------------------------------ plan
@@ -520,10 +536,11 @@ namespace {
 
 // The router, and with `counter` (an int that is zero between launches) the plan as well: in the
 // same kernel when a block takes one token, by the plan's own kernel after the tiled one.
-int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts, int top_k,
+int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts, int top_k, int mode,
                   float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry, int* slot_of_entry,
                   int* active, int* counter, cudaStream_t stream) {
-  if (!x || !w || !ids || !scores || n < 0 || hidden <= 0 || experts <= 0 || top_k <= 0 || top_k > experts)
+  if (!x || !w || !ids || !scores || n < 0 || hidden <= 0 || experts <= 0 || top_k <= 0 || top_k > experts || mode < 0 ||
+      mode > 3)
     return HB_ERR_BAD_ARG;
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
   if (n == 0) return HB_OK;
@@ -536,13 +553,13 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
     if (grid.y > 65535) return HB_ERR_UNSUPPORTED;
     if (w_dtype == HB_DTYPE_F32)
       router_logits_tiled_kernel<float><<<grid, ROUTER_KPARTS * 32, 0, stream>>>(
-          (const float*)x, (const float*)w, n, hidden, experts, top_k, logits_out, ids, scores);
+          (const float*)x, (const float*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores);
     else
       router_logits_tiled_kernel<__nv_bfloat16><<<grid, ROUTER_KPARTS * 32, 0, stream>>>(
-          (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores);
+          (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores);
     HB_LAUNCH_CHECK();
     if (grid.y > 1) {
-      router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, ids, scores);
+      router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, mode, ids, scores);
       HB_LAUNCH_CHECK();
     }
     if (counter) {
@@ -564,21 +581,21 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
   const dim3 grid(n, columns);
   if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_F32)
     router_few_kernel<float, float><<<grid, threads, smem, stream>>>(
-        (const float*)x, (const float*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets, sorted_entry,
+        (const float*)x, (const float*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets, sorted_entry,
         slot_of_entry, active, fused);
   else if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_BF16)
     router_few_kernel<float, __nv_bfloat16><<<grid, threads, smem, stream>>>(
-        (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets,
+        (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets,
         sorted_entry, slot_of_entry, active, fused);
   else if (x_dtype == HB_DTYPE_BF16 && w_dtype == HB_DTYPE_BF16)
     router_few_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, smem, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, logits_out, ids, scores, offsets,
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets,
         sorted_entry, slot_of_entry, active, fused);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();
   if (!fused) {
-    router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, ids, scores);
+    router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, mode, ids, scores);
     HB_LAUNCH_CHECK();
     if (counter) {
       moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, n * top_k, experts, offsets,
@@ -592,15 +609,15 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
 }  // namespace
 
 extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden,
-                              int experts, int top_k, float* logits_out, int* ids, float* scores,
+                              int experts, int top_k, int mode, float* logits_out, int* ids, float* scores,
                               cudaStream_t stream) {
-  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, logits_out, ids, scores, nullptr, nullptr,
+  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, mode, logits_out, ids, scores, nullptr, nullptr,
                        nullptr, nullptr, nullptr, stream);
 }
 
 // Router and plan in one call; `counter` is one int that the caller zeroed once and then leaves alone.
 extern "C" int hb_router_plan(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
-                              int top_k, float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry,
+                              int top_k, int mode, float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry,
                               int* slot_of_entry, int* active, int* counter, cudaStream_t stream) {
   if (!offsets || !sorted_entry || !slot_of_entry || !active || !counter) return HB_ERR_BAD_ARG;
   if (experts <= 0 || experts > 4096) return experts <= 0 ? HB_ERR_BAD_ARG : HB_ERR_UNSUPPORTED;
@@ -610,7 +627,7 @@ extern "C" int hb_router_plan(const void* x, int x_dtype, const void* w, int w_d
     HB_LAUNCH_CHECK();
     return HB_OK;
   }
-  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, logits_out, ids, scores, offsets,
+  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets,
                        sorted_entry, slot_of_entry, active, counter, stream);
 }
 

@@ -32,10 +32,12 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
 }
 
 // A head is taken by head_dim / 16 neighbouring lanes (padded to `lanes_per_head`, a power of
-// two): each lane owns 8 rotation pairs, which are 8 + 8 consecutive elements (pairs (j, j + hd/2))
+// two): each lane owns 8 rotation pairs, which are 8 + 8 consecutive elements (pairs (j, j + rot/2))
 // or 16 consecutive elements (pairs (2j, 2j + 1)), so every load and store is 16 bytes of
-// bfloat16 (32 of float). A block is one token and up to 8 warps of its heads; it computes the
-// token's sines and cosines once.
+// bfloat16 (32 of float). Only the first rot = 2 * rot_pairs dims of a head rotate (rot a multiple
+// of 16; rot = head_dim in Llama 4); the lanes past them own 16 consecutive elements that pass
+// through (and count in the norm). A block is one token and up to 8 warps of its heads; it
+// computes the token's sines and cosines once.
 template <typename T>
 __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ inv_freq,
                                 int rot_pairs, int interleaved, int qk_norm, float qk_eps, int temp_on,
@@ -53,7 +55,7 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
   const int head = first_head + warp * heads_per_warp + lane / lanes_per_head;
   const int sub = lane % lanes_per_head;                 // which 8 pairs of the head
   const int pos = positions[t];
-  const int half = hd >> 1;
+  const int half = rot_pairs;                            // pairs (j, j + half) when not interleaved
   if (inv_freq != nullptr && first_head < nh + nkv) {    // a block of v heads alone rotates nothing
     for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sn_s[j], &cs_s[j]);
   }
@@ -74,11 +76,13 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
     }
   }
   const int j0 = sub * 8;                                // pairs j0 .. j0 + 7
+  const bool rotates = j0 < rot_pairs;                   // else: 16 elements past the rotated dims
+  const bool consecutive = interleaved || !rotates;      // the lane's 16 elements lie side by side
   float a[8], b[8];
   float ss = 0.f;
   if (active) {
     const T* src = qkv + ((size_t)t * heads_total + head) * hd;
-    if (interleaved) {                                   // elements 2 j0 .. 2 j0 + 15: (a0, b0, a1, b1, ...)
+    if (consecutive) {                                   // elements 2 j0 .. 2 j0 + 15: (a0, b0, a1, b1, ...)
       float lo[8], hi[8];
       hb::load8(src + 2 * j0, lo);
       hb::load8(src + 2 * j0 + 8, hi);
@@ -93,7 +97,7 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      if (kind != 2 && inv_freq != nullptr) {
+      if (kind != 2 && inv_freq != nullptr && rotates) {
         const float sn = sn_s[j0 + i], cs = cs_s[j0 + i];
         const float ra = a[i] * cs - b[i] * sn;
         const float rb = b[i] * cs + a[i] * sn;
@@ -111,7 +115,7 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
     mul *= logf(floorf(((float)pos + 1.f) / floor_scale) + 1.f) * attn_scale + 1.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) { a[i] *= mul; b[i] *= mul; }
-  if (interleaved) {
+  if (consecutive) {
     float lo[8], hi[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -137,7 +141,8 @@ extern "C" int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, in
   if (write_kv && (!k_pages || !v_pages || !block_table || !seq_of_token || page_size <= 0 || table_stride <= 0))
     return HB_ERR_BAD_ARG;
   if (hd % 16 != 0 || hd > kMaxHeadDim) return HB_ERR_UNSUPPORTED;
-  if (inv_freq && rot_pairs != hd / 2) return HB_ERR_UNSUPPORTED;  // all of head_dim rotates
+  if (!inv_freq) rot_pairs = 0;
+  if (rot_pairs < 0 || 2 * rot_pairs > hd || rot_pairs % 8 != 0) return HB_ERR_UNSUPPORTED;  // whole lanes rotate
   if (temp_on && !(floor_scale > 0.f)) return HB_ERR_BAD_ARG;
   if (n_tokens == 0) return HB_OK;
   const int heads_total = nh + 2 * nkv;

@@ -32,7 +32,7 @@ class _CpuModel(ctypes.Structure):
 class _CpuLayer(ctypes.Structure):
     _fields_ = [("mixer", I), ("heads", I), ("kv_heads", I), ("head_dim", I), ("chunk", I), ("sliding", I),
                 ("interleaved", I), ("qk_norm", I), ("temperature", I), ("scale", F), ("qk_eps", F), ("floor_scale", F),
-                ("attn_scale", F), ("norm_eps", F), ("inv_freq", P), ("norm_mixer", P), ("norm_feed_forward", P),
+                ("attn_scale", F), ("norm_eps", F), ("inv_freq", P), ("rot_pairs", I), ("norm_mixer", P), ("norm_feed_forward", P),
                 ("wq", P), ("wk", P), ("wv", P), ("wo", P), ("bq", P), ("bk", P), ("bv", P), ("bo", P),
                 ("feed_forward", I), ("inter", I), ("experts", I), ("top_k", I), ("shared_inter", I),
                 ("w_gate", P), ("w_up", P), ("w_down", P), ("router", P), ("shared_gate", P), ("shared_up", P),
@@ -104,7 +104,7 @@ class CpuReference:
                       qk_norm=int(mix.qk_norm), temperature=int(mix.temperature is not None), scale=mix.scale,
                       qk_eps=mix.qk_norm_eps, floor_scale=(mix.temperature or (1.0, 0.0))[0],
                       attn_scale=(mix.temperature or (1.0, 0.0))[1], norm_eps=layer.norm_mixer.eps,
-                      inv_freq=self._ptr(inv_freq), norm_mixer=self._ptr(layer.norm_mixer.weight),
+                      inv_freq=self._ptr(inv_freq), rot_pairs=0 if inv_freq is None else int(inv_freq.numel()), norm_mixer=self._ptr(layer.norm_mixer.weight),
                       norm_feed_forward=self._ptr(layer.norm_feed_forward.weight), wq=self._ptr(wq), wk=self._ptr(wk),
                       wv=self._ptr(wv), wo=self._ptr(mix.w_o), bq=self._ptr(bq), bk=self._ptr(bk), bv=self._ptr(bv),
                       bo=self._ptr(mix.b_o))
@@ -113,6 +113,8 @@ class CpuReference:
             L.feed_forward, L.inter = 1, ff.mlp.inter
             L.w_gate, L.w_up, L.w_down = self._ptr(gate), self._ptr(up), self._ptr(ff.mlp.w_down)
         elif isinstance(ff, SigmoidRoutedExperts):
+            if ff.router_mode or ff.scale_output:
+                raise ValueError(f"{layer.spec.prefix}: the CPU reference knows sigmoid scores on the experts' input only")
             L.feed_forward, L.inter, L.experts, L.top_k = 2, ff.inter, ff.experts, ff.top_k
             L.w_gate, L.w_up, L.w_down, L.router = (self._ptr(ff.w_gate), self._ptr(ff.w_up), self._ptr(ff.w_down),
                                                     self._ptr(ff.w_router))

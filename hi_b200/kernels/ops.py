@@ -19,20 +19,20 @@ P, I, F = c_void_p, c_int, c_float
 _SIGNATURES = {
     "hb_feed_tokens": [P, P, P, P, I, P],
     "hb_embed_gather": [P, I, P, P, I, I, I, P],
-    "hb_add_rmsnorm": [P, P, I, P, P, I, P, I, P, I, P, P, I, I, F, P],
+    "hb_add_rmsnorm": [P, P, I, P, P, P, I, P, I, P, I, P, P, I, I, F, P],
     "hb_swiglu": [P, P, I, I, I, P],
-    "hb_moe_combine": [P, P, P, I, P, I, I, I, P],
+    "hb_moe_combine": [P, P, P, P, I, P, I, I, I, P],
     "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
     "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "hb_attention_merge": [P, P, P, I, I, I, I, P],
     "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P],
-    "hb_attention_decode_fused": [P, P, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P],
+    "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
-    "hb_router_topk": [P, I, P, I, I, I, I, I, P, P, P, P],
+    "hb_router_topk": [P, I, P, I, I, I, I, I, I, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
-    "hb_router_plan": [P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P],
+    "hb_router_plan": [P, I, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P],
     "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, P],
     "hb_moe_down": [P, I, P, P, P, I, P, I, I, I, I, P],
     "hb_gather_rows": [P, P, I, P, I, I, P],
@@ -128,11 +128,13 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
                 out_dtype: torch.dtype, row_map: Optional[torch.Tensor] = None, also_f32: bool = False,
                 routed: Optional[torch.Tensor] = None, slot_of_entry: Optional[torch.Tensor] = None,
-                top_k: int = 0):
+                top_k: int = 0, routed_weight: Optional[torch.Tensor] = None):
     """``x += delta`` (float32, in place) then ``rmsnorm(x) * weight`` in ``out_dtype``.
 
     ``routed`` (float32 [N*k, H], rows in expert-sorted order) with ``slot_of_entry`` adds each
-    token's k routed-expert rows into the same sum: the experts' combine, fused into the norm.
+    token's k routed-expert rows into the same sum: the experts' combine, fused into the norm;
+    ``routed_weight`` (float32 [N*k], by entry) multiplies each of them first (a router score that
+    scales the experts' outputs).
 
     ``also_f32`` returns ``(y, y_float32)``: the same normalised rows unrounded, for a consumer
     that computes in 32-bit (the router).
@@ -162,8 +164,13 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional
         _need(routed, "routed", torch.float32); _need(slot_of_entry, "slot_of_entry", torch.int32)
         if routed.shape[1] != hidden or not 1 <= top_k <= 8:
             raise KernelError("routed rows do not match the residual, or top_k is outside 1..8")
+        if routed_weight is not None:
+            _need(routed_weight, "routed_weight", torch.float32)
+            if routed_weight.numel() != slot_of_entry.numel():
+                raise KernelError("routed_weight needs one factor per routing entry")
     _check(lib().hb_add_rmsnorm(_ptr(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(routed),
-                                _ptr(slot_of_entry), int(top_k), _ptr(weight),
+                                _ptr(slot_of_entry), _ptr(routed_weight) if routed is not None else None, int(top_k),
+                                _ptr(weight),
                                 _dt(weight) if weight is not None else 0, _ptr(y), _dt(y), _ptr(y32), _ptr(row_map),
                                 rows, hidden, float(eps), _stream()), "add_rmsnorm")
     if also_f32:
@@ -183,8 +190,9 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 def moe_combine(y: torch.Tensor, slot_of_entry: torch.Tensor, shared: Optional[torch.Tensor], n: int,
-                top_k: int) -> torch.Tensor:
-    """out[t] = shared[t] + sum_j y[slot_of_entry[t*k + j]]  -> float32 [n, H]."""
+                top_k: int, routed_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = shared[t] + sum_j w[t*k + j] * y[slot_of_entry[t*k + j]]  -> float32 [n, H] (w = 1 without
+    ``routed_weight``)."""
     _need(y, "y", torch.float32); _need(slot_of_entry, "slot_of_entry", torch.int32)
     hidden = y.shape[1]
     if shared is not None:
@@ -192,7 +200,10 @@ def moe_combine(y: torch.Tensor, slot_of_entry: torch.Tensor, shared: Optional[t
         if tuple(shared.shape) != (n, hidden):
             raise KernelError("shared expert output has the wrong shape")
     out = torch.empty((n, hidden), dtype=torch.float32, device=y.device)
-    _check(lib().hb_moe_combine(_ptr(y), _ptr(slot_of_entry), _ptr(shared), _dt(shared) if shared is not None else 0,
+    if routed_weight is not None:
+        _need(routed_weight, "routed_weight", torch.float32)
+    _check(lib().hb_moe_combine(_ptr(y), _ptr(slot_of_entry), _ptr(routed_weight), _ptr(shared),
+                                _dt(shared) if shared is not None else 0,
                                 _ptr(out), n, hidden, top_k, _stream()), "moe_combine")
     return out
 
@@ -224,10 +235,7 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
         raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(nh + 2 * nkv) * hd}")
     if hd % 16 != 0 or hd > 256:
         raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256)")
-    if inv_freq is not None:
-        _need(inv_freq, "inv_freq", torch.float32)
-        if inv_freq.numel() != hd // 2:
-            raise KernelError("inv_freq must have head_dim/2 entries (all of head_dim rotates)")
+    rot_pairs = _rot_pairs(inv_freq, hd)
     stride = 0
     if write_kv:
         for t, nm in ((seq_of_token, "seq_of_token"), (block_table, "block_table")):
@@ -238,11 +246,22 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
         stride = block_table.shape[1]
     q = torch.empty((n, nh, hd), dtype=qkv.dtype, device=qkv.device)
     fs, asc = temperature if temperature is not None else (1.0, 0.0)
-    _check(lib().hb_qkv_post(_ptr(qkv), _dt(qkv), _ptr(inv_freq), hd // 2, int(interleaved), int(qk_norm),
+    _check(lib().hb_qkv_post(_ptr(qkv), _dt(qkv), _ptr(inv_freq), rot_pairs, int(interleaved), int(qk_norm),
                              float(qk_eps), int(temperature is not None), float(fs), float(asc), _ptr(positions),
                              _ptr(seq_of_token), _ptr(block_table), stride, _ptr(q), _ptr(k_pages), _ptr(v_pages),
                              page_size, int(write_kv), n, nh, nkv, hd, _stream()), "qkv_post")
     return q
+
+
+def _rot_pairs(inv_freq: Optional[torch.Tensor], hd: int) -> int:
+    """How many pairs of a head rotate: the table's length; whole lanes of 8 pairs, at most head_dim / 2."""
+    if inv_freq is None:
+        return 0
+    _need(inv_freq, "inv_freq", torch.float32)
+    pairs = inv_freq.numel()
+    if pairs % 8 or not 0 < 2 * pairs <= hd:
+        raise KernelError(f"inv_freq has {pairs} entries: the rotated dims must be a multiple of 16, at most head_dim ({hd})")
+    return pairs
 
 
 ATTENTION_SPLIT = 256      # keys per split of the general attention kernel
@@ -392,10 +411,7 @@ def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positi
         raise KernelError("qkv or the cache pages do not match the heads and head_dim")
     if not decode_attention_supported(qkv.dtype, nh, nkv, hd) or n * nkv > min(FUSED_COUNTERS, FUSED_MAX_GROUPS):
         return None
-    if inv_freq is not None:
-        _need(inv_freq, "inv_freq", torch.float32)
-        if inv_freq.numel() != hd // 2:
-            raise KernelError("inv_freq must have head_dim/2 entries (all of head_dim rotates)")
+    rot_pairs = _rot_pairs(inv_freq, hd)
     longest = max(int(max_context), 1)
     if chunk > 0:
         longest = min(longest, chunk)
@@ -409,7 +425,7 @@ def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positi
         part_ml = torch.empty((n, nh, splits, 2), dtype=torch.float32, device=qkv.device)
     fs, asc = temperature if temperature is not None else (1.0, 0.0)
     code = lib().hb_attention_decode_fused(
-        _ptr(qkv), _ptr(inv_freq), int(interleaved), int(qk_norm), float(qk_eps), int(temperature is not None), float(fs),
+        _ptr(qkv), _ptr(inv_freq), rot_pairs, int(interleaved), int(qk_norm), float(qk_eps), int(temperature is not None), float(fs),
         float(asc), _ptr(k_pages), _ptr(v_pages), n_pages, _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
         _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size, int(chunk), int(window), float(scale), split_size, splits,
         _ptr(part_acc), _ptr(part_ml), _ptr(_fused_counter_buffer(qkv.device)) if merge_inside else None,
@@ -495,8 +511,13 @@ def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
 
 
 # --------------------------------------------------------------------------- experts
-def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool = False):
-    """Router logits (float32), the top-k expert ids (ties to the lower id) and sigmoid scores."""
+ROUTER_SOFTMAX, ROUTER_RENORMALIZE = 1, 2     # bits of a router's ``mode``
+
+
+def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool = False, mode: int = 0):
+    """Router logits (float32), the top-k expert ids (ties to the lower id) and their scores: the
+    sigmoid of the chosen logit, or with ``ROUTER_SOFTMAX`` its softmax over all experts; with
+    ``ROUTER_RENORMALIZE`` divided by the sum of the chosen scores."""
     _need(x, "x"); _need(w, "router weight")
     n, hidden = x.shape
     experts = w.shape[0]
@@ -505,7 +526,7 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool 
     ids = torch.empty((n, top_k), dtype=torch.int32, device=x.device)
     scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
     logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)   # the blocks' meeting place
-    _check(lib().hb_router_topk(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, _ptr(logits),
+    _check(lib().hb_router_topk(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, int(mode), _ptr(logits),
                                 _ptr(ids), _ptr(scores), _stream()), "router_topk")
     return ids, scores, logits if want_logits else None
 
@@ -541,7 +562,7 @@ def _block_counter(dev) -> torch.Tensor:
     return c
 
 
-def router_plan(x: torch.Tensor, w: torch.Tensor, top_k: int):
+def router_plan(x: torch.Tensor, w: torch.Tensor, top_k: int, mode: int = 0):
     """:func:`router_topk` and :func:`moe_plan` in one call: with few tokens one kernel does both
     (the block that ends last groups the entries). Returns ids, scores and the plan."""
     _need(x, "x"); _need(w, "router weight")
@@ -553,7 +574,7 @@ def router_plan(x: torch.Tensor, w: torch.Tensor, top_k: int):
     scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
     logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)   # the blocks' meeting place
     plan = _empty_plan(n * top_k, experts, x.device)
-    _check(lib().hb_router_plan(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, _ptr(logits),
+    _check(lib().hb_router_plan(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, int(mode), _ptr(logits),
                                 _ptr(ids), _ptr(scores), _ptr(plan.offsets), _ptr(plan.sorted_entry),
                                 _ptr(plan.slot_of_entry), _ptr(plan.active), _ptr(_block_counter(x.device)),
                                 _stream()), "router_plan")

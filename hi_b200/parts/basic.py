@@ -63,7 +63,7 @@ class RMSNorm(Part):
                 delta = delta.materialize(residual.shape[0])
             else:
                 return ops.add_rmsnorm(residual, delta.dense, self.weight, self.eps, self.env.dtype, row_map, also_f32,
-                                       delta.routed, delta.slot_of_entry, delta.top_k)
+                                       delta.routed, delta.slot_of_entry, delta.top_k, delta.entry_weights)
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.env.dtype, row_map, also_f32)
 
 
@@ -95,17 +95,21 @@ def llama3_inverse_frequencies(head_dim: int, theta: float, scaling: Optional[di
 
 @register("position", "rope")
 class RotaryPosition(Part):
-    """Rotary encoding of all head_dim dims of q and k.
+    """Rotary encoding of q and k: all head_dim dims, or with ``rot_dim`` the first rot_dim of them
+    (a multiple of 16; the rest pass through).
     params: ``head_dim``, ``theta``, ``scaling`` (dict or None), ``interleaved`` (pairs (2j, 2j+1)
-    instead of (j, j + hd/2))."""
+    instead of (j, j + rot_dim/2)), ``rot_dim`` (default head_dim; the frequencies are
+    theta^(-2j/rot_dim))."""
 
     graph_safe = True
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.interleaved = bool(params.get("interleaved", False))
-        self._table_host = llama3_inverse_frequencies(int(params["head_dim"]), float(params["theta"]),
-                                                      params.get("scaling"))
+        self.rot_dim = int(params.get("rot_dim") or params["head_dim"])
+        if self.rot_dim % 16 or not 0 < self.rot_dim <= int(params["head_dim"]):
+            raise ValueError(f"{prefix}: rot_dim {self.rot_dim} must be a multiple of 16, at most head_dim")
+        self._table_host = llama3_inverse_frequencies(self.rot_dim, float(params["theta"]), params.get("scaling"))
         self._table: Optional[torch.Tensor] = None
 
     def rotary_table(self):

@@ -65,6 +65,7 @@ class Pending:
     routed: Optional[torch.Tensor] = None
     slot_of_entry: Optional[torch.Tensor] = None
     top_k: int = 0
+    entry_weights: Optional[torch.Tensor] = None     # float32 [N*k]: factors of the routed rows in the sum
 
     def materialize(self, n_tokens: int) -> torch.Tensor:
         """The sum as one float32 tensor, for a consumer that is not a norm."""
@@ -72,4 +73,4 @@ class Pending:
 
         if self.routed is None:
             return self.dense
-        return ops.moe_combine(self.routed, self.slot_of_entry, self.dense, n_tokens, self.top_k)
+        return ops.moe_combine(self.routed, self.slot_of_entry, self.dense, n_tokens, self.top_k, self.entry_weights)

@@ -58,14 +58,20 @@ class DenseSwiGLU(Part):
         return self.mlp.forward(normed)
 
 
+@register("feed_forward", "routed_experts")
 @register("feed_forward", "moe_sigmoid")
 class SigmoidRoutedExperts(Part):
-    """Router logits in float32, the k largest (ties to the lower id), score = sigmoid(logit)
-    without renormalisation; the score scales the expert input; an always-on shared expert
-    sees the unscaled input; outputs are summed (Llama4Moe::forward,
-    crates/hi-mlx/src/models.rs:6055-6103; the reference is top-1 only).
+    """Router logits in float32, the k largest (ties to the lower id); by default score =
+    sigmoid(logit) without renormalisation and the score scales the expert input; an always-on
+    shared expert sees the unscaled input; outputs are summed (Llama4Moe::forward,
+    crates/hi-mlx/src/models.rs:6055-6103; the reference is top-1 only). The other routing rules of
+    the reference's donor kernel (crates/hi-cuda/src/kernels.cu:536-546) are parameters too.
 
-    params: ``hidden_size``, ``num_experts``, ``top_k``, ``intermediate_size``, ``shared_expert``.
+    params: ``hidden_size``, ``num_experts``, ``top_k``, ``intermediate_size``, ``shared_expert``;
+      ``score``        "sigmoid" (default) | "softmax" (over all experts)
+      ``renormalize``  the chosen scores are divided by their sum (default False)
+      ``scale``        "input" (default: the score multiplies what the expert reads) | "output"
+                       (it multiplies what the expert returns, in the sum the next norm takes)
     tensors: ``<prefix>.router.weight`` [E, H]; ``<prefix>.experts.{gate,up}_proj.weight`` [E, I, H];
     ``<prefix>.experts.down_proj.weight`` [E, H, I]; ``<prefix>.shared_expert.{gate,up,down}_proj.weight``.
     """
@@ -85,6 +91,13 @@ class SigmoidRoutedExperts(Part):
             raise ValueError(f"{prefix}: top_k {self.top_k} outside 1..{self.experts}")
         self.shared = _SwiGLU(f"{prefix}.shared_expert", self.hidden, self.inter) \
             if params.get("shared_expert", True) else None
+        score, scale = params.get("score", "sigmoid"), params.get("scale", "input")
+        if score not in ("sigmoid", "softmax") or scale not in ("input", "output"):
+            raise ValueError(f"{prefix}: score {score!r} / scale {scale!r} are not known (sigmoid | softmax; input | output)")
+        self.router_mode = (ops.ROUTER_SOFTMAX if score == "softmax" else 0) | \
+            (ops.ROUTER_RENORMALIZE if params.get("renormalize", False) else 0)
+        self.scale_output = scale == "output"
+        self._ones: Optional[torch.Tensor] = None
         self.w_router = self.w_gate = self.w_up = self.w_down = None
         self._side_stream = None
 
@@ -137,16 +150,27 @@ class SigmoidRoutedExperts(Part):
         router_in = normed if normed_f32 is None else normed_f32
         forced = ctx.forced.get(f"{self.prefix}.router_ids") if ctx.forced else None
         if forced is None:
-            ids, scores, plan = ops.router_plan(router_in, self.w_router, self.top_k)
+            ids, scores, plan = ops.router_plan(router_in, self.w_router, self.top_k, self.router_mode)
         else:
             # debug: another run's expert choices, scored with this run's own logits (two runs in
             # different precisions can then be compared token by token)
             _own, _s, logits = ops.router_topk(router_in, self.w_router, self.top_k, want_logits=True)
             ids = forced.to(device=logits.device, dtype=torch.int32).reshape(n, self.top_k).contiguous()
-            scores = torch.sigmoid(torch.gather(logits, 1, ids.long())).contiguous()
+            chosen = torch.gather(logits, 1, ids.long())
+            scores = torch.sigmoid(chosen) if not self.router_mode & ops.ROUTER_SOFTMAX else \
+                torch.exp(chosen - torch.logsumexp(logits, dim=1, keepdim=True))
+            if self.router_mode & ops.ROUTER_RENORMALIZE:
+                scores = scores / scores.sum(dim=1, keepdim=True)
+            scores = scores.contiguous()
             plan = ops.moe_plan(ids, self.experts)
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.router_ids", ids)
+        entry_weights = None
+        if self.scale_output:
+            # the experts read the unscaled rows (a factor of one); their outputs take the score in the sum
+            if self._ones is None or self._ones.numel() < scores.numel():
+                self._ones = torch.ones(max(scores.numel(), 65536), dtype=torch.float32, device=scores.device)
+            entry_weights, scores = scores.view(-1), self._ones[: scores.numel()].view_as(scores)
         tc = ops.moe_tc_supported(normed, self.w_gate)
         few = n * self.top_k <= (self.FEW_ROWS if tc else 128)
         if not few and tc:
@@ -161,4 +185,5 @@ class SigmoidRoutedExperts(Part):
         else:
             shared = self.shared.forward(normed) if self.shared else None
         # the sum shared + routed rows is taken inside the next norm's residual add
-        return Pending(dense=shared, routed=y, slot_of_entry=plan.slot_of_entry, top_k=self.top_k)
+        return Pending(dense=shared, routed=y, slot_of_entry=plan.slot_of_entry, top_k=self.top_k,
+                       entry_weights=entry_weights)

@@ -78,7 +78,8 @@ def test_rotary_table_matches_the_plain_one():
 
 
 @pytest.mark.parametrize("dt,tol", DT)
-@pytest.mark.parametrize("kind", ["chunked_rope_norm", "global_temperature", "sliding_interleaved"])
+@pytest.mark.parametrize("kind", ["chunked_rope_norm", "global_temperature", "sliding_interleaved", "partial_rotary",
+                                  "partial_rotary_interleaved"])
 def test_attention_mixer(kind, dt, tol):
     """The mixer over a paged cache, fed in two steps, against whole-sequence attention."""
     from hi_b200.parts.context import CacheView
@@ -86,7 +87,14 @@ def test_attention_mixer(kind, dt, tol):
     from hi_b200.parts.spec import PartSpec
 
     H, nh, nkv, hd, page, T, cut = 72, 6, 2, 16, 4, 53, 31
+    if kind.startswith("partial_rotary"):
+        hd = 48                     # 32 of 48 dims rotate; the rest pass through and count in the norm
     cfgs = {
+        "partial_rotary": dict(window=("chunk", 20), qk_norm=True,
+                               position=PartSpec("rope", {"head_dim": 48, "rot_dim": 32, "theta": 1e4, "scaling": None})),
+        "partial_rotary_interleaved": dict(window=None, qk_norm=False, temperature=(8.0, 0.3),
+                                           position=PartSpec("rope", {"head_dim": 48, "rot_dim": 16, "theta": 1e4, "scaling": None,
+                                                                      "interleaved": True})),
         "chunked_rope_norm": dict(window=("chunk", 12), position=PartSpec("rope", {"head_dim": hd, "theta": 1e4, "scaling": None}),
                                   qk_norm=True),
         "global_temperature": dict(window=None, position=PartSpec("none"), temperature=(8.0, 0.3)),
@@ -113,9 +121,11 @@ def test_attention_mixer(kind, dt, tol):
     pos = torch.arange(T)
     pspec = cfgs[kind]["position"]
     if pspec.kind == "rope":
-        inv = plain.rope_inverse_frequencies(hd, pspec.params["theta"], pspec.params.get("scaling"))
+        rot = pspec.params.get("rot_dim", hd)
+        inv = plain.rope_inverse_frequencies(rot, pspec.params["theta"], pspec.params.get("scaling"))
         il = pspec.params.get("interleaved", False)
-        q, k = plain.apply_rope(q, pos, inv, il), plain.apply_rope(k, pos, inv, il)
+        q = torch.cat([plain.apply_rope(q[..., :rot], pos, inv, il), q[..., rot:].float()], dim=-1)
+        k = torch.cat([plain.apply_rope(k[..., :rot], pos, inv, il), k[..., rot:].float()], dim=-1)
     if cfgs[kind].get("qk_norm"):
         q, k = plain.rms_norm(q, None, 1e-6), plain.rms_norm(k, None, 1e-6)
     if cfgs[kind].get("temperature"):
@@ -156,6 +166,53 @@ def test_feed_forward_parts(dt, tol):
     close(got, want, tol, "experts")
     own, _ = plain.router_top_k(x.float() @ w["e.router.weight"].float().T, 2)
     assert float((own.sort(-1).values == seen["e.router_ids"].long().sort(-1).values).float().mean()) > 0.9
+
+
+@pytest.mark.parametrize("dt,tol", DT)
+@pytest.mark.parametrize("score,renorm,scale", [("softmax", True, "output"), ("softmax", False, "input"), ("sigmoid", True, "output"),
+                                                ("sigmoid", False, "output")])
+def test_routed_experts_with_other_routing_rules(score, renorm, scale, dt, tol):
+    """The routed feed-forward with the routing rules Llama 4 does not use (softmax scores over all
+    experts, chosen scores renormalised, the score on the expert's output instead of its input),
+    through the same router, grouped-product and combine kernels, for a few rows (the weight-streaming
+    kernels) and for many (tcgen05 in bfloat16), summed by the next norm's kernel and by the
+    standalone combine; against the formulas written out here."""
+    from hi_b200.kernels import ops
+    from hi_b200.parts.registry import build
+    from hi_b200.parts.spec import PartSpec
+
+    H, E, K, I = 96, 7, 3, 64
+    part = build("feed_forward", PartSpec("routed_experts", {"hidden_size": H, "num_experts": E, "top_k": K, "intermediate_size": I,
+                                                             "shared_expert": False, "score": score, "renormalize": renorm,
+                                                             "scale": scale}), env(dt, H), "e")
+    w = {k: v.float() for k, v in fill(part, dt, 6, std=0.25).items()}
+    for n in (5, 200):
+        x = torch.randn(n, H, generator=torch.Generator().manual_seed(n)).to(dt)
+        ctx = ctx_for([n], [0], 4, {})
+        seen = {}
+        ctx.tap = lambda name, t: seen.__setitem__(name, t.cpu())
+        pending = part.forward(x.to(DEV), ctx, normed_f32=x.float().to(DEV))
+        ids = seen["e.router_ids"].long()
+        logits = x.float() @ w["e.router.weight"].T
+        chosen = torch.gather(logits, 1, ids)
+        s = torch.softmax(logits, dim=1).gather(1, ids) if score == "softmax" else torch.sigmoid(chosen)
+        if renorm:
+            s = s / s.sum(dim=1, keepdim=True)
+        want = torch.zeros(n, H)
+        for t in range(n):
+            for j in range(K):
+                e = int(ids[t, j])
+                xin = x[t: t + 1].float() * (s[t, j] if scale == "input" else 1.0)
+                y = plain.swiglu(xin, w["e.experts.gate_proj.weight"][e], w["e.experts.up_proj.weight"][e],
+                                 w["e.experts.down_proj.weight"][e])[0]
+                want[t] += y * (s[t, j] if scale == "output" else 1.0)
+        own, _ = plain.router_top_k(logits, K)
+        assert float((own.sort(-1).values == ids.sort(-1).values).all(-1).float().mean()) > 0.85
+        close(pending.materialize(n), want, tol, f"{n} rows, standalone combine")
+        residual = torch.zeros(n, H, device=DEV)
+        ops.add_rmsnorm(residual, pending.dense, None, 1e-5, torch.float32, None, False, pending.routed,
+                        pending.slot_of_entry, pending.top_k, pending.entry_weights)
+        close(residual, want, tol, f"{n} rows, combine inside the norm")
 
 
 @pytest.mark.parametrize("dt,tol", DT)
