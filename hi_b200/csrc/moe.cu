@@ -64,6 +64,80 @@ __device__ __forceinline__ void plan_block(const int* ids, int n, int experts, i
   }
 }
 
+// The same plan with every warp of the block at work, for the many entries of a prompt portion
+// (plan_block ranks with one warp, whose loads of `ids` follow one another: 20 us for 2,048
+// entries). Warp w takes the w-th run of entries: it counts its run's entries per expert, the runs'
+// counts are scanned per expert (a run's entries follow those of the runs before it: the sort
+// stays stable), and the warp then places its entries. `sm` holds (warps + 2) * experts ints.
+__device__ __forceinline__ void plan_block_wide(const int* __restrict__ ids, int n, int experts,
+                                                int* __restrict__ offsets, int* __restrict__ sorted_entry,
+                                                int* __restrict__ slot_of_entry, int* __restrict__ active, int* sm) {
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* total = sm;                         // [experts] entries of each expert
+  int* first = sm + experts;               // [experts] its first slot
+  int* hist = sm + 2 * experts;            // [warps][experts] entries of the expert in a warp's run, then its next slot
+  for (int i = threadIdx.x; i < warps * experts; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  const int run = ((n + warps - 1) / warps + 31) / 32 * 32;      // whole groups of 32 entries to a warp
+  const int begin = warp * run, end = min(n, begin + run);
+  int* mine = hist + warp * experts;
+  auto walk = [&](bool place) {
+    for (int start = begin; start < end; start += 64) {           // two groups' loads in flight
+      int e2[2];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int i = start + 32 * q + lane;
+        e2[q] = i < end ? ids[i] : -1;
+        if (e2[q] >= experts) e2[q] = -1;
+      }
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int i = start + 32 * q + lane, e = e2[q];
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        if (place && e >= 0) {
+          const int slot = mine[e] + rank;
+          sorted_entry[slot] = i;
+          slot_of_entry[i] = slot;
+        }
+        __syncwarp();
+        if (e >= 0 && rank == 0) mine[e] += __popc(peers);
+        __syncwarp();
+      }
+    }
+  };
+  walk(false);
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int sum = 0;
+    for (int w = 0; w < warps; ++w) sum += hist[w * experts + e];
+    total[e] = sum;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, n_active = 0;
+    for (int e = 0; e < experts; ++e) {
+      offsets[e] = at;
+      first[e] = at;
+      at += total[e];
+      if (total[e] > 0) active[1 + n_active++] = e;
+    }
+    offsets[experts] = at;
+    active[0] = n_active;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {       // counts -> first slot of each warp's run
+    int at = first[e];
+    for (int w = 0; w < warps; ++w) {
+      const int c = hist[w * experts + e];
+      hist[w * experts + e] = at;
+      at += c;
+    }
+  }
+  __syncthreads();
+  walk(true);
+}
+
 // ------------------------------------------------------------------ router
 // logit[t, e] = sum_k x[t, k] * w[e, k] in float32. x may be float32 while the weights are
 // bfloat16: the router reads the float32 output of the norm, so its logits carry no activation
@@ -292,9 +366,22 @@ __global__ void router_select_kernel(const float* __restrict__ logits, int n, in
 // ------------------------------------------------------------------ plan
 __global__ void moe_plan_kernel(const int* ids, int n, int experts, int* __restrict__ offsets,
                                 int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry,
-                                int* __restrict__ active) {
-  extern __shared__ int plan_sm[];  // cnt[experts], base[experts]
-  plan_block(ids, n, experts, offsets, sorted_entry, slot_of_entry, active, plan_sm);
+                                int* __restrict__ active, int wide) {
+  extern __shared__ int plan_sm[];  // cnt[experts], base[experts]; wide: (warps + 2) * experts
+  if (wide) plan_block_wide(ids, n, experts, offsets, sorted_entry, slot_of_entry, active, plan_sm);
+  else plan_block(ids, n, experts, offsets, sorted_entry, slot_of_entry, active, plan_sm);
+}
+
+// One block of 1,024 threads; every warp ranks where the per-warp counts fit shared memory and there
+// are entries enough for it to pay.
+int launch_plan(const int* ids, int n, int experts, int* offsets, int* sorted_entry, int* slot_of_entry, int* active,
+                cudaStream_t stream) {
+  const size_t wide_smem = (size_t)(32 + 2) * experts * sizeof(int);
+  const int wide = n >= 256 && wide_smem <= 40 * 1024;
+  moe_plan_kernel<<<1, 1024, wide ? wide_smem : 2 * (size_t)experts * sizeof(int), stream>>>(
+      ids, n, experts, offsets, sorted_entry, slot_of_entry, active, wide);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
 }
 
 // ------------------------------------------------------------------ grouped products, general form
@@ -563,9 +650,7 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
       HB_LAUNCH_CHECK();
     }
     if (counter) {
-      moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, n * top_k, experts, offsets,
-                                                                              sorted_entry, slot_of_entry, active);
-      HB_LAUNCH_CHECK();
+      if (int rc = launch_plan(ids, n * top_k, experts, offsets, sorted_entry, slot_of_entry, active, stream)) return rc;
     }
     return HB_OK;
   }
@@ -598,9 +683,7 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
     router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, mode, ids, scores);
     HB_LAUNCH_CHECK();
     if (counter) {
-      moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, n * top_k, experts, offsets,
-                                                                              sorted_entry, slot_of_entry, active);
-      HB_LAUNCH_CHECK();
+      if (int rc = launch_plan(ids, n * top_k, experts, offsets, sorted_entry, slot_of_entry, active, stream)) return rc;
     }
   }
   return HB_OK;
@@ -622,10 +705,7 @@ extern "C" int hb_router_plan(const void* x, int x_dtype, const void* w, int w_d
   if (!offsets || !sorted_entry || !slot_of_entry || !active || !counter) return HB_ERR_BAD_ARG;
   if (experts <= 0 || experts > 4096) return experts <= 0 ? HB_ERR_BAD_ARG : HB_ERR_UNSUPPORTED;
   if (n == 0) {  // nothing routed: an empty plan
-    moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, 0, experts, offsets, sorted_entry,
-                                                                            slot_of_entry, active);
-    HB_LAUNCH_CHECK();
-    return HB_OK;
+    return launch_plan(ids, 0, experts, offsets, sorted_entry, slot_of_entry, active, stream);
   }
   return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets,
                        sorted_entry, slot_of_entry, active, counter, stream);
@@ -636,10 +716,7 @@ extern "C" int hb_moe_plan(const int* ids, int n_entries, int experts, int* offs
   if (!ids || !offsets || !sorted_entry || !slot_of_entry || !active || n_entries < 0 || experts <= 0)
     return HB_ERR_BAD_ARG;
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
-  moe_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, n_entries, experts, offsets,
-                                                                          sorted_entry, slot_of_entry, active);
-  HB_LAUNCH_CHECK();
-  return HB_OK;
+  return launch_plan(ids, n_entries, experts, offsets, sorted_entry, slot_of_entry, active, stream);
 }
 
 // gate/up with SwiGLU: act[slot, :] (engine dtype, [n_entries, inter]).

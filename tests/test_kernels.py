@@ -600,3 +600,27 @@ def test_fused_decode_attention_equals_its_three_kernels(shape):
     # a sliding window is not taken: the caller falls back
     assert o.decode_attention_fused(qkv, nh, nkv, hd, pos, inv, interleaved, norm, 1e-6, temperature, sot, bt, k2, v2,
                                     0, 100, hd ** -0.5, max(total)) is None
+
+
+@pytest.mark.parametrize("n,experts", [(1, 4), (255, 16), (256, 16), (2048, 16), (2047, 128), (5000, 5), (9001, 300), (300, 4000)])
+def test_plan_is_a_stable_sort_by_expert(n, experts):
+    """The device-side plan against a stable argsort on the host: offsets, the entry of every
+    sorted slot, the slot of every entry, and the list of experts that have rows; with one warp
+    ranking (few entries, or more experts than fit) and with all of them."""
+    import numpy as np
+
+    o = ops()
+    g = torch.Generator().manual_seed(n + experts)
+    ids = torch.randint(0, experts, (n,), generator=g, dtype=torch.int32)
+    if n > 100:
+        ids[ids == 3] = 2                                   # an expert without rows
+    plan = o.moe_plan(ids.to(DEV), experts)
+    order = np.argsort(ids.numpy(), kind="stable")
+    counts = np.bincount(ids.numpy(), minlength=experts)
+    assert plan.offsets.cpu().tolist() == [0] + np.cumsum(counts).tolist()
+    assert plan.sorted_entry.cpu().numpy()[:n].tolist() == order.tolist()
+    inverse = np.empty(n, dtype=np.int64)
+    inverse[order] = np.arange(n)
+    assert plan.slot_of_entry.cpu().numpy()[:n].tolist() == inverse.tolist()
+    active = plan.active.cpu().tolist()
+    assert active[0] == int((counts > 0).sum()) and active[1: 1 + active[0]] == np.nonzero(counts)[0].tolist()
