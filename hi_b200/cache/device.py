@@ -31,6 +31,51 @@ def plan_groups(cache_specs: Dict[int, Optional[CacheSpec]]) -> Tuple[List[Cache
     return groups, group_of
 
 
+def bytes_per_token(cache_specs: Dict[int, Optional[CacheSpec]], element_size: int) -> List[int]:
+    """Per group: bytes one cached token takes in all the cache slots of the group (keys and values)."""
+    groups, group_of = plan_groups(cache_specs)
+    out = [0] * len(groups)
+    for slot, spec in cache_specs.items():
+        if spec is not None and spec.paged:
+            out[group_of[slot]] += 2 * spec.kv_heads * spec.head_dim * element_size
+    return out
+
+
+def pool_tokens_for_budget(cache_specs: Dict[int, Optional[CacheSpec]], element_size: int, budget_bytes: int,
+                           page_size: int, max_requests: int, most_tokens: Optional[int] = None,
+                           portion_tokens: int = 8192) -> List[int]:
+    """Pool sizes (tokens per group) from a byte budget (the reference sizes its one pool from the
+    token budget of a step, crates/hi-cuda/src/lib.rs:794-797; here the memory that is free decides).
+    A windowed group never holds more than its window, the page being written and the portion in
+    flight for every request, so it gets that (or less, if the budget is smaller); what is left
+    goes to the groups that keep every key, in proportion to what a token costs them. ``most_tokens``
+    caps the result (``max_requests`` requests at the model's longest context need no more)."""
+    groups, _ = plan_groups(cache_specs)
+    cost = bytes_per_token(cache_specs, element_size)
+    if not groups:
+        return []
+    floor = page_size * max(2, max_requests)                     # never less than two pages a request could take
+    tokens = [0] * len(groups)
+    left = int(budget_bytes)
+    windowed = [g for g, spec in enumerate(groups) if spec.window is not None]
+    keep_all = [g for g, spec in enumerate(groups) if spec.window is None]
+    for g in windowed:
+        want = max_requests * (groups[g].window[1] + 2 * page_size) + portion_tokens
+        if most_tokens is not None:
+            want = min(want, most_tokens)
+        share = left // max(1, len(windowed) + len(keep_all)) if keep_all else left // len(windowed)
+        tokens[g] = max(floor, min(want, share // cost[g]))
+        left -= tokens[g] * cost[g]
+    if keep_all:
+        per_token = sum(cost[g] for g in keep_all)
+        t = max(floor, left // per_token)
+        if most_tokens is not None:
+            t = min(t, max(most_tokens, floor))
+        for g in keep_all:
+            tokens[g] = t
+    return [-(-t // page_size) * page_size for t in tokens]
+
+
 class DeviceCache:
     def __init__(self, cache_specs: Dict[int, Optional[CacheSpec]], pages_per_group: Sequence[int], page_size: int,
                  max_requests: int, dtype: torch.dtype, device):

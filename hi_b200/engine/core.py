@@ -17,7 +17,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..cache.device import DeviceCache, plan_groups
+from ..cache.device import DeviceCache, plan_groups, pool_tokens_for_budget
 from ..cache.pages import CacheManager, OutOfPages
 from ..config.registry import load_architecture, lookup
 from ..parts.context import StepContext
@@ -84,11 +84,15 @@ class Engine:
 
     ``kv_cache_tokens`` sizes every page pool (tokens, rounded up to pages);
     ``windowed_cache_tokens`` optionally gives the windowed groups (chunked layers) a smaller
-    pool. ``max_active_requests`` is the number of state slots / block-table rows.
+    pool. Without ``kv_cache_tokens`` the pools are sized from the device memory that is free once
+    the weights are loaded: ``cache_memory_fraction`` of it, windowed groups at what
+    ``max_active_requests`` windows need, the rest to the groups that keep every key.
+    ``max_active_requests`` is the number of state slots / block-table rows.
     """
 
-    def __init__(self, model: Model, *, kv_page_size: int = 64, kv_cache_tokens: int = 8192,
+    def __init__(self, model: Model, *, kv_page_size: int = 64, kv_cache_tokens: Optional[int] = None,
                  windowed_cache_tokens: Optional[int] = None, max_active_requests: int = 8,
+                 cache_memory_fraction: float = 0.9,
                  debug_poison: bool = False, use_cuda_graphs: bool = True, graph_context_bucket: int = 1024,
                  max_graphs: int = 16):
         _require_cuda(model.device)
@@ -97,9 +101,21 @@ class Engine:
         self.dtype = model.dtype
         self.page_size = int(kv_page_size)
         groups, self.group_of = plan_groups(model.cache_specs)
+        auto = None
+        if kv_cache_tokens is None:
+            if not 0.0 < cache_memory_fraction <= 1.0:
+                raise ValueError("cache_memory_fraction must lie in (0, 1]")
+            free, _total = torch.cuda.mem_get_info(self.device)
+            longest = model.spec.max_position_embeddings
+            auto = pool_tokens_for_budget(model.cache_specs, torch.empty((), dtype=model.dtype).element_size(),
+                                          int(free * cache_memory_fraction), self.page_size, max_active_requests,
+                                          most_tokens=None if longest is None else longest * max_active_requests)
         pages = []
-        for spec in groups:
-            tokens = kv_cache_tokens if (spec.window is None or windowed_cache_tokens is None) else windowed_cache_tokens
+        for g, spec in enumerate(groups):
+            if auto is not None:
+                tokens = auto[g] if (spec.window is None or windowed_cache_tokens is None) else windowed_cache_tokens
+            else:
+                tokens = kv_cache_tokens if (spec.window is None or windowed_cache_tokens is None) else windowed_cache_tokens
             pages.append(max(1, -(-int(tokens) // self.page_size)))
         self.manager = CacheManager(groups, pages, self.page_size, max_active_requests)
         self.cache = DeviceCache(model.cache_specs, pages, self.page_size, max_active_requests, model.dtype,

@@ -67,8 +67,8 @@ class LLM:
     ``model`` is a model folder, or a config dict together with ``random_seed`` (weights are
     then generated on the device). Options are the reference's serve flags
     (crates/hi-local/src/main.rs:28-59): ``max_batch_size``, ``max_active_requests``,
-    ``max_batched_tokens``, ``kv_page_size``; plus ``kv_cache_tokens`` (pool capacity) and
-    ``max_prefill_portion``.
+    ``max_batched_tokens``, ``kv_page_size``; plus ``kv_cache_tokens`` (pool capacity; by default
+    nine tenths of the device memory that is free after loading) and ``max_prefill_portion``.
     """
 
     def __init__(self, model: Union[str, dict, Engine], *, dtype="bfloat16", device="cuda:0",
@@ -84,7 +84,7 @@ class LLM:
             self.engine = model
         else:
             opts = dict(kv_page_size=kv_page_size, max_active_requests=slots,
-                        kv_cache_tokens=kv_cache_tokens or max(max_batched_tokens, 8192),
+                        kv_cache_tokens=kv_cache_tokens,      # None: sized from the memory that is free
                         windowed_cache_tokens=windowed_cache_tokens)
             if isinstance(model, dict):
                 self.engine = Engine.from_config(model, seed=random_seed or 0, std=random_std, dtype=dtype,

@@ -165,3 +165,31 @@ def test_step_inputs_are_packed_from_the_tables():
     row_version[0] -= 1
     pack()
     assert buf[o[6]] == m.table(0, "a")[0] and row_version[0] == m.table_version("a")
+
+
+def test_pool_sizes_from_a_byte_budget():
+    """Without an explicit capacity the pools are sized from the memory that is free: windowed groups
+    get what the live requests' windows need, the groups that keep every key the rest; nothing
+    exceeds the budget, a cap on tokens holds, and a tiny budget still leaves every request pages."""
+    from hi_b200.cache.device import bytes_per_token, pool_tokens_for_budget
+    from hi_b200.parts.spec import CacheSpec
+
+    keep, chunk = CacheSpec(8, 128, None), CacheSpec(8, 128, ("chunk", 8192))
+    specs = {i: (keep if i % 4 == 3 else chunk) for i in range(16)}          # Scout: 4 global, 12 chunked layers
+    cost = bytes_per_token(specs, 2)
+    assert cost == [12 * 4096, 4 * 4096] or cost == [4 * 4096, 12 * 4096]
+    from hi_b200.cache.device import plan_groups
+    groups, _ = plan_groups(specs)
+    g_keep = [g for g, s in enumerate(groups) if s.window is None][0]
+    g_chunk = 1 - g_keep
+    budget = 80 << 30
+    tokens = pool_tokens_for_budget(specs, 2, budget, 64, 8)
+    assert all(t % 64 == 0 for t in tokens)
+    assert tokens[g_chunk] == 8 * (8192 + 128) + 8192
+    used = sum(t * c for t, c in zip(tokens, cost))
+    assert 0.99 * budget <= used <= budget
+    capped = pool_tokens_for_budget(specs, 2, budget, 64, 8, most_tokens=100_000)
+    assert capped[g_keep] == 100_032 and capped[g_chunk] == tokens[g_chunk]
+    small = pool_tokens_for_budget(specs, 2, 1 << 20, 64, 8)
+    assert all(t >= 2 * 64 for t in small)
+    assert pool_tokens_for_budget({0: None}, 2, budget, 64, 8) == []

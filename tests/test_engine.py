@@ -320,6 +320,22 @@ def test_the_float32_engine_against_the_cpu_reference(name, model_dirs):
     assert h.rel_err(out, want) <= 1e-4
 
 
+def test_default_cache_size_comes_from_the_memory_that_is_free(model_dirs):
+    """Without kv_cache_tokens the pools are sized from free device memory, capped at what the live
+    requests can ever hold (max_position_embeddings each); generation runs in them."""
+    import hi_b200
+
+    cfg, mdir = model_dirs["A"]
+    llm = hi_b200.LLM(mdir, dtype="float32", max_batch_size=2)
+    groups = llm.engine.manager.snapshot()["groups"]
+    keep = [g for g in groups if not g["window"]][0]
+    chunked = [g for g in groups if g["window"]][0]
+    assert keep["total"] * 64 == 2 * cfg["max_position_embeddings"]
+    assert chunked["total"] * 64 <= 2 * cfg["max_position_embeddings"] and chunked["total"] >= 4
+    outs = llm.generate([h.random_tokens(cfg, 20, seed=1)], hi_b200.SamplingParams(max_tokens=4, ignore_eos=True))
+    assert outs[0].completion_tokens == 4
+
+
 # --------------------------------------------------------------------------- a toy mixer with state
 def test_toy_mixer_with_state_registers_builds_and_steps(model_dirs):
     """A mixer defined here, with per-request state of fixed size (a running mean of a projection),
