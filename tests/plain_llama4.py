@@ -173,12 +173,15 @@ def linear(w: Dict[str, torch.Tensor], prefix: str, x: torch.Tensor) -> torch.Te
     return y if bias is None else y + bias.to(F32)
 
 
-def attention(cfg: dict, w: Dict[str, torch.Tensor], prefix: str, i: int, x: torch.Tensor, inv_freq) -> torch.Tensor:
-    """Llama4Attention::forward (models.rs:5978-6052) plus the chunk rule and temperature."""
+def attention(cfg: dict, w: Dict[str, torch.Tensor], prefix: str, i: int, x: torch.Tensor, inv_freq,
+              first_position: int = 0) -> torch.Tensor:
+    """Llama4Attention::forward (models.rs:5978-6052) plus the chunk rule and temperature.
+    ``first_position``: the sequence's positions are first_position .. (tests of what a layer does
+    and does not take from absolute positions; the sequence must then stay within one chunk)."""
     T = x.shape[0]
     nh, nkv = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"])
     hd = cfg.get("head_dim") or cfg["hidden_size"] // nh
-    pos = torch.arange(T)
+    pos = torch.arange(T) + first_position
     q = linear(w, f"{prefix}.q_proj", x).reshape(T, nh, hd)
     k = linear(w, f"{prefix}.k_proj", x).reshape(T, nkv, hd)
     v = linear(w, f"{prefix}.v_proj", x).reshape(T, nkv, hd)

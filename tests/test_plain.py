@@ -124,6 +124,44 @@ def test_properties_of_the_layer_kinds(models):
     assert torch.allclose(plain.forward(cfg, w, toks[:11]), full[:11], atol=1e-5)
 
 
+def test_what_the_layer_kinds_take_from_positions(models):
+    """A NoPE layer without temperature takes nothing from absolute positions; a rotary layer only
+    differences of positions (all of the sequence within one chunk); with temperature the NoPE layer
+    does change once floor((pos + 1) / floor_scale) moves."""
+    cfg, w = models["A"]
+    c = plain.text_config(copy.deepcopy(cfg))
+    c["attention_chunk_size"] = 4096
+    x = torch.randn(20, c["hidden_size"], generator=torch.Generator().manual_seed(3))
+    inv = plain.rope_inverse_frequencies(c["head_dim"], c["rope_theta"], c.get("rope_scaling"))
+    rotary, nope = "model.layers.0.self_attn", "model.layers.1.self_attn"
+    assert plain.layer_uses_rope(c, 0) and not plain.layer_uses_rope(c, 1)
+    no_temp = dict(c, attn_temperature_tuning=False)
+    a0 = plain.attention(no_temp, w, nope, 1, x, inv)
+    assert torch.allclose(a0, plain.attention(no_temp, w, nope, 1, x, inv, first_position=1000), atol=1e-6)
+    r0 = plain.attention(c, w, rotary, 0, x, inv)
+    assert torch.allclose(r0, plain.attention(c, w, rotary, 0, x, inv, first_position=777), atol=2e-5)
+    assert not torch.allclose(r0, plain.attention(dict(c, attention_chunk_size=8), w, rotary, 0, x, inv), atol=1e-4)
+    t0 = plain.attention(c, w, nope, 1, x[:10], inv)                                    # positions 0..9: factor 1
+    assert torch.allclose(t0, plain.attention(no_temp, w, nope, 1, x[:10], inv), atol=1e-6)
+    assert not torch.allclose(t0, plain.attention(c, w, nope, 1, x[:10], inv, first_position=160), atol=1e-4)
+
+
+def test_one_expert_of_one_is_a_dense_layer_with_a_scaled_input(models):
+    """k = 1 of E = 1: the routed part is the dense feed-forward of the expert's weights on the input
+    scaled by sigmoid(x . w_router), and the shared expert's dense feed-forward is added."""
+    cfg, w = models["A"]
+    c = plain.text_config(cfg)
+    p = "model.layers.0.feed_forward"
+    one = {k: (v[:1] if ".experts." in k or k.endswith("router.weight") else v) for k, v in w.items() if k.startswith(p)}
+    x = torch.randn(9, c["hidden_size"], generator=torch.Generator().manual_seed(4))
+    out = plain.moe_feed_forward(dict(c, num_local_experts=1, num_experts_per_tok=1), one, p, x)
+    score = torch.sigmoid(x @ one[f"{p}.router.weight"].float().T)                       # [9, 1]
+    dense = {f"d.{n}_proj.weight": one[f"{p}.experts.{n}_proj.weight"][0] for n in ("gate", "up", "down")}
+    shared = {f"s.{n}_proj.weight": one[f"{p}.shared_expert.{n}_proj.weight"] for n in ("gate", "up", "down")}
+    want = plain.dense_feed_forward(dense, "d", x * score) + plain.dense_feed_forward(shared, "s", x)
+    assert torch.allclose(out, want, atol=1e-6)
+
+
 def test_sampler_follows_the_reference(models):
     logits = torch.tensor([0.2, 0.1, 4.0, 3.0, 2.0])
     assert plain.sample(logits, 0.0, 1.0, 0, 0.3) == 2
