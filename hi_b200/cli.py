@@ -1,7 +1,7 @@
 """Command line, in the manner of the reference's ``hi-local`` (crates/hi-local/src/main.rs:20-84):
 
     python -m hi_b200 inspect MODEL_PATH
-    python -m hi_b200 run MODEL_PATH --tokens "1,2,3" [--max-tokens N] [--top-k 5] [--temperature T]
+    python -m hi_b200 run MODEL_PATH (--tokens "1,2,3" | --tokens-file F | --prompt TEXT) [--max-tokens N] [--top-k 5] [--temperature T]
                           [--top-p P] [--seed S] [--include-logits] [--dtype bfloat16|float32]
                           [--max-batch-size 8] [--max-batched-tokens 8192] [--kv-page-size 64]
                           [--random-weights [--weights-seed S] [--weights-std 0.02]] [--cpu]
@@ -40,6 +40,7 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("model_path")
     r.add_argument("--tokens")
     r.add_argument("--tokens-file")
+    r.add_argument("--prompt", help="text instead of token ids; needs tokenizer.json in the model folder")
     r.add_argument("--max-tokens", type=int, default=0)
     r.add_argument("--top-k", type=int, default=5)
     r.add_argument("--temperature", type=float, default=0.0)
@@ -109,12 +110,22 @@ def cmd_inspect(args) -> int:
 
 
 def cmd_run(args) -> int:
-    if bool(args.tokens) == bool(args.tokens_file):
-        raise SystemExit("provide either --tokens or --tokens-file")
-    text = args.tokens if args.tokens else open(args.tokens_file).read()
-    tokens = parse_token_ids(text)
+    import os
+
+    from .tokenizer import TokenizerRuntime
+
+    if sum(bool(v) for v in (args.tokens, args.tokens_file, args.prompt)) != 1:
+        raise SystemExit("provide exactly one of --tokens, --tokens-file and --prompt")
+    tokenizer = TokenizerRuntime.load(args.model_path) if os.path.isdir(args.model_path) else None
+    if args.prompt:
+        if tokenizer is None:
+            raise SystemExit("--prompt needs tokenizer.json in the model folder and the `tokenizers` package")
+        tokens = tokenizer.encode(args.prompt)
+    else:
+        tokens = parse_token_ids(args.tokens if args.tokens else open(args.tokens_file).read())
     if not tokens:
-        raise SystemExit("--tokens must include at least one token id")
+        raise SystemExit("the prompt must include at least one token")
+    args.tokenizer = tokenizer
     if args.cpu:
         return _run_on_cpu(args, tokens)
     import torch
@@ -153,14 +164,25 @@ def cmd_run(args) -> int:
         generated = out.token_ids
     result = {
         "backend": f"hi_b200-cuda-{args.dtype}", "input_tokens": tokens, "next_token": next_token,
-        "next_text": "", "generated_tokens": generated, "generated_text": "",
-        "top_logits": [{"token_id": i, "token": None, "logit": v} for i, v in top],
+        "next_text": _text(args, [next_token]), "generated_tokens": generated, "generated_text": _text(args, generated),
+        "top_logits": [{"token_id": i, "token": _token(args, i), "logit": v} for i, v in top],
         "logit_count": logits.numel(),
     }
     if args.include_logits:
         result["logits"] = logits.cpu().tolist()
     print(json.dumps(result, indent=2))
     return 0
+
+
+def _text(args, tokens) -> str:
+    """Text of token ids where the model folder has a tokenizer, else the empty string."""
+    tok = getattr(args, "tokenizer", None)
+    return tok.decode(tokens) if tok is not None and tokens else ""
+
+
+def _token(args, token_id: int):
+    tok = getattr(args, "tokenizer", None)
+    return tok.token(token_id) if tok is not None else None
 
 
 def _run_on_cpu(args, tokens: List[int]) -> int:
@@ -185,8 +207,8 @@ def _run_on_cpu(args, tokens: List[int]) -> int:
             eos_token_ids=ref.model.spec.eos_token_ids)
     result = {
         "backend": "hi_b200-cpu-reference-float32", "input_tokens": tokens, "next_token": int(np.argmax(row)),
-        "next_text": "", "generated_tokens": generated, "generated_text": "",
-        "top_logits": [{"token_id": int(i), "token": None, "logit": float(row[i])} for i in order],
+        "next_text": _text(args, [int(np.argmax(row))]), "generated_tokens": generated, "generated_text": _text(args, generated),
+        "top_logits": [{"token_id": int(i), "token": _token(args, int(i)), "logit": float(row[i])} for i in order],
         "logit_count": int(row.size),
     }
     if args.include_logits:

@@ -98,3 +98,28 @@ def test_generation_on_the_cpu_and_the_command_line(model_dirs):
     last = plain.forward(cfg, w, prompt)[-1]
     assert js["next_token"] == int(last.argmax()) == js["top_logits"][0]["token_id"] and js["logit_count"] == 256
     assert np.allclose(js["logits"], last.numpy(), atol=1e-4)
+
+
+def test_text_in_and_out_where_the_folder_has_a_tokenizer(model_dirs, tmp_path):
+    """--prompt and the text fields of `run`: with a tokenizer.json in the model folder (a word-level
+    one made here) the prompt is encoded without special tokens and the outputs are decoded; without
+    one --prompt is refused and the text fields stay empty."""
+    import shutil
+
+    tokenizers = pytest.importorskip("tokenizers")
+    cfg, mdir = model_dirs["A"]
+    d = str(tmp_path / "with_tokenizer")
+    shutil.copytree(mdir, d)
+    vocab = {f"w{i}": i for i in range(256)}
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="w0"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    tok.decoder = tokenizers.decoders.WordPiece(prefix="##")
+    tok.save(d + "/tokenizer.json")
+    res = run_cli("run", d, "--cpu", "--prompt", "w5 w17 w3 w200", "--max-tokens", "3", "--top-k", "2", "--dtype", "float32")
+    assert res.returncode == 0, res.stderr[-2000:]
+    js = json.loads(res.stdout)
+    assert js["input_tokens"] == [5, 17, 3, 200]
+    assert js["next_text"] == f"w{js['next_token']}" and js["top_logits"][0]["token"] == f"w{js['top_logits'][0]['token_id']}"
+    assert js["generated_text"].split() == [f"w{t}" for t in js["generated_tokens"]]
+    bare = run_cli("run", mdir, "--cpu", "--prompt", "w5", "--dtype", "float32")
+    assert bare.returncode != 0 and "tokenizer.json" in bare.stderr
