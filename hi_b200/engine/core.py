@@ -9,6 +9,7 @@ crates/hi-cuda/src/gpu.rs:8842-8929, 10541-10715, 9026-9132.)
 """
 from __future__ import annotations
 
+import gc
 import itertools
 import os
 from dataclasses import dataclass, field
@@ -467,9 +468,19 @@ class _DecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         self.taps = {}
         self.ctx.tap = self.taps.__setitem__
-        with torch.cuda.graph(self.graph):
-            self.logits = eng.model.forward(self.ctx, eng.cache.views, self.logit_rows)
-        self.ctx.tap = None
+        # Python's cycle collector must not run inside the capture: an engine dropped earlier and its
+        # captured steps refer to each other, so the collector is what frees them, and freeing a CUDA
+        # graph while a stream is being captured invalidates the capture. Collect now, then hold it off.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = eng.model.forward(self.ctx, eng.cache.views, self.logit_rows)
+        finally:
+            if collecting:
+                gc.enable()
+            self.ctx.tap = None
         self.kernels = ops.LAUNCHES[0] - before      # this library's kernels in one replay
         self.uses_tensor_core_experts = ops.TC_USED[0]
         ops.TC_USED[0] = False

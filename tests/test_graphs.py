@@ -172,3 +172,60 @@ def test_a_failed_wait_in_a_step_launched_ahead_aborts_instead_of_committing(tmp
     # the engine goes on: the word was cleared when it was read
     out = llm.generate([h.random_tokens(cfg, 12, seed=1)], hi_b200.SamplingParams(max_tokens=5, ignore_eos=True))
     assert out[0].completion_tokens == 5
+
+
+def test_an_earlier_engine_that_becomes_garbage_while_a_step_is_captured(model_dirs):
+    """An engine and its captured steps refer to each other, so Python frees them whenever its
+    cycle collector happens to run; freeing a CUDA graph is not allowed while a stream is being
+    captured. Here the old engine becomes garbage in the middle of the new engine's capture, and
+    enough objects are made there for the collector to run: the capture must come through."""
+    import gc
+
+    from hi_b200.engine.core import Engine, StepEntry
+
+    cfg, mdir = model_dirs["A"]
+    toks = h.random_tokens(cfg, 40, seed=77)
+
+    def started():
+        eng = Engine.from_dir(mdir, dtype="float32", kv_page_size=8, kv_cache_tokens=128, max_active_requests=1)
+        eng.step([StepEntry("a", toks[:20], [19])])
+        return eng
+
+    gc.collect()
+    was_enabled, thresholds, watch = gc.isenabled(), gc.get_threshold(), None
+    gc.disable()                               # every object made from here on stays in the youngest generation
+    try:
+        old = started()
+        for p in range(20, 24):                # one eager step, the capture, two replays
+            old.step([StepEntry("a", [toks[p]], [0])])
+        assert old._graphs
+        holder = [old]
+        del old
+        new = started()
+        new.step([StepEntry("a", [toks[20]], [0])])              # the shape's first step runs eagerly
+        inner = new.model.forward
+
+        def forward(*args):
+            if torch.cuda.is_current_stream_capturing() and holder:
+                holder.clear()                                    # the old engine is garbage from here on
+                _churn = [[i] for i in range(200000)]             # container objects: the collector's trigger
+            return inner(*args)
+
+        new.model.forward = forward
+        during = []                            # collections that started while the stream was being captured
+        watch = lambda phase, info: during.append(info["generation"]) \
+            if phase == "start" and torch.cuda.is_current_stream_capturing() else None
+        gc.callbacks.append(watch)
+        gc.set_threshold(gc.get_count()[0] + 50000, 1, 1)        # no collection before the capture: the old engine
+        gc.enable()                                               # stays in the youngest generation till then
+        got = new.step([StepEntry("a", [toks[21]], [0])])         # captured here
+        assert not during, "the cycle collector ran inside the capture"
+        assert not holder and new._graphs and torch.isfinite(got).all()
+        again = new.step([StepEntry("a", [toks[22]], [0])])
+        assert torch.isfinite(again).all()
+    finally:
+        if watch in gc.callbacks:
+            gc.callbacks.remove(watch)
+        gc.set_threshold(*thresholds)
+        (gc.enable if was_enabled else gc.disable)()
+    new.finish("a")
