@@ -85,7 +85,9 @@ int hb_moe_gate_up_tc(const void* xs, const int* sorted_entry, const void* w_gat
                       const int* offsets, int experts, const float* scores, void* act, int rows, int inter,
                       int hidden, int* status, cudaStream_t stream);
 int hb_moe_down_tc(const void* act, const void* w_down, const int* offsets, int experts, float* y, int rows,
-                   int hidden, int inter, int* status, cudaStream_t stream);
+                   int hidden, int inter, float* scratch, long long scratch_floats, int* counters, int n_counters,
+                   int* status, cudaStream_t stream);
+long long hb_moe_down_tc_scratch_floats(int sms);
 
 int hb_sample_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* uniforms,
                    int* out, cudaStream_t stream);

@@ -28,6 +28,11 @@
 // accumulates into the other while this one is written out; only a DUAL tile of more than 128
 // tokens needs both (gate in one, up in the other), and its epilogue gives them back as soon as
 // the results are in registers, before it stores them.
+// A down projection whose tiles do not fill the last round over the SMs cuts the tiles of that
+// round along K into up to four pieces, one block each: a piece leaves its float32 partial tile in
+// scratch memory and counts itself in; the piece that arrives last adds the pieces in their fixed
+// order and stores the sum (the result does not depend on which one that was), and puts the
+// counter back to zero for the next launch.
 // Token rows of an X tile past the expert's last token belong to the next expert (or are zero
 // fill), weight rows past n_out to the next expert: they are computed and not stored. Every
 // wait on an mbarrier is bounded; on a time-out the kernel records where it gave up in `status`
@@ -61,9 +66,11 @@ struct Params {
   void* out;                 // DUAL: bfloat16 [rows, n_out]; else float [rows, n_out]
   int* status;               // 0, or a code of the wait that timed out
   int experts, n_out, K, rows;
-  int k_splits;              // 1, or 2: every tile is cut in two along K and the halves are added into `out`
-                             // (not DUAL; `out` starts as zeros; two addends give the same sum in either order)
+  float* scratch;            // not DUAL: [blocks of the launch][BT][BF] partial tiles of the last round's pieces, or null
+  int* counters;             // [blocks of the launch] pieces of each cut tile that have arrived; zero between launches
 };
+constexpr int MAX_PIECES = 4;    // a tile of the last round is cut into at most this many pieces
+constexpr int MIN_PIECE_KB = 8;  // of at least this many k blocks (512 k elements)
 
 __host__ __device__ constexpr int x_box_rows(int box, int bt) {
   const int rows = box == 0 ? 32 : (box == 1 ? 64 : (box == 2 ? 128 : bt));
@@ -78,16 +85,14 @@ struct Maps {                // X boxes of 32, 64, 128 and 192 rows; the weight 
 // Tile t of the launch, in the order (expert, feature tile, token tile of the expert): tiles that
 // share a weight tile are neighbours, so they run at the same time and the weight tile comes from
 // HBM once. Returns false past the last tile. `f_tiles` = feature tiles.
-struct Tile { int expert, row0, tokens, f0, k_part; };
+struct Tile { int expert, row0, tokens, f0; };
 template <int BT>
-__device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t, int f_tiles, int k_splits, Tile& out) {
+__device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t, int f_tiles, Tile& out) {
   for (int e = 0; e < experts; ++e) {
     const int begin = offsets[e], cnt = offsets[e + 1] - begin;
     const int t_tiles = (cnt + BT - 1) / BT;
-    const int here = t_tiles * f_tiles * k_splits;
+    const int here = t_tiles * f_tiles;
     if (t < here) {
-      out.k_part = t % k_splits;                          // the parts of one tile are neighbours too
-      t /= k_splits;
       const int ft = t / t_tiles, tt = t - ft * t_tiles;
       const int per = (cnt + t_tiles - 1) / t_tiles;      // the expert's tokens in equal shares
       out.expert = e;
@@ -100,6 +105,46 @@ __device__ __forceinline__ bool find_tile(const int* offsets, int experts, int t
   }
   return false;
 }
+
+// The work of a block, in order: its tiles of the full rounds (blockIdx.x, blockIdx.x + gridDim.x,
+// ...), then its share of the last, partly filled round: a whole tile, or piece `piece` of `pieces`
+// of cut tile number `cut` (k blocks kb0 .. kb1). Every role of the block walks the same list.
+struct Work { Tile tile; int kb0, kb1, cut, piece, pieces; };
+template <int BT>
+struct WorkList {
+  const int* offsets;
+  int experts, f_tiles, num_kb, rounds, rest, pieces, per;
+  __device__ WorkList(const int* offsets_, int experts_, int f_tiles_, int num_kb_, bool may_cut)
+      : offsets(offsets_), experts(experts_), f_tiles(f_tiles_), num_kb(num_kb_) {
+    int tiles = 0;
+    for (int e = 0; e < experts; ++e) tiles += (offsets[e + 1] - offsets[e] + BT - 1) / BT * f_tiles;
+    rounds = tiles / (int)gridDim.x;
+    rest = tiles - rounds * (int)gridDim.x;
+    pieces = 1;
+    per = num_kb;
+    if (may_cut && rest > 0) {
+      int want = min(min(MAX_PIECES, (int)gridDim.x / rest), num_kb / MIN_PIECE_KB);
+      if (want > 1) {
+        per = (num_kb + want - 1) / want;
+        pieces = (num_kb + per - 1) / per;          // no piece is empty
+      }
+    }
+  }
+  __device__ __forceinline__ bool get(int i, Work& w) const {
+    w.kb0 = 0; w.kb1 = num_kb; w.cut = -1; w.piece = 0; w.pieces = 1;
+    if (i < rounds) return find_tile<BT>(offsets, experts, (int)blockIdx.x + i * (int)gridDim.x, f_tiles, w.tile);
+    if (i > rounds) return false;
+    const int b = (int)blockIdx.x;
+    if (pieces == 1) return b < rest && find_tile<BT>(offsets, experts, rounds * (int)gridDim.x + b, f_tiles, w.tile);
+    if (b >= rest * pieces) return false;
+    w.cut = b / pieces;                              // the pieces of one tile are neighbours: they share its tokens
+    w.piece = b - w.cut * pieces;
+    w.pieces = pieces;
+    w.kb0 = w.piece * per;
+    w.kb1 = min(num_kb, w.kb0 + per);
+    return find_tile<BT>(offsets, experts, rounds * (int)gridDim.x + w.cut, f_tiles, w.tile);
+  }
+};
 
 // The walk over a block's tiles that the MMA issuer and the epilogue warps share: which slot(s)
 // of tensor memory a tile takes, and how often each slot has been used before.
@@ -116,8 +161,7 @@ struct SlotWalk {
   }
 };
 
-// Persistent: each block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... The shared-memory
-// ring runs on across tiles.
+// Persistent: each block walks its work list. The shared-memory ring runs on across tiles.
 template <bool DUAL, int STAGES, int BT>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
@@ -131,14 +175,18 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;               // [2]
   uint64_t* acc_empty = acc_full + 2;                // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  int* s_offsets = reinterpret_cast<int*>(tmem_slot + 2);   // [experts + 1]: the tile search never waits on global memory
+  uint64_t* cut_bar = acc_empty + 2;                 // [2]: a piece's partial tile is written; whether it came last is known
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cut_bar + 2);
+  int* s_last = reinterpret_cast<int*>(tmem_slot + 2);      // whether this block's piece arrived last
+  int* s_offsets = s_last + 1;                              // [experts + 1]: the tile search never waits on global memory
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int e = threadIdx.x; e <= p.experts; e += THREADS) s_offsets[e] = p.offsets[e];
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
     for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], EPI_WARPS); }
+    tc::mbar_init(&cut_bar[0], EPI_WARPS);
+    tc::mbar_init(&cut_bar[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {                              // tensor memory for the two slots
@@ -150,19 +198,19 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
   const uint32_t tmem = *tmem_slot;
   const int f_tiles = (p.n_out + BF - 1) / BF;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int kb_per_part = (num_kb + p.k_splits - 1) / p.k_splits;
+  const WorkList<BT> list(s_offsets, p.experts, f_tiles, num_kb, !DUAL && p.scratch != nullptr);
 
   if (warp == 0) {
     if (lane == 0) {                            // ---- TMA producer
       uint32_t it = 0;                          // stages filled so far, over all tiles
       bool ok = true;
-      Tile tile;
-      for (int t = blockIdx.x; ok && find_tile<BT>(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
+      Work work;
+      for (int i = 0; ok && list.get(i, work); ++i) {
+        const Tile& tile = work.tile;
         const int box = tile.tokens <= 32 ? 0 : (tile.tokens <= 64 ? 1 : (tile.tokens <= 128 ? 2 : 3));
         const uint32_t bytes = NW * W_BYTES + (uint32_t)x_box_rows(box, BT) * BK * 2;
         const int w_row = tile.expert * p.n_out + tile.f0;
-        const int kb0 = tile.k_part * kb_per_part, kb1 = min(num_kb, kb0 + kb_per_part);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        for (int kb = work.kb0; kb < work.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (it >= STAGES && !tc::mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) { atomicExch(p.status, 1); ok = false; break; }
           uint8_t* st = smem + s * STAGE_BYTES;
@@ -178,8 +226,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
       uint32_t it = 0;
       SlotWalk walk;
       bool ok = true;
-      Tile tile;
-      for (int t = blockIdx.x; ok && find_tile<BT>(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
+      Work work;
+      for (int i = 0; ok && list.get(i, work); ++i) {
+        const Tile& tile = work.tile;
         bool both;
         const int b = walk.take(DUAL, tile.tokens, both);
         for (int q = b; ok && q <= (both ? 1 : b); ++q)      // the slot(s) must have been written out
@@ -189,8 +238,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
         const uint32_t idesc = tc::idesc_bf16(BF, (tile.tokens + 15) & ~15, false);
         const uint32_t acc = tmem + b * SLOT_COLS;
         const uint32_t up_off = both ? SLOT_COLS : DUAL_SLOT_T;  // where the second accumulator starts
-        const int kb0 = tile.k_part * kb_per_part, kb1 = min(num_kb, kb0 + kb_per_part);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int kb0 = work.kb0;
+        for (int kb = kb0; kb < work.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (!tc::mbar_wait(&full[s], (it / STAGES) & 1)) { atomicExch(p.status, 2); ok = false; break; }
           tc::fence_after();
@@ -215,8 +264,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
     const int half = (warp - 2) >> 2;           // which runs of 32 tokens it takes
     SlotWalk walk;
     bool ok = true;
-    Tile tile;
-    for (int t = blockIdx.x; ok && find_tile<BT>(s_offsets, p.experts, t, f_tiles, p.k_splits, tile); t += gridDim.x) {
+    Work work;
+    for (int i = 0; ok && list.get(i, work); ++i) {
+      const Tile& tile = work.tile;
       bool both;
       const int b = walk.take(DUAL, tile.tokens, both);
       const int f = tile.f0 + quarter * 32 + lane;        // this thread's feature = its lane of tensor memory
@@ -286,6 +336,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
           }
         }
       } else {
+        // a whole tile goes to `out`; a piece to its place in the scratch memory, [token][feature of the tile]
+        const bool cut = work.cut >= 0;
+        float* part = p.scratch + ((size_t)(work.cut * work.pieces + work.piece) * BT) * BF + quarter * 32 + lane;
 #pragma unroll
         for (int q = 0; q < RUNS; ++q) {
           const int c = half * 32 + q * 64;
@@ -295,9 +348,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
             float* dst = reinterpret_cast<float*>(p.out) + (size_t)(tile.row0 + c) * p.n_out + f;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {             // 32 lanes: 128 bytes in a row
-              if (f_ok && c + j < tile.tokens) {
-                if (p.k_splits == 1) dst[(size_t)j * p.n_out] = g[j];
-                else atomicAdd(dst + (size_t)j * p.n_out, g[j]);
+              if (c + j < tile.tokens) {
+                if (cut) part[(size_t)(c + j) * BF] = g[j];
+                else if (f_ok) dst[(size_t)j * p.n_out] = g[j];
               }
             }
           }
@@ -305,6 +358,55 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
         tc::fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&acc_empty[b]);
+        if (cut) {
+          // Count this piece in once all eight epilogue warps have written theirs; the last piece of the
+          // tile to arrive adds them all, in the order of the pieces. A block has at most one piece (its
+          // last work), so each of the two barriers is used once; their waits are bounded like the others.
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&cut_bar[0]);
+          if (warp == 2 && lane == 0) {
+            if (tc::mbar_wait(&cut_bar[0], 0)) {
+              __threadfence();
+              const int before = atomicAdd(p.counters + work.cut, 1);
+              __threadfence();
+              *s_last = before == work.pieces - 1;
+              if (*s_last) p.counters[work.cut] = 0;     // every piece has arrived: ready for the next launch
+            } else {
+              atomicExch(p.status, 5);
+              *s_last = 0;
+            }
+            tc::mbar_arrive(&cut_bar[1]);
+          }
+          if (!__all_sync(0xffffffffu, tc::mbar_wait(&cut_bar[1], 0))) {
+            if (lane == 0) atomicExch(p.status, 5);
+            ok = false;
+            break;
+          }
+          if (*s_last) {
+            const float* first = p.scratch + ((size_t)(work.cut * work.pieces) * BT) * BF + quarter * 32 + lane;
+#pragma unroll
+            for (int q = 0; q < RUNS; ++q) {
+              const int c = half * 32 + q * 64;
+              if (c >= live || !f_ok) continue;
+              float* dst = reinterpret_cast<float*>(p.out) + (size_t)(tile.row0 + c) * p.n_out + f;
+              for (int j0 = 0; j0 < 32; j0 += 8) {
+                float sum[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+                for (int piece = 0; piece < work.pieces; ++piece) {
+                  const float* src = first + ((size_t)piece * BT + c + j0) * BF;
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if (c + j0 + j < tile.tokens) sum[j] += __ldcg(src + (size_t)j * BF);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (c + j0 + j < tile.tokens) dst[(size_t)(j0 + j) * p.n_out] = sum[j];
+              }
+            }
+          }
+        }
       }
       ++walk.use[b];
       if (both) ++walk.use[1];
@@ -337,8 +439,8 @@ int launch(const void* x, const void* w0, const void* w1, const Params& p, int m
       !tc::make_map_bf16(&maps.w1, DUAL ? w1 : w0, (uint64_t)p.experts * p.n_out, (uint64_t)p.K, BF))
     return HB_ERR_UNSUPPORTED;
   constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * BF * BK * 2 + BT * BK * 2;
-  static_assert((2 * STAGES + 4) * 8 + 8 <= 256, "the barriers and the tensor-memory slot fit their 256 bytes");
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + 4 * ((size_t)p.experts + 1);
+  static_assert((2 * STAGES + 6) * 8 + 12 <= 256, "the barriers and the tensor-memory slot fit their 256 bytes");
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + 4 * ((size_t)p.experts + 2);
   if (smem > 227 * 1024) return HB_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<DUAL, STAGES, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
@@ -346,8 +448,9 @@ int launch(const void* x, const void* w0, const void* w1, const Params& p, int m
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return HB_ERR_BAD_ARG;
-  const long long upper = (long long)max_tiles * ((p.n_out + BF - 1) / BF) * p.k_splits;    // tiles there can be at most
-  const int grid = (int)(upper < sms ? upper : sms);                            // one persistent block per SM
+  // one persistent block per SM; with fewer tiles than SMs, as many blocks as tiles and their pieces can use
+  const long long upper = (long long)max_tiles * ((p.n_out + BF - 1) / BF) * (p.scratch ? MAX_PIECES : 1);
+  const int grid = (int)(upper < sms ? upper : sms);
   grouped_gemm_tc_kernel<DUAL, STAGES, BT><<<grid, THREADS, smem, stream>>>(maps, p);
   HB_LAUNCH_CHECK();
   return HB_OK;
@@ -377,14 +480,18 @@ extern "C" int hb_moe_gate_up_tc(const void* xs, const int* sorted_entry, const 
   const int bt = few ? BT_SHORT : BT_LONG;
   const int max_tiles = (rows + bt - 1) / bt + (experts < rows ? experts : rows);
   if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
-  Params p{offsets, sorted_entry, scores, act, status, experts, inter, hidden, rows, 1};
+  Params p{offsets, sorted_entry, scores, act, status, experts, inter, hidden, rows, nullptr, nullptr};
   return few ? launch<true, 5, BT_SHORT>(xs, w_gate, w_up, p, max_tiles, stream)
              : launch<true, 4, BT_LONG>(xs, w_gate, w_up, p, max_tiles, stream);
 }
 
 // down projection on tensor cores: act [rows, inter] -> y float32 [rows, hidden].
+// `scratch` (`scratch_floats` floats) and `counters` (`n_counters` ints, zero before the first call and
+// left at zero) let the last, partly filled round of tiles be cut along K; they belong to one launch at
+// a time. With room for fewer than one partial tile per block (or null) the tiles stay whole.
 extern "C" int hb_moe_down_tc(const void* act, const void* w_down, const int* offsets, int experts, float* y, int rows,
-                              int hidden, int inter, int* status, cudaStream_t stream) {
+                              int hidden, int inter, float* scratch, long long scratch_floats, int* counters,
+                              int n_counters, int* status, cudaStream_t stream) {
   if (!act || !w_down || !offsets || !y || !status || rows < 0 || experts <= 0) return HB_ERR_BAD_ARG;
   if (hidden % 8 != 0 || inter % 8 != 0 || hidden <= 0 || inter <= 0) return HB_ERR_UNSUPPORTED;
   if (rows == 0) return HB_OK;
@@ -392,20 +499,13 @@ extern "C" int hb_moe_down_tc(const void* act, const void* w_down, const int* of
   const int bt = few ? BT_SHORT : BT_LONG;
   const int max_tiles = (rows + bt - 1) / bt + (experts < rows ? experts : rows);
   if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
-  // With few tokens per expert (decode batches) there are f_tiles x experts equal tiles; when
-  // that is only a few rounds over the SMs, the last, partly filled round costs much. Halving
-  // the tiles along K halves that tail (measured at 64 tokens over 16 experts: 247 -> 234 us).
-  // The halves are added into y, which then has to start as zeros.
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return HB_ERR_BAD_ARG;
-  const long long one_each = (long long)((hidden + BF - 1) / BF) * (experts < rows ? experts : rows);
-  const int k_splits = (one_each < 8LL * sms && rows <= 64LL * experts && inter >= 32 * BK) ? 2 : 1;
-  if (k_splits > 1) {
-    cudaError_t e = cudaMemsetAsync(y, 0, (size_t)rows * hidden * sizeof(float), stream);
-    if (e != cudaSuccess) return (int)e;
-  }
-  Params p{offsets, nullptr, nullptr, y, status, experts, hidden, inter, rows, k_splits};
+  const bool room = scratch && counters && n_counters >= sms && scratch_floats >= (long long)sms * bt * BF;
+  Params p{offsets, nullptr, nullptr, y, status, experts, hidden, inter, rows, room ? scratch : nullptr, counters};
   return few ? launch<false, 8, BT_SHORT>(act, w_down, nullptr, p, max_tiles, stream)
              : launch<false, 5, BT_LONG>(act, w_down, nullptr, p, max_tiles, stream);
 }
+
+extern "C" long long hb_moe_down_tc_scratch_floats(int sms) { return (long long)sms * BT_LONG * BF; }

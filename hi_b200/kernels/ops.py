@@ -37,7 +37,7 @@ _SIGNATURES = {
     "hb_moe_down": [P, I, P, P, P, I, P, I, I, I, I, P],
     "hb_gather_rows": [P, P, I, P, I, I, P],
     "hb_moe_gate_up_tc": [P, P, P, P, P, I, P, P, I, I, I, P, P],
-    "hb_moe_down_tc": [P, P, P, I, P, I, I, I, P, P],
+    "hb_moe_down_tc": [P, P, P, I, P, I, I, I, P, c_longlong, P, I, P, P],
     "hb_argmax_rows": [P, I, I, I, P, P, P, P, P],
     "hb_ranked_rows": [P, I, I, P, P, P, P, P, P],
     "hb_sample_rows": [P, I, I, P, P, P, P],
@@ -63,6 +63,8 @@ def lib():
             fn = getattr(handle, name)
             fn.argtypes = sig
             fn.restype = c_int
+        handle.hb_moe_down_tc_scratch_floats.argtypes = [I]
+        handle.hb_moe_down_tc_scratch_floats.restype = c_longlong
         _lib = handle
     return _lib
 
@@ -644,6 +646,9 @@ def check_tc_status(device=None) -> None:
         code = int(st.item())
         if code != 0:
             st.zero_()
+            for buffers in (_down_scratch_buffers.get(key),):       # a kernel that gave up may have left a count behind
+                if buffers is not None:
+                    buffers[1].zero_()
             where = {1: "grouped product: the TMA producer waiting for a free stage",
                      2: "grouped product: the MMA issuer waiting for a loaded stage",
                      3: "grouped product: the epilogue waiting for the accumulator",
@@ -712,6 +717,20 @@ def moe_gate_up_tc(x: torch.Tensor, plan: MoePlan, top_k: int, w_gate: torch.Ten
     return act
 
 
+_down_scratch_buffers: dict = {}   # device -> (partial tiles of a cut last round, their counters, left at zero)
+
+
+def _down_scratch(dev):
+    key = (dev.type, dev.index)
+    b = _down_scratch_buffers.get(key)
+    if b is None:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        b = _down_scratch_buffers[key] = (
+            torch.empty(int(lib().hb_moe_down_tc_scratch_floats(sms)), dtype=torch.float32, device=dev),
+            torch.zeros(sms, dtype=torch.int32, device=dev))
+    return b
+
+
 def moe_down_tc(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan) -> torch.Tensor:
     """As :func:`moe_down`, on tcgen05."""
     _need(act, "act", torch.bfloat16); _need(w_down, "w_down", torch.bfloat16)
@@ -720,7 +739,9 @@ def moe_down_tc(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan) -> torch
     if i2 != inter:
         raise KernelError("expert down weights do not match the intermediate size")
     y = torch.empty((rows, hidden), dtype=torch.float32, device=act.device)
+    scratch, counters = _down_scratch(act.device)
     _check(lib().hb_moe_down_tc(_ptr(act), _ptr(w_down), _ptr(plan.offsets), experts, _ptr(y), rows, hidden, inter,
+                                _ptr(scratch), scratch.numel(), _ptr(counters), counters.numel(),
                                 _ptr(_tc_status(act.device)), _stream()), "moe_down_tc")
     TC_USED[0] = True
     return y

@@ -344,12 +344,15 @@ def test_router_plan_and_experts(shape, dt, tol):
 
 @pytest.mark.parametrize("shape", [(256, 4, 1, 128, 300), (5120, 16, 1, 512, 2048), (192, 8, 2, 96, 700), (136, 3, 2, 72, 50),
                                    (1024, 5, 1, 1032, 1000), (64, 2, 1, 64, 129), (256, 4, 1, 2112, 100),
-                                   (128, 2, 2, 2048, 40)])
+                                   (128, 2, 2, 2048, 40), (5120, 4, 1, 1024, 100), (2432, 10, 1, 1600, 300),
+                                   (2560, 8, 2, 1536, 60), (1280, 16, 1, 1536, 64)])
 def test_expert_products_on_tcgen05(shape):
     """The tcgen05 grouped products (TMA + tensor memory) against float32 references: token counts
     per expert above and below a tile and a slot of tensor memory, widths that are no multiple of
-    the tile, K tails, and (the last two shapes) few tokens with a long K, where the down
-    projection is cut in two along K and the halves are added."""
+    the tile, K tails, and (from the seventh shape on) a long K with tiles that do not fill the last
+    round over the SMs, where the down projection cuts those tiles along K into two, three or four
+    pieces (with and without full rounds before them) and the piece that arrives last adds them:
+    the same bits on every call."""
     o = ops()
     H, E, k, I, n = shape
     dt = torch.bfloat16
@@ -375,10 +378,15 @@ def test_expert_products_on_tcgen05(shape):
     o.check_tc_status()
     close(act, act_ref, 2e-2, f"tcgen05 gate/up {shape}")
     a = act_ref.to(dt)
-    y = o.moe_down_tc(a.to(DEV), wd.to(DEV), plan)
+    a_d, wd_d = a.to(DEV), wd.to(DEV)
+    y = o.moe_down_tc(a_d, wd_d, plan)
     o.check_tc_status()
     y_ref = torch.einsum("ri,rhi->rh", a.float(), wd.float()[expert_of_slot])
     close(y, y_ref, 2e-5, f"tcgen05 down {shape}")
+    for _ in range(3):                 # pieces arrive in another order; their counters were left at zero
+        again = o.moe_down_tc(a_d, wd_d, plan)
+        o.check_tc_status()
+        assert torch.equal(again, y), f"tcgen05 down {shape}: two calls differ"
     # and against the general kernels on the same inputs
     close(o.moe_gate_up(x.to(DEV), plan, k, wg.to(DEV), wu.to(DEV), scores, False), act_ref, 2e-2, "general gate/up")
     assert not o.moe_tc_supported(x.float().to(DEV), wg.float().to(DEV))
