@@ -7,11 +7,17 @@ crates/hi-local/src/main.rs:60-83, and the captured-batch replay of
 crates/hi-mlx/src/models.rs:11709-11831.)
 
     trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
-              [--page-size P] [--num-pages-global G] [--num-pages-chunk K] [--max-live R]
+              [--page-size P] [--num-pages-global G] [--num-pages-chunk K] [--max-live R] [--cpu]
 
 ``--max-tokens`` sizes every page pool (rounded up to whole pages); ``--num-pages-global`` and
 ``--num-pages-chunk`` size the pool of the layers that keep every key and the pool of the
 windowed layers on their own, so a trace can be driven into the exhaustion of one of them.
+
+``--cpu`` (with ``--dtype float32``) answers the same trace from the CPU reference execution
+instead: no GPU, no cache and no step function, every request recomputed whole by the host
+runtime's plain loops whenever logits of it are wanted (the reference's ``--execution
+cpu-reference`` beside its GPU path, crates/hi-cuda/src/lib.rs:205-226). It is the third arm that
+a trace can be held against, and it runs where there is no GPU.
 
 Standard input: one JSON object per line,
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
@@ -45,6 +51,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--num-pages-chunk", type=int, default=None,
                    help="pages of the pool of windowed layers (default: --max-tokens in pages)")
     p.add_argument("--max-live", type=int, default=MAX_LIVE_REQUESTS, help="requests that may be live at a time")
+    p.add_argument("--cpu", action="store_true",
+                   help="the CPU reference execution (float32, whole sequences recomputed, no cache) instead of the engine")
     p.add_argument("--dump-taps", action="store_true",
                    help="debug: also write <step>.taps.json with the integer tensors parts report "
                         "(the router's expert choices, in the step's flat token order)")
@@ -54,11 +62,11 @@ def build_parser() -> argparse.ArgumentParser:
 def run(args, stdin=None, stdout=None) -> int:
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
-    import numpy as np
-
+    os.makedirs(args.out, exist_ok=True)
+    if args.cpu:
+        return _run_on_cpu(args, stdin, stdout)
     from .core import Engine, StepEntry
 
-    os.makedirs(args.out, exist_ok=True)
     page = args.page_size
     if args.max_tokens < 1 or args.max_live < 1 or (args.num_pages_global or 1) < 1 or (args.num_pages_chunk or 1) < 1:
         raise SystemExit("trace_run: --max-tokens, --max-live and the page counts must be positive")
@@ -88,6 +96,47 @@ def run(args, stdin=None, stdout=None) -> int:
             os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
         for rid in obj.get("end", []):
             engine.finish(rid)
+        print(f"done {step}", file=stdout, flush=True)
+    return 0
+
+
+def _run_on_cpu(args, stdin, stdout) -> int:
+    """The same protocol, answered by :class:`~hi_b200.engine.cpu_reference.CpuReference`: it keeps
+    each live request's tokens and runs them whole for every step that wants logits of it."""
+    import numpy as np
+
+    from .cpu_reference import CpuReference
+
+    if args.dtype != "float32":
+        raise SystemExit("trace_run: --cpu is the float32 reference execution; give --dtype float32")
+    if args.dump_taps:
+        raise SystemExit("trace_run: --dump-taps reports what the engine's parts see; it has no meaning with --cpu")
+    ref = CpuReference.from_dir(args.model)
+    held = {}
+    for line in stdin:
+        line = line.strip()
+        if not line:
+            continue
+        obj = json.loads(line)
+        step, rows = obj["step"], []
+        for e in obj.get("entries", []):
+            if len(held) >= args.max_live and e["id"] not in held:
+                raise SystemExit(f"trace_run: more than --max-live {args.max_live} requests are live")
+            tokens = held.setdefault(e["id"], [])
+            first = len(tokens)
+            tokens.extend(int(t) for t in e["tokens"])
+            want = [first + int(w) for w in e.get("want", [])]
+            if any(not first <= w < len(tokens) for w in want):
+                raise SystemExit(f"trace_run: step {step}, request {e['id']!r}: a wanted place is outside its tokens")
+            if want:
+                rows.append(ref.forward(tokens, want=want).numpy())
+        if rows:
+            arr = np.concatenate(rows, axis=0).astype("<f4", copy=False)
+            tmp = os.path.join(args.out, f"{step}.f32.tmp")
+            arr.tofile(tmp)
+            os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
+        for rid in obj.get("end", []):
+            held.pop(rid, None)
         print(f"done {step}", file=stdout, flush=True)
     return 0
 

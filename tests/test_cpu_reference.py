@@ -123,3 +123,37 @@ def test_text_in_and_out_where_the_folder_has_a_tokenizer(model_dirs, tmp_path):
     assert js["generated_text"].split() == [f"w{t}" for t in js["generated_tokens"]]
     bare = run_cli("run", mdir, "--cpu", "--prompt", "w5", "--dtype", "float32")
     assert bare.returncode != 0 and "tokenizer.json" in bare.stderr
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_trace_run_on_the_cpu_in_the_four_ways_of_cutting(name, model_dirs, tmp_path):
+    """bin/trace_run --cpu, run as a user would where there is no GPU: the CPU arm of the replay.
+    Whole, the last 32 tokens one by one, portions down to two tokens, and mixed with other
+    requests; every row against the test-suite's plain model."""
+    cfg, mdir = model_dirs[name]
+    lengths = {"A": [23, 49, 64, 150], "B": [29, 94, 131]}[name]
+    reqs = {f"r{i}": h.random_tokens(cfg, n, seed=300 + i) for i, n in enumerate(lengths)}
+    traces = {"whole": h.trace_whole(reqs), "tail": h.trace_tail_decode(reqs), "portions": h.trace_portions(reqs),
+              "mixed": h.trace_mixed(reqs, max_tokens=448, page=64, seed=5)}
+    steps = [([(f"{regime}:{r}", t, w) for r, t, w in entries], [f"{regime}:{r}" for r in end])
+             for regime, tr in traces.items() for entries, end in tr]
+    all_reqs = {f"{regime}:{r}": toks for regime in traces for r, toks in reqs.items()}
+    got = h.replay_subprocess(mdir, "float32", steps, 448, str(tmp_path / "out"), h.vocab_of(cfg), extra=["--cpu"])
+    h.compare_with_plain(cfg, h.read_weights(mdir), all_reqs, got, TOL, what=f"trace_run --cpu, tiny {name}")
+    for rid, toks in all_reqs.items():
+        assert sorted(got[rid]) == list(range(len(toks))), f"{rid}: not every position came back"
+
+
+def test_trace_run_on_the_cpu_refuses_what_it_cannot_mean(model_dirs, tmp_path):
+    import os
+    import subprocess
+    import sys
+
+    _cfg, mdir = model_dirs["A"]
+    base = [sys.executable, os.path.join(h.ROOT, "bin", "trace_run"), "--model", mdir, "--out", str(tmp_path / "o"),
+            "--max-tokens", "64", "--cpu"]
+    proc = subprocess.run(base + ["--dtype", "bfloat16"], input="", capture_output=True, text=True, timeout=300)
+    assert proc.returncode != 0 and "float32" in proc.stderr
+    trace = h.trace_json([([("a", [1, 2, 3], [3])], [])])
+    proc = subprocess.run(base + ["--dtype", "float32"], input=trace, capture_output=True, text=True, timeout=300)
+    assert proc.returncode != 0 and "outside its tokens" in proc.stderr
