@@ -4,12 +4,15 @@
 //   warp 0      one lane issues TMA loads: the Q tile once, then K and V tiles of 64 key positions
 //               (one box per page, 128-byte swizzle) into a 2-stage ring;
 //   warp 1      allocates tensor memory; one lane issues S = Q K^T (tcgen05.mma, M 128, N 64) into
-//               one of two S buffers and, a tile behind, O += P V (P from shared memory, V as the
-//               MN-major operand), so the next S is computed while the softmax works on this one;
+//               one of two S buffers and, a tile behind, O += P V (P read from tensor memory, where
+//               it lies over its own S; V from shared memory as the MN-major operand), so the next
+//               S is computed while the softmax works on this one;
 //   warps 2..5  softmax: thread r owns row r (tensor-memory lane r): it reads its S row with
 //               tcgen05.ld, masks by absolute position (causal, chunk, sliding window), keeps the
 //               running max and sum in float32, rescales its O row in tensor memory when the max
-//               moved, and writes P as bfloat16 into shared memory in the swizzled K-major layout.
+//               moved, and writes P as bfloat16 back into tensor memory (tcgen05.st): the products
+//               are bound by what the SM can read from shared memory, and P from there would add a
+//               fifth to it.
 // Every mbarrier wait is bounded; on a time-out a code goes to `status` and the block leaves
 // through the common exit, where tensor memory is freed.
 #include <cuda.h>
@@ -47,7 +50,7 @@ __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const Args a) {
   constexpr int DBLK = HD / 64;                 // 64-dim blocks of a row
-  constexpr int QBYTES = BQ * HD * 2, KBYTES = BKEYS * HD * 2, PBYTES = BQ * BKEYS * 2;
+  constexpr int QBYTES = BQ * HD * 2, KBYTES = BKEYS * HD * 2;
   constexpr int QBLOCK = BQ * 128;              // bytes of one [128 rows x 64 elements] swizzled block of Q
   constexpr int KVBLOCK = BKEYS * 128;          // the same for a K or V tile (rows = key positions)
   constexpr int S_COLS = BKEYS;                 // columns of one S buffer
@@ -63,8 +66,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
   uint8_t* q_s = smem;
   uint8_t* kv_s = q_s + QBYTES;                 // [2 stages][K | V]
-  uint8_t* p_s = kv_s + 4 * KBYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + PBYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + 4 * KBYTES);
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // 2   K and V have barriers of their own: a K buffer is free
   uint64_t* k_empty = bars + 3;       // 2   as soon as its S is computed, long before its V is used,
@@ -154,12 +156,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       bool ok = tc::mbar_wait(q_full, 0);
       if (!ok) atomicExch(a.status, 12);
       tc::fence_after();
-      const uint32_t q_addr = tc::smem_u32(q_s), p_addr = tc::smem_u32(p_s);
+      const uint32_t q_addr = tc::smem_u32(q_s);
       for (int j = 0; j <= nt && ok; ++j) {
         if (j < nt) {
           const int s = j & 1;
           if (!tc::mbar_wait(&k_full[s], (j >> 1) & 1)) { atomicExch(a.status, 13); ok = false; break; }
           if (j >= 2 && !tc::mbar_wait(&s_free[s], ((j >> 1) - 1) & 1)) { atomicExch(a.status, 14); ok = false; break; }
+          // S_j goes where P_{j-2} lies: the product that reads that P must be through (it is the last one
+          // committed to this barrier so far, so the parity is its own)
+          if (j >= 2 && !tc::mbar_wait(pv_done, (j - 2) & 1)) { atomicExch(a.status, 24); ok = false; break; }
           tc::fence_after();
           const uint32_t k_addr = tc::smem_u32(kv_s + s * 2 * KBYTES);
 #pragma unroll
@@ -176,10 +181,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!tc::mbar_wait(p_ready, i & 1)) { atomicExch(a.status, 15); ok = false; break; }
           tc::fence_after();
           const uint32_t v_addr = tc::smem_u32(kv_s + s * 2 * KBYTES + KBYTES);
+          const uint32_t p_tmem = tmem + s * S_COLS;     // P_i lies over the first half of S_i's columns
 #pragma unroll
           for (int k = 0; k < BKEYS / 16; ++k) {
-            tc::mma(tmem_o, tc::desc_kmajor(p_addr + k * 32), tc::desc_mnmajor(v_addr + k * 2048, KVBLOCK), idesc_pv,
-                   (i | k) != 0);
+            tc::mma_a_tmem(tmem_o, p_tmem + k * 8, tc::desc_mnmajor(v_addr + k * 2048, KVBLOCK), idesc_pv, (i | k) != 0);
           }
           tc::commit(&v_empty[s]);
           tc::commit(pv_done);
@@ -268,7 +273,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       l = l * corr + sum;
       if (j > 0) {
-        // the previous P V product must have finished: O is stable and the P buffer is free
+        // The previous P V product must have finished: O is stable. The wait also keeps the warps
+        // and the MMA issuer within a tile of one another: that product started only after every
+        // warp had handed over its P of the tile before and the issuer had seen it, so the one
+        // barrier that counts the hand-overs tile after tile never runs a phase ahead of anyone.
         if (!__all_sync(0xffffffffu, tc::mbar_wait(pv_done, (j - 1) & 1))) {
           if (lane == 0) atomicExch(a.status, 17);
           ok = false;
@@ -286,18 +294,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
       }
-      // P row r, bfloat16, K-major with the 128-byte swizzle: 16-byte chunk q of row r sits at chunk q ^ (r % 8)
-      uint8_t* prow = p_s + (r / 8) * 1024 + (r % 8) * 128;
+      // P row r as bfloat16 goes back into tensor memory, over the first 32 columns of the S row it
+      // was made from (two keys a column): the P V product takes it from there as its A operand,
+      // so P costs no shared-memory traffic. The product that read the P two tiles ago from these
+      // columns ran before the Q K^T that refilled them (one thread issues them, in that order).
+      {
+        uint32_t packed[BKEYS / 2];
 #pragma unroll
-      for (int q = 0; q < BKEYS / 8; ++q) {
-        uint4 pack;
-        uint32_t* w = reinterpret_cast<uint32_t*>(&pack);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 hh = __floats2bfloat162_rn(sv[q * 8 + 2 * i], sv[q * 8 + 2 * i + 1]);
-          w[i] = *reinterpret_cast<uint32_t*>(&hh);
+        for (int i = 0; i < BKEYS / 2; ++i) {
+          __nv_bfloat162 hh = __floats2bfloat162_rn(sv[2 * i], sv[2 * i + 1]);
+          packed[i] = *reinterpret_cast<uint32_t*>(&hh);
         }
-        *reinterpret_cast<uint4*>(prow + ((q ^ (r % 8)) * 16)) = pack;
+        tc::st32_nowait(tmem + lane_addr + sb * S_COLS, packed);
+        tc::wait_st();
       }
       if (j == nt - 1 && (p_last + 1) % BKEYS != 0) {
         // Value rows of positions past the portion's end hold whatever the page held before
@@ -315,8 +324,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(vrow + blk * KVBLOCK + q * 16) = make_uint4(0, 0, 0, 0);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
       tc::fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(p_ready);
@@ -365,7 +374,7 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const Args& 
       !tc::make_map_bf16(&mk, k_pages, (uint64_t)pool_rows, HD, a.box_rows) ||
       !tc::make_map_bf16(&mv, v_pages, (uint64_t)pool_rows, HD, a.box_rows))
     return HB_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKEYS * HD * 2 + (size_t)BQ * BKEYS * 2 + 256;
+  const size_t smem = (size_t)BQ * HD * 2 + 4 * (size_t)BKEYS * HD * 2 + 256;
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int q_tiles = (max_new + BQ - 1) / BQ;
