@@ -324,12 +324,19 @@ router_logits_tiled_kernel(const float* __restrict__ x, const TW* __restrict__ w
         const int e = min(e0 + es + q, experts - 1);         // rows past the last expert: computed, not used
         hb::load8(w + (size_t)e * hidden + j, wv[q]);
       }
+      // two experts an instruction (fma on a pair of floats): each logit still adds its products in
+      // the same order, so the sums are the ones the single fma gives
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
+      for (int q = 0; q < 4; q += 2)
 #pragma unroll
-        for (int tt = 0; tt < ROUTER_TOK; ++tt)
+        for (int tt = 0; tt < ROUTER_TOK; ++tt) {
+          float2 a2 = make_float2(acc[tt][es + q], acc[tt][es + q + 1]);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[tt][es + q] += xv[tt][i] * wv[q][i];
+          for (int i = 0; i < 8; ++i)
+            a2 = __ffma2_rn(make_float2(xv[tt][i], xv[tt][i]), make_float2(wv[q][i], wv[q + 1][i]), a2);
+          acc[tt][es + q] = a2.x;
+          acc[tt][es + q + 1] = a2.y;
+        }
     }
   }
 #pragma unroll
@@ -631,8 +638,8 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
     return HB_ERR_BAD_ARG;
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
   if (n == 0) return HB_OK;
-  if (x_dtype == HB_DTYPE_F32 && n >= 192 && hidden % 8 == 0 && (w_dtype == HB_DTYPE_F32 || w_dtype == HB_DTYPE_BF16)) {
-    // many tokens (measured: faster than one block per token from about 200): register tiles of
+  if (x_dtype == HB_DTYPE_F32 && n >= 96 && hidden % 8 == 0 && (w_dtype == HB_DTYPE_F32 || w_dtype == HB_DTYPE_BF16)) {
+    // many tokens (measured: faster than one block per token from about 100): register tiles of
     // 4 tokens x 16 experts; with more than 16 experts the
     // selection needs the stored logits of all block columns
     dim3 grid((n + ROUTER_TOK - 1) / ROUTER_TOK, (experts + ROUTER_EXP - 1) / ROUTER_EXP);
