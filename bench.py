@@ -278,6 +278,28 @@ def long_context_point(engine, cfg, args, pk, vocab, cpu_gen):
         engine.finish(rid)
     out["mixed_steps"] = {"portion_tokens": portion, "decoding_requests": 3, "portions": portions,
                           "chunked_pages_in_use_after_each_step": pages, "page_tokens": PAGE}
+    # a short portion far into a context: few blocks with long runs of keys, which the layers that
+    # see every key share out among several blocks each; timed with that and without
+    from hi_b200.kernels import ops
+
+    short = 512
+    engine.assume_cached("Ls", ctx - 4 * short)
+    toks = torch.randint(0, vocab, (3 * short,), generator=cpu_gen).tolist()
+    times = []
+    for i, min_tiles in enumerate((None, None, 1 << 30)):       # the first runs untimed
+        keep = ops.PREFILL_SPLIT_MIN_TILES
+        if min_tiles:
+            ops.PREFILL_SPLIT_MIN_TILES = min_tiles
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step([StepEntry("Ls", toks[i * short:(i + 1) * short], [])])
+        end.record()
+        torch.cuda.synchronize()
+        ops.PREFILL_SPLIT_MIN_TILES = keep
+        times.append(start.elapsed_time(end))
+    engine.finish("Ls")
+    out["short_portion"] = {"tokens": short, "offset": ctx - 3 * short, "ms": round(times[1], 2),
+                            "ms_one_block_per_query_tile": round(times[2], 2)}
     return out
 
 

@@ -62,7 +62,8 @@ int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages
 int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                             int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_tokens,
                             int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
-                            int window, float scale, int skip_single, int* status, cudaStream_t stream);
+                            int window, float scale, int skip_single, int key_splits, float* part_acc, float* part_ml,
+                            int* status, cudaStream_t stream);
 
 // mode: bit 0 = scores are the softmax over all experts (clear: the sigmoid of the chosen logit),
 // bit 1 = the chosen scores are divided by their sum

@@ -47,6 +47,12 @@ struct Args {
   int* status;
   int table_stride, nh, nkv, page_size, chunk, window, skip_single, box_rows;
   float scale_log2;          // softmax scale * log2(e)
+  // With key_splits > 1 every (query tile, head) is `key_splits` blocks, each over its share of the
+  // key tiles; a block leaves its rows unnormalised in part_acc [row][split][head_dim] with (max,
+  // sum) in part_ml [row][split][2] (max in natural-log units), and hb_attention_merge combines them.
+  int key_splits;
+  float* part_acc;
+  float* part_ml;
 };
 
 template <int HD>
@@ -86,14 +92,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   // Blocks start in the order x, y, z: the heads are x and the query tiles y, latest first, so
   // the tiles that read the most keys start first for every head and the short ones fill the end.
-  const int seq = blockIdx.z, h = blockIdx.x;
+  const int seq = blockIdx.z, h = blockIdx.x % a.nh, piece = blockIdx.x / a.nh;
   const int qt = gridDim.y - 1 - blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq_begin = a.cu_seqlens[seq], seq_end = a.cu_seqlens[seq + 1];
   const int tok0 = seq_begin + qt * BQ;
   const int n_valid = min(BQ, seq_end - tok0);
   if (n_valid <= 0) return;
-  if (a.skip_single && seq_end - seq_begin == 1) return;
+  // a row that this block leaves out weighs nothing in the merge
+  auto no_part = [&](int row) {
+    float* ml = a.part_ml + (((size_t)(tok0 + row) * a.nh + h) * a.key_splits + piece) * 2;
+    ml[0] = -INFINITY;
+    ml[1] = 0.f;
+  };
+  if (a.skip_single && seq_end - seq_begin == 1) {
+    if (a.key_splits > 1 && threadIdx.x == 0) no_part(0);
+    return;
+  }
   const int kvh = h / (a.nh / a.nkv);
   const int p_first = a.positions[tok0];
   const int p_last = p_first + n_valid - 1;
@@ -103,8 +118,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (a.window > 0 && pos - a.window + 1 > lo) lo = pos - a.window + 1;
     return lo;
   };
-  const int tile_begin = first_visible(p_first) / BKEYS;
-  const int nt = p_last / BKEYS - tile_begin + 1;
+  int tile_begin = first_visible(p_first) / BKEYS;
+  int nt = p_last / BKEYS - tile_begin + 1;
+  if (a.key_splits > 1) {                       // this block's share of the key tiles
+    const int share = (nt + a.key_splits - 1) / a.key_splits;
+    tile_begin += piece * share;
+    nt = min(share, nt - piece * share);
+    if (nt <= 0) {
+      if ((int)threadIdx.x < n_valid) no_part(threadIdx.x);
+      return;
+    }
+  }
 
   if (threadIdx.x == 0) {
     tc::mbar_init(q_full, 1);
@@ -330,7 +354,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc::st32_nowait(tmem + lane_addr + sb * S_COLS, packed);
         tc::wait_st();
       }
-      if (j == nt - 1 && (p_last + 1) % BKEYS != 0) {
+      if (tile_begin + j == p_last / BKEYS && (p_last + 1) % BKEYS != 0) {
         // Value rows of positions past the portion's end hold whatever the page held before
         // (another request's numbers, possibly not finite): P is zero there, but 0 x NaN is NaN.
         // Once the V tile has landed, the threads of those rows zero them.
@@ -357,6 +381,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) atomicExch(a.status, 18);
       } else {
         tc::fence_after();
+        if (a.key_splits > 1) {
+          // this share of the keys only: the row as it is, with its max and sum, for the merge
+          const size_t at = ((size_t)(tok0 + r) * a.nh + h) * a.key_splits + piece;
+          if (row_ok) {
+            a.part_ml[at * 2] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;
+            a.part_ml[at * 2 + 1] = l;
+          }
+#pragma unroll 1
+          for (int c = 0; c < HD; c += 32) {
+            float o[32];
+            tc::ld32(tmem_o + lane_addr + c, o);
+            if (row_ok) {
+              float4* dst4 = reinterpret_cast<float4*>(a.part_acc + at * HD + c);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) dst4[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+          }
+        } else {
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* dst = a.out + ((size_t)(tok0 + r) * a.nh + h) * HD;
 #pragma unroll 1
@@ -376,6 +418,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               *reinterpret_cast<uint4*>(dst + c + i) = pack;
             }
           }
+        }
         }
       }
     }
@@ -401,7 +444,8 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const Args& 
   if (e != cudaSuccess) return (int)e;
   const int q_tiles = (max_new + BQ - 1) / BQ;
   if (q_tiles > 65535 || n_seqs > 65535) return HB_ERR_UNSUPPORTED;
-  dim3 grid(a.nh, q_tiles, n_seqs);
+  if ((long long)a.nh * a.key_splits > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
+  dim3 grid(a.nh * a.key_splits, q_tiles, n_seqs);
   attn_prefill_tc_kernel<HD><<<grid, THREADS, smem, stream>>>(mq, mk, mv, a);
   HB_LAUNCH_CHECK();
   return HB_OK;
@@ -411,23 +455,27 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const Args& 
 
 // bfloat16, head_dim 64 or 128, page_size a multiple of 16 that divides 64 or is a multiple of it.
 // Arguments as hb_attention_prefill, plus the number of rows of `q`, the number of pages of the
-// pools, and `status` (one int on the device, zero before the call; nonzero afterwards = a wait
+// pools, `key_splits` (1, or how many blocks share the key tiles of a query tile and head: the rows
+// then go unnormalised to `part_acc` [n_tokens * nh][key_splits][hd] and `part_ml`
+// [n_tokens * nh][key_splits][2] for hb_attention_merge, and `out` is not written), and `status` (one int on the device, zero before the call; nonzero afterwards = a wait
 // timed out). HB_ERR_UNSUPPORTED for other shapes: the caller uses hb_attention_prefill.
 extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                        int table_stride, const int* cu_seqlens, const int* positions, void* out,
                                        int n_tokens, int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd,
-                                       int page_size, int chunk, int window, float scale, int skip_single, int* status,
+                                       int page_size, int chunk, int window, float scale, int skip_single,
+                                       int key_splits, float* part_acc, float* part_ml, int* status,
                                        cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out || !status) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || n_pages <= 0 || n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 ||
-      page_size <= 0 || table_stride <= 0 || chunk < 0 || window < 0)
+      page_size <= 0 || table_stride <= 0 || chunk < 0 || window < 0 || key_splits < 1 || key_splits > 64 ||
+      (key_splits > 1 && (!part_acc || !part_ml)))
     return HB_ERR_BAD_ARG;
   if (page_size % 16 != 0 || !(BKEYS % page_size == 0 || page_size % BKEYS == 0)) return HB_ERR_UNSUPPORTED;
   if (n_seqs > 65535 || nh > 65535) return HB_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return HB_ERR_UNSUPPORTED;       // the largest raw score is taken for the largest scaled one
   if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return HB_OK;
   Args a{block_table, cu_seqlens, positions, (__nv_bfloat16*)out, status, table_stride, nh, nkv, page_size, chunk,
-         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f};
+         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml};
   const long long pool_rows = (long long)n_pages * nkv * page_size;
   if (hd == 128) return launch<128>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 64) return launch<64>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);

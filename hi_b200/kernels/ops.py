@@ -29,7 +29,7 @@ _SIGNATURES = {
     "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P],
     "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
-    "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
+    "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, P, P, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, I, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
     "hb_router_plan": [P, I, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P],
@@ -488,8 +488,10 @@ def prefill_attention_tc_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: 
 def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                          cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, max_new: int, chunk: int,
                          window: int, scale: float, skip_single: bool = False,
-                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """As :func:`prefill_attention`, on tcgen05 (S, P V and O in tensor memory, TMA page loads)."""
+                         out: Optional[torch.Tensor] = None, key_splits: int = 1) -> torch.Tensor:
+    """As :func:`prefill_attention`, on tcgen05 (S, P V and O in tensor memory, TMA page loads).
+    ``key_splits`` > 1: that many blocks share the key tiles of every (query tile, head) and a
+    merge kernel combines their rows (see :func:`prefill_key_splits`)."""
     _need(q, "q", torch.bfloat16); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
         _need(t, nm, torch.int32)
@@ -503,13 +505,59 @@ def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
         raise KernelError("cu_seqlens / block_table do not match the number of requests")
     if out is None:
         out = torch.empty_like(q)
+    key_splits = int(key_splits)
+    part_acc = part_ml = None
+    if key_splits > 1:
+        part_acc = torch.empty((n * nh, key_splits, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n * nh, key_splits, 2), dtype=torch.float32, device=q.device)
     _check(lib().hb_attention_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                          block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(out), n, n_pages,
                                          n_seqs, int(max_new), nh, nkv, hd, page_size, int(chunk), int(window),
-                                         float(scale), int(skip_single), _ptr(_tc_status(q.device)), _stream()),
+                                         float(scale), int(skip_single), key_splits, _ptr(part_acc) if part_acc is not None else None,
+                                         _ptr(part_ml) if part_ml is not None else None, _ptr(_tc_status(q.device)),
+                                         _stream()),
            "attention_prefill_tc")
     TC_USED[0] = True
+    if key_splits > 1:
+        _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, key_splits,
+                                        _stream()), "attention_merge")
     return out
+
+
+_sm_counts: dict = {}
+
+
+def sm_count(device) -> int:
+    key = torch.device(device)
+    if key not in _sm_counts:
+        _sm_counts[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_counts[key]
+
+
+PREFILL_RESIDENT_BLOCKS_PER_SM = 2     # of the tcgen05 prefill kernel (tensor memory: 256 of 512 columns each)
+PREFILL_SPLIT_MIN_TILES = 512          # key tiles (of 64 keys) a block must have before its keys are shared out
+PREFILL_SPLIT_MIN_SHARE = 128          # and the fewest a share may get
+
+
+def prefill_key_splits(blocks: int, key_tiles: int, sms: int) -> int:
+    """How many blocks should share the key tiles of each (query tile, head) of the tcgen05 prefill
+    kernel, when the ``blocks`` of a launch all have about ``key_tiles`` key tiles (a short portion
+    far into a long context). The kernel runs two blocks per SM; with fewer blocks than that, or a
+    few more, most of the GPU waits for the last ones. Measured at 65,000 cached tokens, 40 heads:
+    128 new tokens 933 -> 256 us in six shares, 256 tokens 935 -> 448 us in three, 512 tokens
+    1,116 -> 795 us in five, 1,024 tokens 2,163 -> 1,521 us in four; nothing gained at 16,000
+    cached tokens, and a loss from 2,048 new tokens on (4,096: 5.09 -> 5.88 ms in three: the
+    unnormalised rows written out and merged cost more than the fuller last round gains).
+    So: only launches of up to 1.25 rounds with at least 512 key tiles; the number of shares (up to
+    8, at least 128 tiles each) that fills the rounds best, the fewest among those within 0.05."""
+    places = PREFILL_RESIDENT_BLOCKS_PER_SM * max(int(sms), 1)
+    if blocks <= 0 or blocks > 1.25 * places or key_tiles < PREFILL_SPLIT_MIN_TILES:
+        return 1
+    fill = {k: (blocks * k / places) / -(-blocks * k // places) for k in range(1, 9)
+            if k == 1 or key_tiles // k >= PREFILL_SPLIT_MIN_SHARE}
+    best = max(fill.values())
+    choice = min(k for k, f in fill.items() if f >= best - 0.05)
+    return choice if fill[choice] > fill[1] else 1
 
 
 # --------------------------------------------------------------------------- experts

@@ -85,6 +85,21 @@ class AttentionMixer(Part):
         b_o = fetch(f"{self.prefix}.o_proj.bias")
         self.b_o = None if b_o is None else b_o.to(self.w_o.dtype).contiguous()
 
+    def _key_splits(self, ctx, chunk: int, sliding: int, single: bool, device) -> int:
+        """Portions far into long contexts on a layer that sees every key: all blocks of the
+        tensor-core prefill kernel then have about the same many key tiles, and a partly filled
+        last round of blocks is worth splitting the keys for (ops.prefill_key_splits)."""
+        if chunk or sliding:
+            return 1
+        portions = [(s, n) for s, n in zip(ctx.start_pos, ctx.n_new) if n > 1 or not single]
+        if not portions:
+            return 1
+        shortest, longest_new = min(s for s, _n in portions), max(n for _s, n in portions)
+        if shortest < 2 * longest_new:
+            return 1
+        blocks = self.nh * sum(-(-n // ops.PREFILL_TC_MIN_TOKENS) for _s, n in portions)
+        return ops.prefill_key_splits(blocks, shortest // 64, ops.sm_count(device))
+
     def forward(self, normed, ctx, cache):
         qkv = linear(normed, self.w_qkv, bias=self.b_qkv)
         positions = ctx.positions
@@ -120,9 +135,13 @@ class AttentionMixer(Part):
             # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync
             tc = ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS and ops.prefill_attention_tc_supported(
                 q.dtype, self.nh, self.nkv, self.hd, ctx.page_size)
-            kernel = ops.prefill_attention_tc if tc else ops.prefill_attention
-            o = kernel(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
-                       ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale, skip_single=single)
+            if tc:
+                o = ops.prefill_attention_tc(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
+                                             ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale, skip_single=single,
+                                             key_splits=self._key_splits(ctx, chunk, sliding, single, q.device))
+            else:
+                o = ops.prefill_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
+                                          ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale, skip_single=single)
             if single:
                 # single tokens beside portions: their long key ranges go through the split decode kernel
                 rows = ctx.decode_rows

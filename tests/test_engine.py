@@ -582,3 +582,46 @@ def test_the_tensor_core_kernels_take_the_sizes_they_are_built_for(tmp_path):
         # and what they returned: every row against the plain model (bfloat16 given its own expert choices)
         h.compare_with_plain(cfg, h.read_weights(mdir), {"a": toks}, got, tol, forced=forced if dtype == "bfloat16" else None,
                              what=f"sizes of the fast kernels, {dtype}", margin=h.ROUTING_MARGIN)
+
+
+def test_portions_far_into_a_context_share_their_keys_among_blocks(tmp_path, monkeypatch):
+    """A short portion behind a long context gives the tensor-core prefill attention few blocks
+    with long runs of keys; the global layers then let several blocks share a block's keys and a
+    merge kernel combines their rows. The thresholds are lowered so that a 700-token request shows
+    it (in use they ask for 32,768 cached tokens): portions of 130 and 140 tokens behind 384 and
+    514, two requests side by side, every row against the plain model."""
+    from hi_b200.engine.core import Engine
+    from hi_b200.kernels import ops
+
+    monkeypatch.setattr(ops, "PREFILL_SPLIT_MIN_TILES", 4)
+    monkeypatch.setattr(ops, "PREFILL_SPLIT_MIN_SHARE", 1)
+    cfg = dict(TINY_A, hidden_size=128, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+               attention_chunk_size=256, intermediate_size=64, intermediate_size_mlp=128, vocab_size=211,
+               num_hidden_layers=4, nope_layer_interval=2)
+    mdir = h.make_model(str(tmp_path / "m"), cfg, seed=9, std=0.05)
+    reqs = {"a": h.random_tokens(cfg, 700, seed=1), "b": h.random_tokens(cfg, 660, seed=2)}
+    cuts = {"a": [384, 130, 140, 46], "b": [400, 131, 129]}
+    steps, at = [], {r: 0 for r in reqs}
+    for i in range(4):
+        entries = []
+        for r, sizes in cuts.items():
+            if i < len(sizes):
+                n = sizes[i]
+                entries.append((r, reqs[r][at[r]: at[r] + n], list(range(n))))
+                at[r] += n
+        steps.append((entries, [r for r in reqs if at[r] == len(reqs[r]) and any(e[0] == r for e in entries)]))
+    assert all(at[r] == len(reqs[r]) for r in reqs)
+    seen = []
+    real = ops.prefill_attention_tc
+
+    def spy(*args, **kw):
+        seen.append(kw.get("key_splits", 1))
+        return real(*args, **kw)
+
+    monkeypatch.setattr(ops, "prefill_attention_tc", spy)
+    eng = Engine.from_dir(mdir, dtype="bfloat16", kv_page_size=16, kv_cache_tokens=1536, max_active_requests=2)
+    got, forced = h.replay_in_process(eng, steps, record_routing=True)
+    assert max(seen) > 1, f"no launch shared its keys (shares seen: {sorted(set(seen))})"
+    assert 1 in seen, "the layers with chunked attention keep one block per query tile and head"
+    h.compare_with_plain(cfg, h.read_weights(mdir), reqs, got, h.TOL_BF16, forced=forced,
+                         what="keys shared among blocks", margin=h.ROUTING_MARGIN)

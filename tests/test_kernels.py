@@ -60,13 +60,13 @@ def test_embed_and_norm(dt, tol):
 @pytest.mark.parametrize("dt,tol", DT)
 def test_swiglu(dt, tol):
     o = ops()
-    gu = (torch.randn(13, 2 * 72) * 2).to(dt)
+    gu = (torch.randn(13, 2 * 72, generator=torch.Generator().manual_seed(13)) * 2).to(dt)
     g, u = gu[:, :72].float(), gu[:, 72:].float()
     close(o.swiglu(gu.to(DEV)), g * torch.sigmoid(g) * u, tol, "swiglu")
 
 
 def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, interleaved, qk_norm, temp, seed,
-               split=True, tc=False):
+               split=True, tc=False, key_splits=()):
     """Two phases: fill `starts` tokens of every sequence, then run `lens` new tokens; returns the
     kernel's q and attention output for the second phase and the plain reference's."""
     g = torch.Generator().manual_seed(seed)
@@ -104,6 +104,10 @@ def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, 
             if tc:
                 got = got + (o.prefill_attention_tc(q, kp, vp, bt.to(DEV), cu.to(DEV), pos.to(DEV), S,
                                                     max(b - a for a, b in spans), chunk, window, hd ** -0.5),)
+                for k in key_splits:      # the same with the key tiles of every block shared among k blocks
+                    got = got + (o.prefill_attention_tc(q, kp, vp, bt.to(DEV), cu.to(DEV), pos.to(DEV), S,
+                                                        max(b - a for a, b in spans), chunk, window, hd ** -0.5,
+                                                        key_splits=k),)
     # plain: whole sequences
     want_q, want_o = [], []
     for s in range(S):
@@ -214,16 +218,21 @@ def test_decode_attention_on_tensor_cores(shape):
                                    (2, 1, 128, 128, 0, 0), (2, 2, 64, 256, 300, 0), (5, 1, 128, 64, 256, 0)])
 def test_prefill_attention_on_tcgen05(shape):
     """The tcgen05 prefill kernel (TMA page loads, S / P V / O in tensor memory) against whole-sequence
-    attention: portions that start inside a sequence, straddle chunks and pages, and end off a tile."""
+    attention: portions that start inside a sequence, straddle chunks and pages, and end off a tile;
+    and the same with the key tiles of every (query tile, head) shared among two, three or five
+    blocks whose rows a merge kernel combines (some shares are empty: fewer tiles than blocks)."""
     o = ops()
     nh, nkv, hd, page, chunk, window = shape
     dt = torch.bfloat16
     assert o.prefill_attention_tc_supported(dt, nh, nkv, hd, page)
     inv = plain.rope_inverse_frequencies(hd, 10000.0, None)
     got, want = paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens=[300, 140, 1, 129], starts=[0, 77, 500, 128],
-                           inv_freq=inv, interleaved=False, qk_norm=True, temp=None, seed=hd + page, split=True, tc=True)
+                           inv_freq=inv, interleaved=False, qk_norm=True, temp=None, seed=hd + page, split=True, tc=True,
+                           key_splits=(2, 3, 5))
     o.check_tc_status()
     close(got[3], want[1].reshape(got[3].shape), 2e-2, f"tcgen05 prefill attention {shape}")
+    for k, shared in zip((2, 3, 5), got[4:]):
+        close(shared, want[1].reshape(shared.shape), 2e-2, f"tcgen05 prefill attention {shape}, keys in {k} shares")
     close(got[1], want[1].reshape(got[1].shape), 2e-2, f"general attention {shape}")
 
 

@@ -54,8 +54,9 @@ def test_rmsnorm_part(dt, tol):
 
     part = build("norm", PartSpec("rmsnorm", {"size": 200, "eps": 3e-4}), env(dt, 200), "n")
     w = fill(part, dt, 1)["n.weight"]
-    x = torch.randn(5, 200) * 2
-    d = torch.randn(5, 200).to(dt)
+    g = torch.Generator().manual_seed(50)
+    x = torch.randn(5, 200, generator=g) * 2
+    d = torch.randn(5, 200, generator=g).to(dt)
     xg = x.clone().to(DEV)
     close(part.forward(xg, d.to(DEV)), plain.rms_norm(x + d.float(), torch.ones(200), 3e-4), tol)
     close(xg, x + d.float(), 1e-7)
@@ -110,7 +111,7 @@ def test_attention_mixer(kind, dt, tol):
     table = {0: torch.arange(blocks, dtype=torch.int32).flip(0).reshape(1, blocks).contiguous()}
     view = CacheView(group=0, k_pages=torch.zeros(blocks, nkv, page, hd, dtype=dt, device=DEV),
                      v_pages=torch.zeros(blocks, nkv, page, hd, dtype=dt, device=DEV))
-    x = torch.randn(T, H).to(dt)
+    x = torch.randn(T, H, generator=torch.Generator().manual_seed(len(kind))).to(dt)   # inputs do not depend on what ran before
     outs = [part.forward(x[a:b].to(DEV).contiguous(), ctx_for([b - a], [a], page, table), view) for a, b in ((0, cut), (cut, T))]
     got = torch.cat(outs)
     # plain, whole sequence, same formulas with this part's options
@@ -149,7 +150,7 @@ def test_feed_forward_parts(dt, tol):
     from hi_b200.parts.spec import PartSpec
 
     H = 88
-    x = torch.randn(37, H).to(dt)
+    x = torch.randn(37, H, generator=torch.Generator().manual_seed(37)).to(dt)
     ctx = ctx_for([37], [0], 4, {})
     dense = build("feed_forward", PartSpec("dense_swiglu", {"hidden_size": H, "intermediate_size": 136}), env(dt, H), "f")
     w = fill(dense, dt, 3, std=0.2)
@@ -225,7 +226,7 @@ def test_embedding_and_head(dt, tol):
     we = fill(emb, dt, 5)["emb.weight"]
     toks = torch.tensor([0, 330, 17, 17], dtype=torch.int32)
     close(emb.forward(toks.to(DEV)), we.float()[toks.long()], 1e-7)
-    z = torch.randn(4, H).to(dt)
+    z = torch.randn(4, H, generator=torch.Generator().manual_seed(4)).to(dt)
     tied = build("head", PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "tie": True}), env(dt, H), "head")
     assert fill(tied, dt, 6) == {}
     out = tied.forward(z.to(DEV), emb)
@@ -254,8 +255,9 @@ def test_block_arrangement(dt, tol):
     w = {}
     for part in layer.parts():
         w.update(fill(part, dt, 9, std=0.12))
-    x = torch.randn(T, H)
-    carried = (torch.randn(T, H) * 0.5).to(dt)
+    g = torch.Generator().manual_seed(257)
+    x = torch.randn(T, H, generator=g)
+    carried = (torch.randn(T, H, generator=g) * 0.5).to(dt)
     blocks = -(-T // page)
     view = CacheView(group=0, k_pages=torch.zeros(blocks, nkv, page, hd, dtype=dt, device=DEV),
                      v_pages=torch.zeros(blocks, nkv, page, hd, dtype=dt, device=DEV))
