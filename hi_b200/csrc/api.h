@@ -92,6 +92,9 @@ long long hb_moe_down_tc_scratch_floats(int sms);
 
 int hb_sample_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* uniforms,
                    int* out, cudaStream_t stream);
+int hb_sample_rows_parts(const float* logits, int rows, int vocab, int parts, const float* temperatures,
+                         const float* uniforms, float* part_val, int* part_idx, float* part_max, float* part_sum,
+                         int* counters, int* out, cudaStream_t stream);
 int hb_ranked_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* top_ps,
                    const int* top_ks, const float* uniforms, int* out, cudaStream_t stream);
 int hb_argmax_rows(const float* logits, int rows, int vocab, int parts, float* part_val, int* part_idx, int* counters,

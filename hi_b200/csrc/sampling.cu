@@ -12,6 +12,7 @@
 namespace {
 
 constexpr int ST = 1024;
+constexpr int SAMPLE_MAX_PARTS = 64;
 
 __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temps,
                                    const float* __restrict__ uniforms, int* __restrict__ out) {
@@ -158,6 +159,208 @@ __global__ void argmax_parts_kernel(const float* __restrict__ logits, int vocab,
     if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
   }
   out[r] = bi == 0x7fffffff ? 0 : bi;
+}
+
+// The same choice as sample_rows_kernel with every row cut into gridDim.y parts, so that a few rows
+// of a large vocabulary are read by many SMs (one block a row reads its 800 KB three times through
+// one SM: about 40 us at 202,048 words). A block leaves of its part: the largest logit and its
+// lowest id, the largest finite scaled logit m_p, and the sum s_p of exp(l/T - m_p) in vocabulary
+// order. The block of a row that finishes last (a counter per row, zero between launches) picks
+// the part that holds u * total, where total = sum_p s_p e^(m_p - M) in part order and M = max m_p,
+// and walks that part alone with the weights exp(l/T - M), as the one-block kernel walks the row.
+__global__ void sample_parts_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temps,
+                                    const float* __restrict__ uniforms, float* part_val, int* part_idx,
+                                    float* part_max, float* part_sum, int* counters, int* __restrict__ out) {
+  __shared__ float scratch[33];
+  __shared__ float sval[ST];
+  __shared__ int sidx[ST];
+  __shared__ int s_last, s_part, s_done;
+  __shared__ float s_m, s_target, s_before;
+  __shared__ float p_val[SAMPLE_MAX_PARTS], p_max[SAMPLE_MAX_PARTS], p_sum[SAMPLE_MAX_PARTS];
+  __shared__ int p_idx[SAMPLE_MAX_PARTS];
+  const int r = blockIdx.x, part = blockIdx.y, parts = gridDim.y, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  const float temp = temps ? temps[r] : 0.f;
+  const bool greedy = !(temp > 0.f) || !isfinite(temp);
+  const int slice = (vocab + parts - 1) / parts;
+  const int begin = min(part * slice, vocab), end = min(begin + slice, vocab);
+  const int chunk = (slice + ST - 1) / ST;          // a thread's run of consecutive words: the order of the vocabulary
+  // ---- this part: argmax with lowest-id ties
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = begin + tid; i < end; i += ST) {
+    const float v = row[i];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  sval[tid] = bv; sidx[tid] = bi;
+  __syncthreads();
+  for (int s = ST / 2; s > 0; s >>= 1) {
+    if (tid < s) {
+      const float ov = sval[tid + s];
+      const int oi = sidx[tid + s];
+      if (ov > sval[tid] || (ov == sval[tid] && oi < sidx[tid])) { sval[tid] = ov; sidx[tid] = oi; }
+    }
+    __syncthreads();
+  }
+  const float top_v = sval[0];
+  const int top_i = sidx[0];
+  // ---- this part: largest finite scaled logit and the sum against it
+  float mp = -INFINITY, sp = 0.f;
+  if (!greedy) {
+    const int cb = min(begin + tid * chunk, end), ce = min(cb + chunk, end);
+    float mx = -INFINITY;
+    for (int i = cb; i < ce; ++i) {
+      const float v = row[i];
+      if (isfinite(v)) {
+        const float sc = v / temp;
+        if (isfinite(sc)) mx = fmaxf(mx, sc);
+      }
+    }
+    mp = hb::block_max(mx, scratch);
+    if (isfinite(mp)) {
+      float local = 0.f;
+      for (int i = cb; i < ce; ++i) {
+        const float v = row[i];
+        if (isfinite(v)) local += expf(v / temp - mp);
+      }
+      sp = hb::block_sum(local, scratch);             // a fixed tree: the same words give the same sum
+    }
+  }
+  if (tid == 0) {
+    const size_t at = (size_t)r * parts + part;
+    part_val[at] = top_v; part_idx[at] = top_i; part_max[at] = mp; part_sum[at] = sp;
+    __threadfence();
+    s_last = atomicAdd(&counters[r], 1) == parts - 1;
+    if (s_last) counters[r] = 0;                      // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // ---- the row's last block: which part, by one thread over the parts in order (a thread a part
+  // fetches what the parts left, so the loads are in flight together)
+  if (tid < parts) {
+    const size_t at = (size_t)r * parts + tid;
+    p_val[tid] = __ldcg(part_val + at); p_idx[tid] = __ldcg(part_idx + at);
+    p_max[tid] = __ldcg(part_max + at); p_sum[tid] = __ldcg(part_sum + at);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float av = -INFINITY;
+    int ai = 0x7fffffff;
+    float big = -INFINITY;
+    for (int q = 0; q < parts; ++q) {
+      const float v = p_val[q];
+      const int i = p_idx[q];
+      if (v > av || (v == av && i < ai)) { av = v; ai = i; }
+      big = fmaxf(big, p_max[q]);
+    }
+    const int arg = ai == 0x7fffffff ? 0 : ai;
+    s_done = 1;
+    out[r] = arg;                                     // greedy rows, and rows without a usable weight
+    if (!greedy && isfinite(big)) {
+      float total = 0.f;
+      for (int q = 0; q < parts; ++q)
+        if (isfinite(p_max[q])) total += p_sum[q] * expf(p_max[q] - big);
+      if (total > 0.f && isfinite(total)) {
+        float u = uniforms ? uniforms[r] : 0.f;
+        u = isfinite(u) ? fminf(fmaxf(u, 0.f), 0.99999994f) : 0.f;
+        const float target = u * total;
+        float before = 0.f, last_before = 0.f;
+        int pick = -1, last = -1;
+        for (int q = 0; q < parts && pick < 0; ++q) {
+          const float w = isfinite(p_max[q]) ? p_sum[q] * expf(p_max[q] - big) : 0.f;
+          if (w > 0.f) {
+            last = q; last_before = before;
+            if (target < before + w) pick = q; else before += w;
+          }
+        }
+        if (pick < 0) { pick = last; before = last_before; }     // rounding left the target past every part
+        if (pick >= 0) { s_done = 0; s_part = pick; s_m = big; s_target = target; s_before = before; }
+      }
+    }
+  }
+  __syncthreads();
+  if (s_done) return;
+  // ---- walk the chosen part with the row's weights
+  const int pb = min(s_part * slice, vocab), pe = min(pb + slice, vocab);
+  const int cb = min(pb + tid * chunk, pe), ce = min(cb + chunk, pe);
+  const float mx = s_m, target = s_target;
+  float local = 0.f;
+  int last_pos = -1;                                  // this thread's last word with a positive weight
+  for (int i = cb; i < ce; ++i) {
+    const float v = row[i];
+    if (isfinite(v)) {
+      const float w = expf(v / temp - mx);
+      local += w;
+      if (w > 0.f) last_pos = i;
+    }
+  }
+  // Exclusive prefix of the threads' sums, in thread order (warp scans, then the warps' totals), and
+  // the part's last word with a weight. Thread t owns the targets in [prefix_t, prefix_(t+1)): the
+  // bounds are the same numbers for both neighbours, so every target has exactly one owner.
+  const int lane = tid & 31, warp = tid >> 5;
+  float incl = local;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const float up = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += up;
+  }
+  int last_any = last_pos;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) last_any = max(last_any, __shfl_xor_sync(0xffffffffu, last_any, d));
+  if (lane == 31) scratch[warp] = incl;
+  if (lane == 0) sidx[warp] = last_any;
+  __syncthreads();
+  if (warp == 0) {
+    float t = scratch[lane];                          // ST / 32 = 32 warps
+    float ti = t;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, ti, d);
+      if (lane >= d) ti += up;
+    }
+    scratch[lane] = ti - t;                           // exclusive: what the warps before this one hold
+    int la = sidx[lane];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) la = max(la, __shfl_xor_sync(0xffffffffu, la, d));
+    if (lane == 0) s_part = la;
+  }
+  __syncthreads();
+  const float prefix = s_before + scratch[warp] + (incl - local);
+  const int fallback = s_part;
+  sval[tid] = prefix;
+  __syncthreads();
+  const float upper = tid + 1 < ST ? sval[tid + 1] : INFINITY;
+  __syncthreads();
+  sidx[tid] = 0x7fffffff;
+  if (target >= prefix && target < upper) {
+    float cum = prefix;
+    int pick = -1, last = -1;
+    for (int i = cb; i < ce; ++i) {
+      const float v = row[i];
+      if (!isfinite(v)) continue;
+      const float w = expf(v / temp - mx);
+      if (w <= 0.f) continue;
+      last = i;
+      cum += w;
+      if (target < cum) { pick = i; break; }
+    }
+    sidx[tid] = pick >= 0 ? pick : last;              // (-1: no word with a weight here; the fallback below)
+  }
+  __syncthreads();
+  // at most one thread owned the target
+  int mine = sidx[tid];
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) mine = min(mine, __shfl_xor_sync(0xffffffffu, mine, d));
+  __syncthreads();
+  if (lane == 0) sidx[warp] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    int pick = 0x7fffffff;
+    for (int i = 0; i < ST / 32; ++i) pick = min(pick, sidx[i]);
+    if (pick == 0x7fffffff || pick < 0) pick = fallback;          // rounding: the part's last word with a weight
+    if (pick >= 0) out[r] = pick;
+  }
 }
 
 // ---------------------------------------------------------------- ranked rows (top-k / top-p)
@@ -346,6 +549,21 @@ extern "C" int hb_ranked_rows(const float* logits, int rows, int vocab, const fl
   if (!logits || !temperatures || !top_ps || !top_ks || !uniforms || !out || rows < 0 || vocab <= 0) return HB_ERR_BAD_ARG;
   if (rows == 0) return HB_OK;
   ranked_rows_kernel<<<rows, RANK_THREADS, 0, stream>>>(logits, vocab, temperatures, top_ps, top_ks, uniforms, out);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+// hb_sample_rows with every row cut into `parts` blocks; part_val, part_idx, part_max, part_sum hold
+// rows * parts entries each, counters rows ints that are zero between launches.
+extern "C" int hb_sample_rows_parts(const float* logits, int rows, int vocab, int parts, const float* temperatures,
+                                    const float* uniforms, float* part_val, int* part_idx, float* part_max,
+                                    float* part_sum, int* counters, int* out, cudaStream_t stream) {
+  if (!logits || !out || !part_val || !part_idx || !part_max || !part_sum || !counters || rows < 0 || vocab <= 0 ||
+      parts <= 0 || parts > SAMPLE_MAX_PARTS)
+    return HB_ERR_BAD_ARG;
+  if (rows == 0) return HB_OK;
+  sample_parts_kernel<<<dim3(rows, parts), ST, 0, stream>>>(logits, vocab, temperatures, uniforms, part_val, part_idx,
+                                                            part_max, part_sum, counters, out);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

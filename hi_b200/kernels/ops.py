@@ -41,6 +41,7 @@ _SIGNATURES = {
     "hb_argmax_rows": [P, I, I, I, P, P, P, P, P],
     "hb_ranked_rows": [P, I, I, P, P, P, P, P, P],
     "hb_sample_rows": [P, I, I, P, P, P, P],
+    "hb_sample_rows_parts": [P, I, I, I, P, P, P, P, P, P, P, P, P],
     "hb_random_normal": [P, I, c_longlong, c_longlong, c_uint64, F, P],
 }
 
@@ -799,6 +800,8 @@ def moe_down_tc(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan) -> torch
 ARGMAX_PARTS = 16            # blocks per row of the all-greedy sampler
 ARGMAX_MAX_ROWS = 1024
 ARGMAX_MIN_VOCAB = 8192
+SAMPLE_PARTS = 16            # blocks per row of the sampler with temperatures, for steps of few rows
+SAMPLE_PARTS_MAX_BLOCKS = 2048   # beyond 128 rows a block per row keeps the GPU as busy
 _argmax_scratch: dict = {}   # device -> (values, ids, counters); shared by launches that follow one another
 
 
@@ -807,7 +810,9 @@ def _argmax_buffers(dev):
     if b is None:
         b = _argmax_scratch[dev] = (torch.empty(ARGMAX_MAX_ROWS * ARGMAX_PARTS, dtype=torch.float32, device=dev),
                                     torch.empty(ARGMAX_MAX_ROWS * ARGMAX_PARTS, dtype=torch.int32, device=dev),
-                                    torch.zeros(ARGMAX_MAX_ROWS, dtype=torch.int32, device=dev))
+                                    torch.zeros(ARGMAX_MAX_ROWS, dtype=torch.int32, device=dev),
+                                    torch.empty(ARGMAX_MAX_ROWS * ARGMAX_PARTS, dtype=torch.float32, device=dev),
+                                    torch.empty(ARGMAX_MAX_ROWS * ARGMAX_PARTS, dtype=torch.float32, device=dev))
     return b
 
 
@@ -820,7 +825,7 @@ def sample_rows(logits: torch.Tensor, temperatures: Optional[torch.Tensor],
     rows, vocab = logits.shape
     if temperatures is None and rows <= ARGMAX_MAX_ROWS and vocab >= ARGMAX_MIN_VOCAB:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-        vals, ids, counters = _argmax_buffers(logits.device)
+        vals, ids, counters = _argmax_buffers(logits.device)[:3]
         _check(lib().hb_argmax_rows(_ptr(logits), rows, vocab, ARGMAX_PARTS, _ptr(vals), _ptr(ids), _ptr(counters),
                                     _ptr(out), _stream()), "argmax_rows")
         return out
@@ -830,6 +835,13 @@ def sample_rows(logits: torch.Tensor, temperatures: Optional[torch.Tensor],
             if t.numel() != rows:
                 raise KernelError(f"{nm} needs one entry per row")
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if rows * SAMPLE_PARTS <= SAMPLE_PARTS_MAX_BLOCKS and vocab >= ARGMAX_MIN_VOCAB:
+        # a few rows of a large vocabulary: every row over SAMPLE_PARTS blocks, the last of them picks
+        vals, ids, counters, maxima, sums = _argmax_buffers(logits.device)
+        _check(lib().hb_sample_rows_parts(_ptr(logits), rows, vocab, SAMPLE_PARTS, _ptr(temperatures), _ptr(uniforms),
+                                          _ptr(vals), _ptr(ids), _ptr(maxima), _ptr(sums), _ptr(counters), _ptr(out),
+                                          _stream()), "sample_rows_parts")
+        return out
     _check(lib().hb_sample_rows(_ptr(logits), rows, vocab, _ptr(temperatures), _ptr(uniforms), _ptr(out), _stream()),
            "sample_rows")
     return out

@@ -534,6 +534,49 @@ def test_sampling_kernel_matches_the_plain_sampler():
         assert got == want, f"vocab {vocab}: {got} != {want}"
 
 
+def test_sampling_with_rows_cut_over_many_blocks():
+    """Few rows of a large vocabulary are cut over 16 blocks each and the block that finishes last
+    picks. The pick must be the word at which the running sum of the weights, in vocabulary order,
+    passes u * total: checked in float64, with 2e-5 of the total for the kernel's float32 sums (the
+    choice is a threshold on a sum of 200,000 terms; u = 0 and a row whose whole weight is one word
+    are checked exactly). Peaked and flat rows, rows that are greedy beside rows that sample, logits
+    that are not finite, parts without any weight, and the same again on later calls (the counters
+    were left at zero)."""
+    o = ops()
+    g = torch.Generator().manual_seed(77)
+    for vocab, rows in ((8192, 5), (50000, 16), (202048, 8), (202049, 3)):
+        logits = torch.randn(rows, vocab, generator=g) * torch.linspace(0.5, 6.0, rows)[:, None]
+        logits[0, vocab - 1] = 200.0                              # all of the weight in the last word
+        logits[1, 5] = float("-inf")
+        if rows > 3:
+            logits[3, : vocab // 2] = float("-inf")               # whole parts without weight
+        temps = torch.tensor([0.7, 0.0, 1.0, 1.3, 0.5, 2.0, 0.9, 1.0, 0.0, 0.3, 1.0, 1.0, 5.0, 1.0, 0.8, 1.1][:rows])
+        for turn in range(3):
+            us = torch.rand(rows, generator=g)
+            us[turn % rows] = 0.0
+            us[(turn + 1) % rows] = 0.99999994
+            got = o.sample_rows(logits.to(DEV), temps.to(DEV), us.to(DEV)).cpu().tolist()
+            for r in range(rows):
+                what = f"vocab {vocab} turn {turn} row {r}: picked {got[r]}"
+                if not float(temps[r]) > 0:
+                    assert got[r] == int(torch.argmax(logits[r])), what
+                    continue
+                z = (logits[r] / float(temps[r])).double()
+                w = torch.exp(z - z[torch.isfinite(z)].max())
+                w[~torch.isfinite(z)] = 0.0
+                total = float(w.sum())
+                before = float(w[: got[r]].sum())
+                target = float(us[r]) * total
+                assert float(w[got[r]]) > 0, what + ", a word without weight"
+                if float(us[r]) == 0.0:
+                    first = int(torch.nonzero(torch.exp((z - z[torch.isfinite(z)].max()).float()) > 0)[0])
+                    assert got[r] == first, what + f", not the first word with a float32 weight ({first})"
+                else:
+                    assert before <= target + 2e-5 * total and target < before + float(w[got[r]]) + 2e-5 * total, \
+                        what + f": sum before {before / total:.7f}, its weight {float(w[got[r]]) / total:.2e}, u {float(us[r]):.7f}"
+            assert got[0] == vocab - 1
+
+
 def test_kernels_refuse_what_they_cannot_do():
     o = ops()
     from hi_b200.kernels.ops import KernelError
