@@ -668,7 +668,105 @@ def case_prefill_step(tokens=2048, layers=2):
     torch.cuda.synchronize()
 
 
-CASES = {"decode_attention": case_decode_attention, "decode_attention_fused": case_decode_attention_fused, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
+def case_sweep():
+    """The hot kernels alone over further sizes, timed with CUDA events (median of five, a buffer
+    larger than L2 written between calls), with their fractions of the measured peaks: decode
+    attention by batch and context, the expert products by the number of routed tokens (the kernel
+    the feed-forward part would pick), prefill attention by portion length and offset. Markdown."""
+    import torch
+
+    from hi_b200.kernels import ops
+    from hi_b200.parts.attention import AttentionMixer
+    from hi_b200.parts.feed_forward import SigmoidRoutedExperts
+
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    g = torch.Generator(device=DEV).manual_seed(0)
+
+    def timed(fn):
+        fn()
+        ts = []
+        for _ in range(5):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return sorted(ts)[2]
+
+    nh, nkv, hd, page = 40, 8, 128, 64
+    print(f"peaks: {pk['hbm_gbs']:.1f} GB/s copy, {pk['bf16_tflops']:.1f} TFLOP/s bf16 ({pk['source']}); times include the launch\n")
+    print("decode attention, 40 heads / 8 kv heads, head_dim 128 (one launch: q/k/v encoding, append, attention, merge; "
+          "from 256 (token, kv head) pairs on: qkv_post + attention + merge)\n")
+    print("| requests | keys each | us | GB/s of K and V | of the copy peak |\n|---|---|---|---|---|")
+    for context in (1024, 8192, 32768, 65536):
+        for batch in (1, 2, 4, 8, 16, 32, 64):
+            if batch * context > 64 * 8192 * 2:
+                continue
+            blocks = -(-context // page)
+            kp = torch.randn(batch * blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+            vp = torch.randn(batch * blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+            bt = torch.randperm(batch * blocks, device=DEV, generator=g).to(torch.int32).view(batch, blocks).contiguous()
+            qkv = torch.randn(batch, (nh + 2 * nkv) * hd, device=DEV, generator=g).to(torch.bfloat16)
+            pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+            sot = torch.arange(batch, dtype=torch.int32, device=DEV)
+
+            def attend():
+                o = ops.decode_attention_fused(qkv, nh, nkv, hd, pos, None, False, True, 1e-6, (8192.0, 0.1), sot, bt, kp, vp,
+                                               0, 0, hd ** -0.5, context)
+                if o is None:
+                    q = ops.qkv_post(qkv, nh, nkv, hd, pos, None, False, True, 1e-6, (8192.0, 0.1), sot, bt, kp, vp, page, True)
+                    ops.decode_attention(q, kp, vp, bt, sot, pos, 0, 0, hd ** -0.5, context)
+
+            us = timed(attend)
+            gbs = batch * context * 2 * nkv * hd * 2 / us / 1e3
+            print(f"| {batch} | {context} | {us:.1f} | {gbs:.0f} | {gbs / pk['hbm_gbs']:.2f} |")
+            del kp, vp
+    x, wg, wu, wd, scores, _plan = _experts(16, 4096)
+    print("\nrouted experts, 16 experts top-1, hidden 5120, intermediate 8192: gate/up + SwiGLU, then down\n")
+    print("| tokens | experts with rows | kernels | us | GB/s of expert weights | of the copy peak |\n|---|---|---|---|---|---|")
+    for n in (1, 2, 4, 8, 10, 12, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096):
+        ids = torch.randint(0, 16, (n, 1), device=DEV, generator=g).to(torch.int32)
+        plan = ops.moe_plan(ids, 16)
+        distinct = int(torch.unique(ids).numel())
+        few = n <= SigmoidRoutedExperts.FEW_ROWS
+
+        def experts():
+            if few:
+                ops.moe_down(ops.moe_gate_up(x[:n], plan, 1, wg, wu, scores[:n], True), wd, plan, True)
+            else:
+                ops.moe_down_tc(ops.moe_gate_up_tc(x[:n], plan, 1, wg, wu, scores[:n]), wd, plan)
+
+        us = timed(experts)
+        gbs = distinct * 3 * 8192 * 5120 * 2 / us / 1e3
+        print(f"| {n} | {distinct} | {'weight streaming' if few else 'tcgen05'} | {us:.1f} | {gbs:.0f} | {gbs / pk['hbm_gbs']:.2f} |")
+    ops.check_tc_status()
+    del x, wg, wu, wd
+    print("\nprefill attention (tcgen05), one request, 40 heads / 8 kv heads, head_dim 128, a layer that sees every key\n")
+    print("| new tokens | cached before | key shares | us | TFLOP/s | of sustained bf16 |\n|---|---|---|---|---|---|")
+    for cached in (0, 8192, 61440):
+        for tokens in (128, 256, 512, 1024, 2048, 4096, 8192):
+            if cached and tokens > 4096:
+                continue
+            total = tokens + cached
+            blocks = -(-total // page)
+            kp = torch.randn(blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+            vp = torch.randn(blocks, nkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+            bt = torch.randperm(blocks, device=DEV, generator=g).to(torch.int32).view(1, blocks).contiguous()
+            q = torch.randn(tokens, nh, hd, device=DEV, generator=g).to(torch.bfloat16)
+            pos = torch.arange(cached, total, dtype=torch.int32, device=DEV)
+            cu = torch.tensor([0, tokens], dtype=torch.int32, device=DEV)
+            shares = 1
+            if cached >= 2 * tokens:
+                shares = ops.prefill_key_splits(nh * -(-tokens // 128), cached // 64, ops.sm_count(DEV))
+            us = timed(lambda: ops.prefill_attention_tc(q, kp, vp, bt, cu, pos, 1, tokens, 0, 0, hd ** -0.5, key_splits=shares))
+            tf = 4 * nh * hd * (tokens * cached + tokens * (tokens + 1) / 2) / us / 1e6
+            print(f"| {tokens} | {cached} | {shares} | {us:.1f} | {tf:.0f} | {tf / pk['bf16_tflops']:.2f} |")
+            del kp, vp
+    ops.check_tc_status()
+
+
+CASES = {"sweep": case_sweep, "decode_attention": case_decode_attention, "decode_attention_fused": case_decode_attention_fused, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
          "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step}
 
 
