@@ -102,9 +102,8 @@ def paged_case(o, dt, nh, nkv, hd, page, chunk, window, lens, starts, inv_freq, 
                                        chunk, window, hd ** -0.5)
             got = (q, out, fast)
             if tc:
-                got = got + (o.prefill_attention_tc(q, kp, vp, bt.to(DEV), cu.to(DEV), pos.to(DEV), S,
-                                                    max(b - a for a, b in spans), chunk, window, hd ** -0.5),)
-                for k in key_splits:      # the same with the key tiles of every block shared among k blocks
+                # and the same with the key tiles of every block shared among k blocks
+                for k in (1,) + tuple(key_splits):
                     got = got + (o.prefill_attention_tc(q, kp, vp, bt.to(DEV), cu.to(DEV), pos.to(DEV), S,
                                                         max(b - a for a, b in spans), chunk, window, hd ** -0.5,
                                                         key_splits=k),)
@@ -230,9 +229,10 @@ def test_prefill_attention_on_tcgen05(shape):
                            inv_freq=inv, interleaved=False, qk_norm=True, temp=None, seed=hd + page, split=True, tc=True,
                            key_splits=(2, 3, 5))
     o.check_tc_status()
-    close(got[3], want[1].reshape(got[3].shape), 2e-2, f"tcgen05 prefill attention {shape}")
-    for k, shared in zip((2, 3, 5), got[4:]):
-        close(shared, want[1].reshape(shared.shape), 2e-2, f"tcgen05 prefill attention {shape}, keys in {k} shares")
+    labels = ["one block per query tile and head"] + [f"keys in {k} shares" for k in (2, 3, 5)]
+    assert len(got) == 3 + len(labels)
+    for label, res in zip(labels, got[3:]):
+        close(res, want[1].reshape(res.shape), 2e-2, f"tcgen05 prefill attention {shape}, {label}")
     close(got[1], want[1].reshape(got[1].shape), 2e-2, f"general attention {shape}")
 
 
