@@ -589,7 +589,7 @@ def test_portions_far_into_a_context_share_their_keys_among_blocks(tmp_path, mon
     with long runs of keys; the global layers then let several blocks share a block's keys and a
     merge kernel combines their rows. The thresholds are lowered so that a 700-token request shows
     it (in use they ask for 32,768 cached tokens): portions of 130 and 140 tokens behind 384 and
-    514, two requests side by side, every row against the plain model."""
+    514, two requests side by side and a third that decodes beside them, every row against the plain model."""
     from hi_b200.engine.core import Engine
     from hi_b200.kernels import ops
 
@@ -599,8 +599,9 @@ def test_portions_far_into_a_context_share_their_keys_among_blocks(tmp_path, mon
                attention_chunk_size=256, intermediate_size=64, intermediate_size_mlp=128, vocab_size=211,
                num_hidden_layers=4, nope_layer_interval=2)
     mdir = h.make_model(str(tmp_path / "m"), cfg, seed=9, std=0.05)
-    reqs = {"a": h.random_tokens(cfg, 700, seed=1), "b": h.random_tokens(cfg, 660, seed=2)}
-    cuts = {"a": [384, 130, 140, 46], "b": [400, 131, 129]}
+    # "c" decodes single tokens beside the portions of "a" and "b": its rows go through the decode kernel
+    reqs = {"a": h.random_tokens(cfg, 700, seed=1), "b": h.random_tokens(cfg, 660, seed=2), "c": h.random_tokens(cfg, 43, seed=3)}
+    cuts = {"a": [384, 130, 140, 46], "b": [400, 131, 129], "c": [40, 1, 1, 1]}
     steps, at = [], {r: 0 for r in reqs}
     for i in range(4):
         entries = []
@@ -619,7 +620,7 @@ def test_portions_far_into_a_context_share_their_keys_among_blocks(tmp_path, mon
         return real(*args, **kw)
 
     monkeypatch.setattr(ops, "prefill_attention_tc", spy)
-    eng = Engine.from_dir(mdir, dtype="bfloat16", kv_page_size=16, kv_cache_tokens=1536, max_active_requests=2)
+    eng = Engine.from_dir(mdir, dtype="bfloat16", kv_page_size=16, kv_cache_tokens=1536, max_active_requests=3)
     got, forced = h.replay_in_process(eng, steps, record_routing=True)
     assert max(seen) > 1, f"no launch shared its keys (shares seen: {sorted(set(seen))})"
     assert 1 in seen, "the layers with chunked attention keep one block per query tile and head"
