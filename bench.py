@@ -766,7 +766,77 @@ def case_sweep():
     ops.check_tc_status()
 
 
-CASES = {"sweep": case_sweep, "decode_attention": case_decode_attention, "decode_attention_fused": case_decode_attention_fused, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
+def _timeline(run, warm, what):
+    """Kernel starts and ends of one step from the profiler's activity records (real durations, with
+    what runs beside what), as markdown: the first two layers' launches, then totals by kernel."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    for _ in range(warm):
+        run()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type.name == "CUDA" and "emcpy" not in e.name and "emset" not in e.name]
+    evs.sort(key=lambda e: e.time_range.start)
+    name = lambda e: e.name.replace("void ", "").replace("(anonymous namespace)::", "").split("(")[0][:58]
+    t0 = evs[0].time_range.start
+    span = evs[-1].time_range.end - t0
+    print(f"{what}: {len(evs)} kernels in {span:.0f} us\n")
+    print("| start us | end us | us | kernel |\n|---|---|---|---|")
+    norms = 0
+    for e in evs:
+        norms += "add_rmsnorm" in e.name
+        if norms > 5:                       # two layers: four norms, then the third layer's first
+            break
+        print(f"| {e.time_range.start - t0:.1f} | {e.time_range.end - t0:.1f} | {e.time_range.end - e.time_range.start:.1f} | {name(e)} |")
+    agg = {}
+    for e in evs:
+        a = agg.setdefault(name(e), [0, 0.0])
+        a[0] += 1
+        a[1] += e.time_range.end - e.time_range.start
+    print("\n| kernel | launches | us in all | us each |\n|---|---|---|---|")
+    for k, (c, v) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        print(f"| {k} | {c} | {v:.1f} | {v / c:.1f} |")
+
+
+def case_decode_timeline(batch=8, context=8192, layers=4):
+    """One captured decode step of ``batch`` requests at ``context`` cached tokens: when each kernel ran."""
+    import torch
+
+    from hi_b200.engine.core import StepEntry
+
+    eng = _case_engine(layers, batch * (context + 128), batch + 1)
+    eng.use_cuda_graphs = True
+    for view in eng.cache.views.values():
+        view.k_pages.normal_(); view.v_pages.normal_()
+    for i in range(batch):
+        eng.assume_cached(i, context - 16)
+    g = torch.Generator().manual_seed(0)
+    step = lambda: eng.step([StepEntry(i, [int(torch.randint(0, 202048, (1,), generator=g))], [0]) for i in range(batch)])
+    _timeline(step, 6, f"decode step, {batch} requests x {context} cached tokens, {layers} Scout-sized layers, captured graph")
+
+
+def case_prefill_timeline(tokens=2048, layers=4):
+    """One prompt of ``tokens`` tokens in one step: when each kernel ran."""
+    import torch
+
+    from hi_b200.engine.core import StepEntry
+
+    eng = _case_engine(layers, tokens + 128, 2)
+    g = torch.Generator().manual_seed(0)
+    count = [0]
+
+    def step():
+        count[0] += 1
+        eng.step([StepEntry(count[0], torch.randint(0, 202048, (tokens,), generator=g).tolist(), [tokens - 1])])
+        eng.finish(count[0])
+
+    _timeline(step, 3, f"prefill step, one prompt of {tokens} tokens, {layers} Scout-sized layers")
+
+
+CASES = {"sweep": case_sweep, "decode_timeline": case_decode_timeline, "prefill_timeline": case_prefill_timeline, "decode_attention": case_decode_attention, "decode_attention_fused": case_decode_attention_fused, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
          "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step}
 
 
